@@ -1,0 +1,334 @@
+#!/usr/bin/env python
+"""CP4 conv2d forward + backward-data + backward-filter throughput (images/s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: the configuration the headline metric is quoted on -- N=32 images per GPU,
+C=T=64, 56x56, 3x3 filter, rank 16, same padding, fp32, seeded synthetic inputs.
+One step = forward, backward-data and backward-filter over one batch (plus the allreduce
+of the packed factor gradients when more than one GPU runs).  Batches are sharded across
+ranks (weak scaling: every rank owns N=32 images).
+
+Timing: CUDA events on the launching stream; a barrier + synchronize on both sides; the
+maximum over ranks.  Every step uses the next of several distinct buffer sets so that a set
+is evicted from L2 before it is used again.  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(N=32, C=64, T=64, H=56, W=56, F=3, R=16, pad=1)
+WORKLOAD = "cp4_conv2d fwd+bwd_data+bwd_filter N=32/GPU C=T=64 56x56 3x3 R=16 same-pad fp32"
+METRIC = "CP4 conv fwd+bwd images/sec"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def make_inputs(seed, n):
+    from oracle.cp_oracle import make_cp4_inputs  # seeded generator shared with the tests
+    return make_cp4_inputs(seed, n, CFG["C"], CFG["T"], CFG["H"], CFG["W"], CFG["F"], CFG["F"], CFG["R"])
+
+
+def synth_inputs(seed, n):
+    """Same distributions as the test generator, without importing the oracle (used by the GPU arm)."""
+    rng = np.random.default_rng(seed)
+    c = CFG
+    std = 1.0 / np.sqrt(c["C"] * c["F"] * c["F"])
+    X = rng.uniform(-1, 1, size=(n, c["C"], c["H"], c["W"])).astype(np.float32)
+    K0 = rng.normal(0, std, size=(c["T"], c["R"])).astype(np.float32)
+    K1 = rng.normal(0, std, size=(c["C"], c["R"])).astype(np.float32)
+    KH = rng.normal(0, std, size=(c["F"], c["R"])).astype(np.float32)
+    KW = rng.normal(0, std, size=(c["F"], c["R"])).astype(np.float32)
+    dU = rng.normal(0, 1, size=(n, c["T"], c["H"], c["W"])).astype(np.float32)
+    return X, K0, K1, KH, KW, dU
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled during the timed region."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def cpu_step_fn(n):
+    """The reference's CPU path: its unfused CP-layer composition (test/layers.py:265-283) restated for
+    torch-CPU, forward + autograd backward, on all host threads."""
+    from oracle import cpu_composition as CC
+    X, K0, K1, KH, KW, dU = [torch.from_numpy(a) for a in make_inputs(1, n)]
+
+    def step():
+        CC.cp4_step(X, K0, K1, KH, KW, dU, CFG["pad"])
+    return step
+
+
+def time_cpu(n, steps, warmup, budget_s):
+    step = cpu_step_fn(n)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    done = 0
+    while done < steps and (time.perf_counter() - t0 < budget_s or done == 0):
+        step()
+        done += 1
+    dt = (time.perf_counter() - t0) / done
+    return n / dt, dt, done
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU path on this box's host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    n = CFG["N"]
+    ips, dt, done = time_cpu(n, args.steps, args.warmup, budget_s=120.0)
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": ips, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": done, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded; X~U[-1,1], factors~N(0,1/sqrt(9C)), dU~N(0,1))",
+        "config": {"workload": WORKLOAD, "images_per_step": n},
+        "cpu_baseline": {"value": ips, "unit": "images/s", "cores": cores, "kind": "port",
+                         "sample": f"{done} full steps of N={n} (torch-CPU restatement of the unfused composition)"},
+        "e2e": {"value": ips, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=60)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc3x"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import paralleltnnlayers_b200 as P   # raises if libb200cp.so is missing: there is no fallback
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    flags = {"auto": P.PATH_AUTO, "simt": P.PATH_SIMT, "tc3x": P.PATH_TC3X}[args.path]
+
+    c = CFG
+    n = c["N"]
+    HW = c["H"] * c["W"]
+    X, K0, K1, KH, KW, dU = synth_inputs(1000 + rank, n)
+    fac = [torch.from_numpy(a).cuda() for a in (K0, K1, KH, KW)]
+    # distinct buffer sets: (X, dU, U, dX) = 4 * 25.7 MB each; 6 sets = 617 MB >> 126 MB of L2
+    NSETS = 6
+    Xd, dUd = torch.from_numpy(X).cuda(), torch.from_numpy(dU).cuda()
+    sets = []
+    for i in range(NSETS):
+        sets.append((Xd.clone() if i else Xd, dUd.clone() if i else dUd,
+                     torch.empty((n, c["T"], c["H"], c["W"]), device="cuda"),
+                     torch.empty((n, c["C"], c["H"], c["W"]), device="cuda")))
+    nK = (c["T"] + c["C"] + 2 * c["F"]) * c["R"]
+    dK = torch.empty(nK, device="cuda")
+    import ctypes as C
+    s = P.tensor_shape(n, c["C"], c["H"], c["W"], c["T"], c["F"], c["F"], c["R"], c["pad"])
+    lib = P._lib.lib
+    wsb = lib.b200cp_cp4_bwd_filter_workspace_bytes(C.byref(s), flags)
+    ws = torch.empty(wsb // 4, device="cuda")
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    fp = [ptr(f) for f in fac]
+
+    def step(i, ev=None):
+        x, du, u, dx = sets[i % NSETS]
+        if ev:
+            ev[0].record()
+        P._lib.check(lib.b200cp_cp4_fwd(C.byref(s), ptr(x), *fp, ptr(u), st, flags))
+        if ev:
+            ev[1].record()
+        P._lib.check(lib.b200cp_cp4_bwd_data(C.byref(s), ptr(du), *fp, ptr(dx), st, flags))
+        if ev:
+            ev[2].record()
+        P._lib.check(lib.b200cp_cp4_bwd_filter(C.byref(s), ptr(x), ptr(du), *fp, ptr(dK), ptr(ws), wsb, st, flags))
+        if ev:
+            ev[3].record()
+        if dist is not None:
+            dist.all_reduce(dK)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    K = args.steps
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    l0 = P.launch_count()
+    e0.record()
+    for i in range(K):
+        step(i, evs[i])
+    e1.record()
+    barrier()
+    launches = P.launch_count() - l0
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    kt = np.array([[evs[i][j].elapsed_time(evs[i][j + 1]) for j in range(3)] for i in range(K)])  # ms
+    if dist is not None:
+        tms = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+        tl = torch.tensor([launches], device="cuda", dtype=torch.int64)
+        dist.all_reduce(tl)
+        launches = int(tl.item())
+    value = world * n * K / (ms * 1e-3)
+
+    # ---- end to end: host buffers through the C ABI's host entry point ------------------------
+    Ks = max(3, min(K, 10))
+    hX, hdU = torch.from_numpy(X).pin_memory(), torch.from_numpy(dU).pin_memory()
+    hf = [torch.from_numpy(a).pin_memory() for a in (K0, K1, KH, KW)]
+    hout = (torch.empty((n, c["T"], c["H"], c["W"])).pin_memory(), torch.empty((n, c["C"], c["H"], c["W"])).pin_memory(),
+            torch.empty(nK).pin_memory())
+    for _ in range(2):
+        P.cp4_conv2d_step_host(hX, hdU, *hf, pad=c["pad"], flags=flags, out=hout)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(Ks):
+        P.cp4_conv2d_step_host(hX, hdU, *hf, pad=c["pad"], flags=flags, out=hout)
+        if dist is not None:   # the gradient exchange of a data-parallel step, on the host-visible result
+            g = hout[2].cuda(non_blocking=True)
+            dist.all_reduce(g)
+            hout[2].copy_(g)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        te = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_s = float(te.item())
+    h2d = 4 * (X.size + dU.size + sum(a.numel() for a in hf))
+    d2h = 4 * sum(a.numel() for a in hout)
+    e2e = world * n * Ks / e2e_s
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel ---------------------------------------------------------
+    names = ["cp4_fwd", "cp4_bwd_data", "cp4_bwd_filter"]
+    mean_ms = kt.mean(axis=0)
+    dom = int(np.argmax(mean_ms))
+    alg_bytes = 4 * n * HW * (c["C"] + c["T"]) + 4 * c["R"] * (c["T"] + c["C"] + 2 * c["F"])
+    peak, peak_kind = hbm_peak()
+    achieved = alg_bytes / (mean_ms[dom] * 1e-3) / 1e9
+    traffic = None
+    try:
+        traffic = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json"))).get(names[dom])
+    except Exception:
+        pass
+    roofline = {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
+                "algorithmic_bytes_per_launch": alg_bytes,
+                "per_kernel_us": {nm: float(v * 1e3) for nm, v in zip(names, mean_ms)},
+                "per_kernel_frac": {nm: float(alg_bytes / (v * 1e-3) / 1e9 / peak) for nm, v in zip(names, mean_ms)}}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        ips, dt, done = time_cpu(n, 1000, 1, budget_s=15.0)
+        cpu = {"value": ips, "unit": "images/s", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{done} full steps of N={n} in {dt * done:.1f} s (torch-CPU restatement of the reference's "
+                         "unfused composition, forward + autograd backward)"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic (seeded; X~U[-1,1], factors~N(0,1/sqrt(9C)), dU~N(0,1))",
+        "config": {"workload": WORKLOAD, "images_per_step_per_gpu": n, "path": args.path,
+                   "l2": f"{NSETS} rotating buffer sets ({NSETS * 4 * n * HW * 64 * 4 / 1e6:.0f} MB) > 126 MB L2",
+                   "collective": "allreduce of %d packed factor-gradient floats" % nK if world > 1 else "none"},
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ks},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,152 @@
+/* b200cp -- C ABI of the B200 (sm_100a) fused CP-decomposed layer kernels.
+ *
+ * Plain C: pointers, sizes, an opaque stream handle.  Every pointer named
+ * "device" must be device memory of the current CUDA device; the *_host entry
+ * points take ordinary host memory and do the transfers themselves.  All
+ * tensors are fp32, row-major, last index fastest:
+ *
+ *   X  [N, C, H, W]   U, dU [N, T, H, W]
+ *   K0 [T, R]  K1 [C, R]  KH [Y, R]  KW [X, R]      (the reference's FT, FC, FY, FX)
+ *
+ * Every function returns a b200cp_status (0 = ok, negative = error, nothing
+ * was launched unless stated).  Calls are asynchronous on `stream` (a
+ * cudaStream_t passed as void*; NULL = the default stream) and re-entrant
+ * across streams and devices; no function allocates device memory except the
+ * *_host helpers and those that say so.
+ */
+#ifndef B200CP_H
+#define B200CP_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+/* Same field order and types as the reference's `struct tensor_shape`
+ * (Cuda_kernels/Tensor.cuh:10-19): N H W pad T C Y X Rank. */
+typedef struct b200cp_tensor_shape {
+  unsigned N, H, W, pad, T, C, Y, X, Rank;
+} b200cp_tensor_shape;
+
+typedef enum b200cp_status {
+  B200CP_OK = 0,
+  B200CP_ERR_INVALID_ARG = -1,  /* null pointer, zero dimension, misaligned buffer */
+  B200CP_ERR_UNSUPPORTED = -2,  /* shape outside what the kernels implement       */
+  B200CP_ERR_WORKSPACE = -3,    /* workspace missing or too small                  */
+  B200CP_ERR_CUDA = -4,         /* a CUDA runtime call failed                      */
+  B200CP_ERR_TIMEOUT = -5,      /* a bounded device-side wait ran out              */
+  B200CP_ERR_NO_DEVICE = -6     /* no sm_100 device / driver entry point missing   */
+} b200cp_status;
+
+/* flags: which arithmetic path runs the two channel contractions. */
+enum {
+  B200CP_PATH_AUTO = 0,   /* tensor path where the shape allows it, else SIMT */
+  B200CP_PATH_SIMT = 1,   /* exact fp32 FFMA                                        */
+  B200CP_PATH_TC3X = 2,   /* tcgen05 kind::tf32, 3-term split (fp32-grade accuracy) */
+  B200CP_PATH_TC1X = 3,   /* tcgen05 kind::tf32, single pass (about 1e-3 relative)  */
+  B200CP_PATH_MASK = 7
+};
+
+/* ---- CP4 conv2d ------------------------------------------------------- */
+
+/* U[n,t,h,w] = sum_r K0[t,r] sum_c K1[c,r] sum_{y,x} KH[y,r] KW[x,r] X[n,c,h+y-pad,w+x-pad].
+ * Replaces cp4_conv2d_forward_gpu (Cuda_kernels/cp4Conv2dForward.cuh:7-14,
+ * body cp4Conv2dForward.cu:187-328) and, with K0..KW permuted, the TF launcher
+ * Cp4Conv2dFusedNchwKernelLauncher (Kernels/cp4_conv_nchw.cc:34). */
+int b200cp_cp4_fwd(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1, const float* KH,
+                   const float* KW, float* U, void* stream, int flags);
+
+/* dX[n,c,h,w] = sum_r K1[c,r] sum_t K0[t,r] sum_{y,x} KH[Y-1-y,r] KW[X-1-x,r] dU[n,t,h+y-pad,w+x-pad].
+ * Replaces cp4_conv2d_backward_data_gpu (Cuda_kernels/cp4Conv2dBackwardData.cuh:7-14,
+ * body cp4Conv2dBackwardData.cu:112-282). */
+int b200cp_cp4_bwd_data(const b200cp_tensor_shape* s, const float* dU, const float* K0, const float* K1,
+                        const float* KH, const float* KW, float* dX, void* stream, int flags);
+
+/* Bytes of device scratch b200cp_cp4_bwd_filter needs for this shape (0 on error). */
+size_t b200cp_cp4_bwd_filter_workspace_bytes(const b200cp_tensor_shape* s, int flags);
+
+/* All four factor gradients in one pass over X and dU, written back-to-back:
+ *   dK_packed = [ dK0 (T*R) | dK1 (C*R) | dKH (Y*R) | dKW (X*R) ]
+ * Replaces cp4_conv2d_backward_filter_{t,c,y,x}_gpu
+ * (Cuda_kernels/cp4Conv2dBackwardFilter.cuh:13-47, bodies
+ * cp4Conv2dBackwardFilter.cu:64-257), which are host loops in the reference.
+ * The gradients are overwritten, not accumulated; the sum over tiles is done
+ * in a fixed order (bitwise reproducible).  Requires Y == X odd, pad = (Y-1)/2. */
+int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                          const float* K1, const float* KH, const float* KW, float* dK_packed, void* workspace,
+                          size_t workspace_bytes, void* stream, int flags);
+
+/* Dense filter gradient dK[t,c,y,x] = sum_{n,h,w} dU[n,t,h,w] Xpad[n,c,h+y,w+x].
+ * Replaces cp4_conv2d_backward_filter_full_gpu (Cuda_kernels/cp4Conv2dBackwardFilter.cuh:7-11). */
+int b200cp_cp4_bwd_filter_full(const b200cp_tensor_shape* s, const float* X, const float* dU, float* dK, void* stream);
+
+/* K[t,c,y,x] = sum_r K0[t,r] K1[c,r] KH[y,r] KW[x,r]  (the reference's cp4recom,
+ * Cuda_kernels/Utils.cu:36-98). */
+int b200cp_cp4_recompose(const b200cp_tensor_shape* s, const float* K0, const float* K1, const float* KH,
+                         const float* KW, float* K, void* stream);
+
+/* Host-memory variants: copy in, run, copy out, synchronise.  They allocate
+ * (and cache per device) their own device buffers.  `dK_packed` may be NULL in
+ * the step call to skip nothing -- all three results are always produced. */
+int b200cp_cp4_fwd_host(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,
+                        const float* KH, const float* KW, float* U, int flags);
+int b200cp_cp4_step_host(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                         const float* K1, const float* KH, const float* KW, float* U, float* dX, float* dK_packed,
+                         int flags);
+
+/* ---- reshaped-CP (rCP) conv2d, order m (1..4) ------------------------- */
+
+/* V[n,t,h,w] = sum_r sum_{i,j} S[i,j,r] sum_c (prod_k A_k[c_k,t_k,r]) X[n,c,h+i-p,w+j-p],
+ * c = (c_1,..,c_m) and t = (t_1,..,t_m) flattened first mode slowest, p = (FH-1)/2.
+ * A[k] is [c_k, t_k, R], S is [FH, FW, R]: the operand order of
+ * Conv2dRcpFusedNchwKernelLauncher(U, K0, K1, KC, V) (Kernels/rcp_fused_nchw.cc:33,
+ * kernel Kernels/rcp_fused_nchw.cu:4-89), generalised from its one compiled shape. */
+int b200cp_rcp_fwd(int N, int H, int W, int order, const int* cdims, const int* tdims, int R, int FH, int FW,
+                   const float* X, const float* const* A, const float* S, float* V, void* stream, int flags);
+
+size_t b200cp_rcp_bwd_workspace_bytes(int N, int H, int W, int order, const int* cdims, const int* tdims, int R,
+                                      int FH, int FW, int flags);
+
+/* Gradients of b200cp_rcp_fwd: dX [N,C,H,W], dA[k] [c_k,t_k,R], dS [FH,FW,R]
+ * (any of dX / dA / dS may be NULL to skip it; dA and dS are skipped together).
+ * The reference has no rCP backward. */
+int b200cp_rcp_bwd(int N, int H, int W, int order, const int* cdims, const int* tdims, int R, int FH, int FW,
+                   const float* X, const float* dV, const float* const* A, const float* S, float* dX,
+                   float* const* dA, float* dS, void* workspace, size_t workspace_bytes, void* stream, int flags);
+
+/* ---- CP dense layer, order m (1..4) ------------------------------------ */
+
+/* Y[b,o] = sum_r sum_i X[b,i] prod_k F_k[i_k,o_k,r]; F[k] is [i_k, o_k, R]: the
+ * operand order of DenseCpKernelLauncher(U, K0, K1, K2, V) (Kernels/dense_cp.cc:33,
+ * kernel Kernels/dense_cp.cu:4-57), generalised from its one compiled shape. */
+int b200cp_dense_fwd(int B, int order, const int* idims, const int* odims, int R, const float* X,
+                     const float* const* F, float* Y, void* stream, int flags);
+
+size_t b200cp_dense_bwd_workspace_bytes(int B, int order, const int* idims, const int* odims, int R, int flags);
+
+/* Gradients of b200cp_dense_fwd: dX [B,I], dF[k] [i_k,o_k,R] (dX or dF may be NULL).
+ * The reference has no dense-CP backward. */
+int b200cp_dense_bwd(int B, int order, const int* idims, const int* odims, int R, const float* X, const float* dY,
+                     const float* const* F, float* dX, float* const* dF, void* workspace, size_t workspace_bytes,
+                     void* stream, int flags);
+
+/* ---- misc --------------------------------------------------------------- */
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* b200cp_last_error_string(void);
+const char* b200cp_status_string(int status);
+/* Number of kernel launches issued by this library since load (all threads). */
+unsigned long long b200cp_launch_count(void);
+int b200cp_version(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200CP_H */

@@ -1,0 +1,355 @@
+// extern "C" surface of libb200cp: argument validation, rank chunking, host-buffer helpers.
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace b200cp {
+
+std::atomic<unsigned long long> g_launches{0};
+
+char* last_error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int device_info(DeviceInfo* out) {
+  static std::mutex mu;
+  static DeviceInfo cache[64];
+  int dev = 0;
+  B200CP_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200CP_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (cache[dev].sm_count == 0) {
+    DeviceInfo d;
+    B200CP_CUDA_OK(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    B200CP_CUDA_OK(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    B200CP_CUDA_OK(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (d.cc_major != 10)
+      return fail(B200CP_ERR_NO_DEVICE, "this library is built for sm_100a only; device %d is sm_%d0", dev, d.cc_major);
+    cache[dev] = d;
+  }
+  *out = cache[dev];
+  return B200CP_OK;
+}
+
+namespace {
+
+int check_shape(const b200cp_tensor_shape* s, const char* who) {
+  if (!s) return fail(B200CP_ERR_INVALID_ARG, "%s: shape is null", who);
+  if (!s->N || !s->H || !s->W || !s->T || !s->C || !s->Y || !s->X || !s->Rank)
+    return fail(B200CP_ERR_INVALID_ARG, "%s: zero dimension in shape N=%u H=%u W=%u T=%u C=%u Y=%u X=%u Rank=%u", who,
+                s->N, s->H, s->W, s->T, s->C, s->Y, s->X, s->Rank);
+  if ((size_t)s->H * s->W >= (1u << 30) || s->Y > 31 || s->X > 31)
+    return fail(B200CP_ERR_UNSUPPORTED, "%s: image or filter too large (H*W=%zu, Y=%u, X=%u)", who,
+                (size_t)s->H * s->W, s->Y, s->X);
+  return B200CP_OK;
+}
+
+int check_ptrs(const char* who, std::initializer_list<const void*> ps) {
+  for (const void* p : ps) {
+    if (!p) return fail(B200CP_ERR_INVALID_ARG, "%s: null pointer argument", who);
+    if (reinterpret_cast<uintptr_t>(p) & 3) return fail(B200CP_ERR_INVALID_ARG, "%s: pointer not 4-byte aligned", who);
+  }
+  return B200CP_OK;
+}
+
+int path_of(int flags) { return flags & B200CP_PATH_MASK; }
+
+int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, const float* K1, const float* KH,
+             const float* KW, float* out, cudaStream_t st, int flags, bool backward) {
+  const int path = path_of(flags);
+  if (path == B200CP_PATH_TC3X || path == B200CP_PATH_TC1X)
+    return fail(B200CP_ERR_UNSUPPORTED, "cp4: the tcgen05 path is not available for this operation");
+  Cp4Args a{};
+  a.N = s->N; a.H = s->H; a.W = s->W; a.Y = s->Y; a.X = s->X; a.pad = s->pad;
+  a.Cin = backward ? s->T : s->C;
+  a.Cout = backward ? s->C : s->T;
+  a.Fin = backward ? K0 : K1;
+  a.Fout = backward ? K1 : K0;
+  a.KH = KH; a.KW = KW; a.in = in; a.out = out;
+  a.flip = backward ? 1 : 0;
+  a.Rs = s->Rank;
+  for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
+    a.r0 = r0;
+    a.R = std::min(64u, s->Rank - r0);
+    a.accumulate = r0 > 0;
+    if (int rc = cp4_simt_launch(a, st)) return rc;
+  }
+  return B200CP_OK;
+}
+
+// ---- cached device buffers of the *_host helpers --------------------------
+struct HostCtx {
+  std::vector<void*> bufs;
+  std::vector<size_t> sizes;
+  cudaStream_t stream = nullptr;
+};
+std::mutex g_host_mu;
+HostCtx g_host_ctx[64];
+
+int host_buffer(HostCtx& c, size_t slot, size_t bytes, float** out) {
+  if (c.bufs.size() <= slot) {
+    c.bufs.resize(slot + 1, nullptr);
+    c.sizes.resize(slot + 1, 0);
+  }
+  if (c.sizes[slot] < bytes) {
+    if (c.bufs[slot]) B200CP_CUDA_OK(cudaFree(c.bufs[slot]));
+    c.bufs[slot] = nullptr;
+    c.sizes[slot] = 0;
+    B200CP_CUDA_OK(cudaMalloc(&c.bufs[slot], bytes));
+    c.sizes[slot] = bytes;
+  }
+  *out = static_cast<float*>(c.bufs[slot]);
+  return B200CP_OK;
+}
+
+}  // namespace
+}  // namespace b200cp
+
+using namespace b200cp;
+
+extern "C" {
+
+int b200cp_cp4_fwd(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1, const float* KH,
+                   const float* KW, float* U, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_fwd")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_fwd", {X, K0, K1, KH, KW, U})) return rc;
+  return run_conv(s, X, K0, K1, KH, KW, U, static_cast<cudaStream_t>(stream), flags, false);
+}
+
+int b200cp_cp4_bwd_data(const b200cp_tensor_shape* s, const float* dU, const float* K0, const float* K1,
+                        const float* KH, const float* KW, float* dX, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_bwd_data")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_bwd_data", {dU, K0, K1, KH, KW, dX})) return rc;
+  return run_conv(s, dU, K0, K1, KH, KW, dX, static_cast<cudaStream_t>(stream), flags, true);
+}
+
+size_t b200cp_cp4_bwd_filter_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
+  (void)flags;
+  if (check_shape(s, "b200cp_cp4_bwd_filter_workspace_bytes")) return 0;
+  return cp4_bwd_filter_simt_workspace(*s);
+}
+
+int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                          const float* K1, const float* KH, const float* KW, float* dK_packed, void* workspace,
+                          size_t workspace_bytes, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_bwd_filter")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_bwd_filter", {X, dU, K0, K1, KH, KW, dK_packed})) return rc;
+  if (s->Y != s->X || (s->Y & 1) == 0 || s->pad != (s->Y - 1) / 2)
+    return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp4_bwd_filter: needs Y == X odd and pad == (Y-1)/2 (Y=%u X=%u pad=%u)",
+                s->Y, s->X, s->pad);
+  const int path = path_of(flags);
+  if (path == B200CP_PATH_TC3X || path == B200CP_PATH_TC1X)
+    return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: the tcgen05 path is not available for this operation");
+  if (!workspace) return fail(B200CP_ERR_WORKSPACE, "b200cp_cp4_bwd_filter: workspace is null");
+  Cp4BwdFilterArgs a{};
+  a.N = s->N; a.C = s->C; a.T = s->T; a.H = s->H; a.W = s->W; a.F = s->Y; a.pad = s->pad;
+  a.Rs = s->Rank;
+  a.X = X; a.dU = dU; a.K0 = K0; a.K1 = K1; a.KH = KH; a.KW = KW; a.dK = dK_packed;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
+    a.r0 = r0;
+    a.R = std::min(64u, s->Rank - r0);
+    if (int rc = cp4_bwd_filter_simt_launch(a, static_cast<cudaStream_t>(stream))) return rc;
+  }
+  return B200CP_OK;
+}
+
+int b200cp_cp4_bwd_filter_full(const b200cp_tensor_shape* s, const float* X, const float* dU, float* dK,
+                               void* stream) {
+  if (int rc = check_shape(s, "b200cp_cp4_bwd_filter_full")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_bwd_filter_full", {X, dU, dK})) return rc;
+  if ((size_t)s->T * s->C > 0x7fffffffu) return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp4_bwd_filter_full: T*C too large");
+  return cp4_bwd_filter_full_launch(*s, X, dU, dK, static_cast<cudaStream_t>(stream));
+}
+
+int b200cp_cp4_recompose(const b200cp_tensor_shape* s, const float* K0, const float* K1, const float* KH,
+                         const float* KW, float* K, void* stream) {
+  if (int rc = check_shape(s, "b200cp_cp4_recompose")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_recompose", {K0, K1, KH, KW, K})) return rc;
+  return cp4_recompose_launch(*s, K0, K1, KH, KW, K, static_cast<cudaStream_t>(stream));
+}
+
+int b200cp_cp4_step_host(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                         const float* K1, const float* KH, const float* KW, float* U, float* dX, float* dK_packed,
+                         int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_step_host")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_step_host", {X, K0, K1, KH, KW})) return rc;
+  const bool bwd = dU != nullptr;
+  if (!U && !bwd) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host: nothing to compute");
+  if (bwd && (!dX || !dK_packed)) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host: dX and dK_packed required with dU");
+  int dev = 0;
+  B200CP_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200CP_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_host_mu);
+  HostCtx& c = g_host_ctx[dev];
+  if (!c.stream) B200CP_CUDA_OK(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  const size_t HW = (size_t)s->H * s->W, R = s->Rank;
+  const size_t nX = (size_t)s->N * s->C * HW, nU = (size_t)s->N * s->T * HW;
+  const size_t nK0 = s->T * R, nK1 = s->C * R, nKH = s->Y * R, nKW = s->X * R, nK = nK0 + nK1 + nKH + nKW;
+  float *dXin, *dUout, *dF, *ddU = nullptr, *ddX = nullptr, *ddK = nullptr, *ws = nullptr;
+  if (int rc = host_buffer(c, 0, nX * 4, &dXin)) return rc;
+  if (int rc = host_buffer(c, 1, nU * 4, &dUout)) return rc;
+  if (int rc = host_buffer(c, 2, nK * 4, &dF)) return rc;
+  size_t wsb = 0;
+  if (bwd) {
+    wsb = b200cp_cp4_bwd_filter_workspace_bytes(s, flags);
+    if (int rc = host_buffer(c, 3, nU * 4, &ddU)) return rc;
+    if (int rc = host_buffer(c, 4, nX * 4, &ddX)) return rc;
+    if (int rc = host_buffer(c, 5, nK * 4, &ddK)) return rc;
+    if (int rc = host_buffer(c, 6, wsb, &ws)) return rc;
+  }
+  cudaStream_t st = c.stream;
+  float *dK0 = dF, *dK1 = dK0 + nK0, *dKH = dK1 + nK1, *dKW = dKH + nKH;
+  B200CP_CUDA_OK(cudaMemcpyAsync(dXin, X, nX * 4, cudaMemcpyHostToDevice, st));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dK0, K0, nK0 * 4, cudaMemcpyHostToDevice, st));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dK1, K1, nK1 * 4, cudaMemcpyHostToDevice, st));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dKH, KH, nKH * 4, cudaMemcpyHostToDevice, st));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dKW, KW, nKW * 4, cudaMemcpyHostToDevice, st));
+  if (bwd) B200CP_CUDA_OK(cudaMemcpyAsync(ddU, dU, nU * 4, cudaMemcpyHostToDevice, st));
+  if (U) {
+    if (int rc = b200cp_cp4_fwd(s, dXin, dK0, dK1, dKH, dKW, dUout, st, flags)) return rc;
+    B200CP_CUDA_OK(cudaMemcpyAsync(U, dUout, nU * 4, cudaMemcpyDeviceToHost, st));
+  }
+  if (bwd) {
+    if (int rc = b200cp_cp4_bwd_data(s, ddU, dK0, dK1, dKH, dKW, ddX, st, flags)) return rc;
+    B200CP_CUDA_OK(cudaMemcpyAsync(dX, ddX, nX * 4, cudaMemcpyDeviceToHost, st));
+    if (int rc = b200cp_cp4_bwd_filter(s, dXin, ddU, dK0, dK1, dKH, dKW, ddK, ws, wsb, st, flags)) return rc;
+    B200CP_CUDA_OK(cudaMemcpyAsync(dK_packed, ddK, nK * 4, cudaMemcpyDeviceToHost, st));
+  }
+  B200CP_CUDA_OK(cudaStreamSynchronize(st));
+  return B200CP_OK;
+}
+
+int b200cp_cp4_fwd_host(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,
+                        const float* KH, const float* KW, float* U, int flags) {
+  if (!U) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_fwd_host: U is null");
+  return b200cp_cp4_step_host(s, X, nullptr, K0, K1, KH, KW, U, nullptr, nullptr, flags);
+}
+
+// ---- rCP -------------------------------------------------------------------
+static int check_modes(const char* who, int order, const int* a, const int* b, const float* const* F) {
+  if (order < 1 || order > 4) return fail(B200CP_ERR_UNSUPPORTED, "%s: order %d not in 1..4", who, order);
+  if (!a || !b || !F) return fail(B200CP_ERR_INVALID_ARG, "%s: null mode-size or factor array", who);
+  for (int k = 0; k < order; ++k)
+    if (!F[k]) return fail(B200CP_ERR_INVALID_ARG, "%s: factor %d is null", who, k);
+  return B200CP_OK;
+}
+
+int b200cp_rcp_fwd(int N, int H, int W, int order, const int* cdims, const int* tdims, int R, int FH, int FW,
+                   const float* X, const float* const* A, const float* S, float* V, void* stream, int flags) {
+  (void)flags;
+  if (int rc = check_modes("b200cp_rcp_fwd", order, cdims, tdims, A)) return rc;
+  if (int rc = check_ptrs("b200cp_rcp_fwd", {X, S, V})) return rc;
+  return rcp_chain_launch(N, H, W, order, cdims, tdims, R, FH, FW, X, A, S, V, false,
+                          static_cast<cudaStream_t>(stream));
+}
+
+size_t b200cp_rcp_bwd_workspace_bytes(int N, int H, int W, int order, const int* cdims, const int* tdims, int R,
+                                      int FH, int FW, int flags) {
+  (void)N; (void)H; (void)W; (void)R; (void)flags;
+  if (order < 1 || order > 4 || !cdims || !tdims || FH < 1 || FW < 1) return 0;
+  size_t C = 1, T = 1;
+  for (int k = 0; k < order; ++k) { C *= (size_t)cdims[k]; T *= (size_t)tdims[k]; }
+  return T * C * FH * FW * sizeof(float);
+}
+
+int b200cp_rcp_bwd(int N, int H, int W, int order, const int* cdims, const int* tdims, int R, int FH, int FW,
+                   const float* X, const float* dV, const float* const* A, const float* S, float* dX,
+                   float* const* dA, float* dS, void* workspace, size_t workspace_bytes, void* stream, int flags) {
+  if (int rc = check_modes("b200cp_rcp_bwd", order, cdims, tdims, A)) return rc;
+  if (int rc = check_ptrs("b200cp_rcp_bwd", {dV, S})) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dX) {
+    if (int rc = rcp_chain_launch(N, H, W, order, cdims, tdims, R, FH, FW, dV, A, S, dX, true, st)) return rc;
+  }
+  if (dA || dS) {
+    if (!dA || !dS || !X) return fail(B200CP_ERR_INVALID_ARG, "b200cp_rcp_bwd: dA, dS and X go together");
+    for (int k = 0; k < order; ++k)
+      if (!dA[k]) return fail(B200CP_ERR_INVALID_ARG, "b200cp_rcp_bwd: dA[%d] is null", k);
+    const size_t need = b200cp_rcp_bwd_workspace_bytes(N, H, W, order, cdims, tdims, R, FH, FW, flags);
+    if (!workspace || workspace_bytes < need)
+      return fail(B200CP_ERR_WORKSPACE, "b200cp_rcp_bwd: workspace of %zu bytes needed, %zu given", need,
+                  workspace_bytes);
+    int C = 1, T = 1;
+    for (int k = 0; k < order; ++k) { C *= cdims[k]; T *= tdims[k]; }
+    float* G = static_cast<float*>(workspace);
+    if (int rc = dense_grad_launch(N, T, C, H, W, FH, FW, dV, X, G, st)) return rc;
+    if (int rc = contract_factors_launch(order, cdims, tdims, R, FH * FW, A, S, G, dA, dS, st)) return rc;
+  }
+  return B200CP_OK;
+}
+
+// ---- dense-CP -----------------------------------------------------------------
+int b200cp_dense_fwd(int B, int order, const int* idims, const int* odims, int R, const float* X,
+                     const float* const* F, float* Y, void* stream, int flags) {
+  (void)flags;
+  if (int rc = check_modes("b200cp_dense_fwd", order, idims, odims, F)) return rc;
+  if (int rc = check_ptrs("b200cp_dense_fwd", {X, Y})) return rc;
+  return dense_chain_launch(B, order, idims, odims, R, X, F, Y, false, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200cp_dense_bwd_workspace_bytes(int B, int order, const int* idims, const int* odims, int R, int flags) {
+  (void)B; (void)R; (void)flags;
+  if (order < 1 || order > 4 || !idims || !odims) return 0;
+  size_t I = 1, O = 1;
+  for (int k = 0; k < order; ++k) { I *= (size_t)idims[k]; O *= (size_t)odims[k]; }
+  return I * O * sizeof(float);
+}
+
+int b200cp_dense_bwd(int B, int order, const int* idims, const int* odims, int R, const float* X, const float* dY,
+                     const float* const* F, float* dX, float* const* dF, void* workspace, size_t workspace_bytes,
+                     void* stream, int flags) {
+  if (int rc = check_modes("b200cp_dense_bwd", order, idims, odims, F)) return rc;
+  if (int rc = check_ptrs("b200cp_dense_bwd", {dY})) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dX) {
+    if (int rc = dense_chain_launch(B, order, idims, odims, R, dY, F, dX, true, st)) return rc;
+  }
+  if (dF) {
+    if (!X) return fail(B200CP_ERR_INVALID_ARG, "b200cp_dense_bwd: X is needed for dF");
+    for (int k = 0; k < order; ++k)
+      if (!dF[k]) return fail(B200CP_ERR_INVALID_ARG, "b200cp_dense_bwd: dF[%d] is null", k);
+    const size_t need = b200cp_dense_bwd_workspace_bytes(B, order, idims, odims, R, flags);
+    if (!workspace || workspace_bytes < need)
+      return fail(B200CP_ERR_WORKSPACE, "b200cp_dense_bwd: workspace of %zu bytes needed, %zu given", need,
+                  workspace_bytes);
+    int I = 1, O = 1;
+    for (int k = 0; k < order; ++k) { I *= idims[k]; O *= odims[k]; }
+    float* G = static_cast<float*>(workspace);  // G[o][i] = sum_b dY[b,o] X[b,i]
+    if (int rc = dense_grad_launch(B, O, I, 1, 1, 1, 1, dY, X, G, st)) return rc;
+    if (int rc = contract_factors_launch(order, idims, odims, R, 1, F, nullptr, G, dF, nullptr, st)) return rc;
+  }
+  return B200CP_OK;
+}
+
+const char* b200cp_last_error_string(void) { return last_error_buffer(); }
+
+const char* b200cp_status_string(int status) {
+  switch (status) {
+    case B200CP_OK: return "ok";
+    case B200CP_ERR_INVALID_ARG: return "invalid argument";
+    case B200CP_ERR_UNSUPPORTED: return "unsupported shape or path";
+    case B200CP_ERR_WORKSPACE: return "workspace missing or too small";
+    case B200CP_ERR_CUDA: return "CUDA runtime error";
+    case B200CP_ERR_TIMEOUT: return "device-side wait timed out";
+    case B200CP_ERR_NO_DEVICE: return "no usable sm_100 device";
+    default: return "unknown status";
+  }
+}
+
+unsigned long long b200cp_launch_count(void) { return g_launches.load(); }
+int b200cp_version(void) { return 100; }
+
+}  // extern "C"

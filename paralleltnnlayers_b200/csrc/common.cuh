@@ -1,0 +1,92 @@
+// Shared host/device helpers of the b200cp library (internal).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "b200cp.h"
+
+namespace b200cp {
+
+// ---- error reporting ------------------------------------------------------
+char* last_error_buffer();  // thread-local, 512 bytes
+int fail(int status, const char* fmt, ...);
+extern std::atomic<unsigned long long> g_launches;
+
+inline void count_launch(unsigned n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+#define B200CP_CUDA_OK(expr)                                                                        \
+  do {                                                                                              \
+    cudaError_t err__ = (expr);                                                                     \
+    if (err__ != cudaSuccess)                                                                       \
+      return ::b200cp::fail(B200CP_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__));    \
+  } while (0)
+
+#define B200CP_LAUNCH_OK(name)                                                                      \
+  do {                                                                                              \
+    cudaError_t err__ = cudaPeekAtLastError();                                                      \
+    if (err__ != cudaSuccess)                                                                       \
+      return ::b200cp::fail(B200CP_ERR_CUDA, "launch of %s failed: %s", name,                       \
+                            cudaGetErrorString(cudaGetLastError()));                                \
+    ::b200cp::count_launch();                                                                       \
+  } while (0)
+
+// ---- device properties (cached per device) --------------------------------
+struct DeviceInfo {
+  int sm_count = 0;
+  int smem_optin = 0;  // max dynamic shared memory per block (opt-in), bytes
+  int cc_major = 0;
+};
+int device_info(DeviceInfo* out);  // status
+
+__host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// padded rank used by the SIMT kernels' register tiles
+inline int padded_rank(int r) { return r <= 4 ? 4 : r <= 8 ? 8 : r <= 16 ? 16 : r <= 32 ? 32 : 64; }
+
+// ---- launch entry points implemented in the .cu files ---------------------
+struct Cp4Args {
+  int N, Cin, Cout, H, W, Y, X, pad;
+  int R;        // ranks handled by this launch (<= 64)
+  int Rs;       // row stride of the factor matrices (total rank)
+  int r0;       // first rank of this launch
+  int flip;     // 1: use KH[Y-1-y], KW[X-1-x]
+  int accumulate;
+  const float *in, *Fin, *Fout, *KH, *KW;
+  float* out;
+};
+int cp4_simt_launch(const Cp4Args& a, cudaStream_t st);
+
+struct Cp4BwdFilterArgs {
+  int N, C, T, H, W, F, pad;
+  int R, Rs, r0;
+  const float *X, *dU, *K0, *K1, *KH, *KW;
+  float* dK;  // packed [T*Rs | C*Rs | F*Rs | F*Rs]
+  void* ws;
+  size_t ws_bytes;
+};
+size_t cp4_bwd_filter_simt_workspace(const b200cp_tensor_shape& s);
+int cp4_bwd_filter_simt_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
+int cp4_bwd_filter_full_launch(const b200cp_tensor_shape& s, const float* X, const float* dU, float* dK,
+                               cudaStream_t st);
+int cp4_recompose_launch(const b200cp_tensor_shape& s, const float* K0, const float* K1, const float* KH,
+                         const float* KW, float* K, cudaStream_t st);
+
+
+int rcp_chain_launch(int N, int H, int W, int order, const int* cdims, const int* tdims, int R, int FH, int FW,
+                     const float* X, const float* const* A, const float* S, float* V, bool transposed,
+                     cudaStream_t st);
+int dense_chain_launch(int B, int order, const int* idims, const int* odims, int R, const float* X,
+                       const float* const* F, float* Y, bool transposed, cudaStream_t st);
+// G[t][c][tap] = sum_{n,h,w} dV[n,t,h,w] * Xpad[n,c,h+y,w+x]
+int dense_grad_launch(int N, int T, int C, int H, int W, int FH, int FW, const float* dV, const float* X, float* G,
+                      cudaStream_t st);
+int contract_factors_launch(int order, const int* cdims, const int* tdims, int R, int taps, const float* const* A,
+                            const float* S, const float* G, float* const* dA, float* dS, cudaStream_t st);
+
+}  // namespace b200cp

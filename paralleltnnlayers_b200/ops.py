@@ -1,0 +1,293 @@
+"""Operator-level mirror of the reference's entry points.
+
+C++ order (``Cuda_kernels/cp4Conv2d.cuh:8-28``): ``cp4_conv2d_forward(Input, FT, FC, FY, FX, pad)``
+and the backward pair.  TF custom-op order (``Kernels/cp4_conv_nchw.cc:6-13``,
+``test/test_conv2d_cp4.py:13-25``): ``cp4_conv2d_nchw(U, K0[C,R], K1[FH,R], K2[FW,R], K3[T,R])``;
+``conv2d_rcp_fused_nchw(U, K0, K1, ..., KC)`` (``Kernels/rcp_fused_nchw.cc:6-12``) and
+``dense_cp(U, K0, K1, ...)`` (``Kernels/dense_cp.cc:6-12``), generalised from the single shape
+each reference op was compiled for.  Arguments are fp32 CUDA tensors; errors raise, like
+the reference ops' ``OP_REQUIRES``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import TensorShape, check, int_array, lib, ptr_array
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev(t, name):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.float32:
+        raise TypeError(f"{name} must be a float32 CUDA tensor")
+    return t.contiguous()
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def tensor_shape(N, C_, H, W, T, Y, X, Rank, pad):
+    return TensorShape(N=N, H=H, W=W, pad=pad, T=T, C=C_, Y=Y, X=X, Rank=Rank)
+
+
+def _shape_from(inp, FT, FC, FY, FX, pad, in_is_upstream=False):
+    if inp.dim() != 4:
+        raise ValueError("input must be a rank-4 NCHW tensor")
+    for f, nm in ((FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")):
+        if f.dim() != 2 or f.shape[1] != FT.shape[1]:
+            raise ValueError(f"{nm} must be [dim, rank] with the same rank as FT")
+    ch = FT.shape[0] if in_is_upstream else FC.shape[0]
+    if inp.shape[1] != ch:
+        raise ValueError(f"input has {inp.shape[1]} channels, the factor has {ch}")
+    return tensor_shape(inp.shape[0], FC.shape[0], inp.shape[2], inp.shape[3], FT.shape[0], FY.shape[0],
+                        FX.shape[0], FT.shape[1], pad)
+
+
+# ---- CP4, C++ order ---------------------------------------------------------
+def cp4_conv2d_forward(Input, FT, FC, FY, FX, pad=1, flags=0):
+    """``CP::Conv2dForward`` (Cuda_kernels/cp4Conv2d.cu:14-43): returns Out [N,T,H,W]."""
+    Input, FT, FC, FY, FX = (_dev(t, n) for t, n in ((Input, "Input"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(Input, FT, FC, FY, FX, pad)
+    out = torch.empty((s.N, s.T, s.H, s.W), device=Input.device, dtype=torch.float32)
+    with torch.cuda.device(Input.device):
+        check(lib.b200cp_cp4_fwd(C.byref(s), _p(Input), _p(FT), _p(FC), _p(FY), _p(FX), _p(out), _stream(), flags))
+    return out
+
+
+def cp4_conv2d_backward_data(Upstream, FT, FC, FY, FX, pad=1, flags=0):
+    """``CP::Conv2dBackwardData`` (Cuda_kernels/cp4Conv2d.cu:48-77): returns dX [N,C,H,W]."""
+    Upstream, FT, FC, FY, FX = (_dev(t, n) for t, n in
+                                ((Upstream, "Upstream"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(Upstream, FT, FC, FY, FX, pad, in_is_upstream=True)
+    out = torch.empty((s.N, s.C, s.H, s.W), device=Upstream.device, dtype=torch.float32)
+    with torch.cuda.device(Upstream.device):
+        check(lib.b200cp_cp4_bwd_data(C.byref(s), _p(Upstream), _p(FT), _p(FC), _p(FY), _p(FX), _p(out), _stream(),
+                                      flags))
+    return out
+
+
+def cp4_conv2d_backward_filter(dLdO, In, FT, FC, FY, FX, pad=1, flags=0, packed=False):
+    """The four factor gradients of ``CP::Conv2dBackwardFilter``
+    (Cuda_kernels/cp4Conv2d.cu:83-153): returns (dFT, dFC, dFY, dFX), or the
+    packed buffer [dFT|dFC|dFY|dFX] with ``packed=True`` (the allreduce unit)."""
+    dLdO, In, FT, FC, FY, FX = (_dev(t, n) for t, n in
+                                ((dLdO, "dLdO"), (In, "In"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(In, FT, FC, FY, FX, pad)
+    if tuple(dLdO.shape) != (s.N, s.T, s.H, s.W):
+        raise ValueError("dLdO must be [N,T,H,W]")
+    R = s.Rank
+    nT, nC, nY, nX = s.T * R, s.C * R, s.Y * R, s.X * R
+    dK = torch.empty(nT + nC + nY + nX, device=In.device, dtype=torch.float32)
+    with torch.cuda.device(In.device):
+        wsb = lib.b200cp_cp4_bwd_filter_workspace_bytes(C.byref(s), flags)
+        ws = torch.empty(max(wsb, 4) // 4, device=In.device, dtype=torch.float32)
+        check(lib.b200cp_cp4_bwd_filter(C.byref(s), _p(In), _p(dLdO), _p(FT), _p(FC), _p(FY), _p(FX), _p(dK), _p(ws),
+                                        ws.numel() * 4, _stream(), flags))
+    if packed:
+        return dK
+    return (dK[:nT].view(s.T, R), dK[nT:nT + nC].view(s.C, R), dK[nT + nC:nT + nC + nY].view(s.Y, R),
+            dK[nT + nC + nY:].view(s.X, R))
+
+
+def cp4_conv2d_backward_filter_full(dLdO, In, Y, X, pad=1):
+    """``cp4_conv2d_backward_filter_full_gpu`` (Cuda_kernels/cp4Conv2dBackwardFilter.cu:23-59): dK [T,C,Y,X]."""
+    dLdO, In = _dev(dLdO, "dLdO"), _dev(In, "In")
+    s = tensor_shape(In.shape[0], In.shape[1], In.shape[2], In.shape[3], dLdO.shape[1], Y, X, 1, pad)
+    dK = torch.empty((s.T, s.C, Y, X), device=In.device, dtype=torch.float32)
+    with torch.cuda.device(In.device):
+        check(lib.b200cp_cp4_bwd_filter_full(C.byref(s), _p(In), _p(dLdO), _p(dK), _stream()))
+    return dK
+
+
+def cp4recom(FT, FC, FY, FX):
+    """``cp4recom`` (Cuda_kernels/Utils.cu:67-98): dense K [T,C,Y,X]."""
+    FT, FC, FY, FX = (_dev(t, n) for t, n in ((FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = tensor_shape(1, FC.shape[0], 1, 1, FT.shape[0], FY.shape[0], FX.shape[0], FT.shape[1], 0)
+    K = torch.empty((s.T, s.C, s.Y, s.X), device=FT.device, dtype=torch.float32)
+    with torch.cuda.device(FT.device):
+        check(lib.b200cp_cp4_recompose(C.byref(s), _p(FT), _p(FC), _p(FY), _p(FX), _p(K), _stream()))
+    return K
+
+
+def cp4_conv2d_step_host(X, dU, FT, FC, FY, FX, pad=1, flags=0, out=None):
+    """Forward + both backward passes through the host-buffer entry point
+    (``b200cp_cp4_step_host``): CPU tensors in, CPU tensors out, transfers included.
+    ``out`` may hold preallocated (pinned) ``(U, dX, dK_packed)``."""
+    ts = [X, dU, FT, FC, FY, FX]
+    for t in ts:
+        if t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+            raise TypeError("host entry point takes contiguous float32 CPU tensors")
+    s = tensor_shape(X.shape[0], FC.shape[0], X.shape[2], X.shape[3], FT.shape[0], FY.shape[0], FX.shape[0],
+                     FT.shape[1], pad)
+    R = s.Rank
+    if out is None:
+        out = (torch.empty((s.N, s.T, s.H, s.W)), torch.empty((s.N, s.C, s.H, s.W)),
+               torch.empty((s.T + s.C + s.Y + s.X) * R))
+    U, dX, dK = out
+    check(lib.b200cp_cp4_step_host(C.byref(s), _p(X), _p(dU), _p(FT), _p(FC), _p(FY), _p(FX), _p(U), _p(dX), _p(dK),
+                                   flags))
+    return U, dX, dK
+
+
+# ---- TF custom-op order -----------------------------------------------------
+def cp4_conv2d_nchw(U, K0, K1, K2, K3, flags=0):
+    """``Cp4Conv2dNchw`` (Kernels/cp4_conv_nchw.cc:6-13): K0 [C,R], K1 [FH,R], K2 [FW,R], K3 [T,R],
+    SAME padding (test/test_conv2d_cp4.py:25-33)."""
+    return cp4_conv2d_forward(U, K3, K0, K1, K2, pad=(K1.shape[0] - 1) // 2, flags=flags)
+
+
+def _modes(factors, what):
+    a, b = [], []
+    R = factors[0].shape[2]
+    for k, f in enumerate(factors):
+        if f.dim() != 3 or f.shape[2] != R:
+            raise ValueError(f"{what}: kernel {k} must be [in, out, rank] with a common rank")
+        a.append(f.shape[0])
+        b.append(f.shape[1])
+    return a, b, R
+
+
+def conv2d_rcp_fused_nchw(U, *kernels, flags=0):
+    """``Conv2dRcpFusedNchw`` (Kernels/rcp_fused_nchw.cc:6-12): ``(U[N,S0..,H,W], K0[S0,T0,R], ..., KC[FH,FW,R])``
+    -> ``V[N,T0..,H,W]``.  ``U`` may also be given as [N,C,H,W]."""
+    *A, KC = kernels
+    U = _dev(U, "input")
+    A = [_dev(a, f"kernel{k}") for k, a in enumerate(A)]
+    KC = _dev(KC, "kernelc")
+    cd, td, R = _modes(A, "conv2d_rcp_fused_nchw")
+    if KC.dim() != 3 or KC.shape[2] != R:
+        raise ValueError("kernelc must be [FH, FW, rank]")
+    Cc = 1
+    for c in cd:
+        Cc *= c
+    folded = U.dim() == 4
+    if not folded and tuple(U.shape[1:-2]) != tuple(cd):
+        raise ValueError("input modes do not match the kernels")
+    N, H, W = U.shape[0], U.shape[-2], U.shape[-1]
+    if U.numel() != N * Cc * H * W:
+        raise ValueError("input channel count does not match the kernels")
+    Tc = 1
+    for t in td:
+        Tc *= t
+    V = torch.empty((N, Tc, H, W), device=U.device, dtype=torch.float32)
+    with torch.cuda.device(U.device):
+        check(lib.b200cp_rcp_fwd(N, H, W, len(A), int_array(cd), int_array(td), R, KC.shape[0], KC.shape[1], _p(U),
+                                 ptr_array([a.data_ptr() for a in A]), _p(KC), _p(V), _stream(), flags))
+    return V if folded else V.view(N, *td, H, W)
+
+
+def rcp_conv2d_backward(U, dV, *kernels, flags=0, need_dx=True, need_dw=True):
+    """Gradients of ``conv2d_rcp_fused_nchw``: (dU, [dK_k], dKC)."""
+    *A, KC = kernels
+    U, dV = _dev(U, "input"), _dev(dV, "dV")
+    A = [_dev(a, f"kernel{k}") for k, a in enumerate(A)]
+    KC = _dev(KC, "kernelc")
+    cd, td, R = _modes(A, "rcp_conv2d_backward")
+    N, H, W = U.shape[0], U.shape[-2], U.shape[-1]
+    dU = torch.empty_like(U) if need_dx else None
+    dA = [torch.empty_like(a) for a in A] if need_dw else None
+    dS = torch.empty_like(KC) if need_dw else None
+    with torch.cuda.device(U.device):
+        wsb = lib.b200cp_rcp_bwd_workspace_bytes(N, H, W, len(A), int_array(cd), int_array(td), R, KC.shape[0],
+                                                 KC.shape[1], flags)
+        ws = torch.empty(max(wsb, 4) // 4, device=U.device, dtype=torch.float32)
+        check(lib.b200cp_rcp_bwd(N, H, W, len(A), int_array(cd), int_array(td), R, KC.shape[0], KC.shape[1], _p(U),
+                                 _p(dV), ptr_array([a.data_ptr() for a in A]), _p(KC),
+                                 _p(dU) if need_dx else None,
+                                 ptr_array([a.data_ptr() for a in dA]) if need_dw else None,
+                                 _p(dS) if need_dw else None, _p(ws), ws.numel() * 4, _stream(), flags))
+    return dU, dA, dS
+
+
+def dense_cp(U, *kernels, flags=0):
+    """``DenseCp`` (Kernels/dense_cp.cc:6-12): ``(U[N,S0,S1,..], K0[S0,T0,R], ...)`` -> ``V[N,T0,T1,..]``
+    (output dims are ``kernel_k.dim(1)``, Kernels/dense_cp.cc:86-91).  ``U`` may also be [N, I]."""
+    U = _dev(U, "input")
+    Fk = [_dev(f, f"kernel{k}") for k, f in enumerate(kernels)]
+    idims, odims, R = _modes(Fk, "dense_cp")
+    I = 1
+    for d in idims:
+        I *= d
+    O = 1
+    for d in odims:
+        O *= d
+    B = U.shape[0]
+    if U.numel() != B * I:
+        raise ValueError("input size does not match the kernels")
+    flat = U.dim() == 2
+    Y = torch.empty((B, O), device=U.device, dtype=torch.float32)
+    with torch.cuda.device(U.device):
+        check(lib.b200cp_dense_fwd(B, len(Fk), int_array(idims), int_array(odims), R, _p(U),
+                                   ptr_array([f.data_ptr() for f in Fk]), _p(Y), _stream(), flags))
+    return Y if flat else Y.view(B, *odims)
+
+
+def dense_cp_backward(U, dV, *kernels, flags=0, need_dx=True, need_dw=True):
+    """Gradients of ``dense_cp``: (dU, [dK_k])."""
+    U, dV = _dev(U, "input"), _dev(dV, "dV")
+    Fk = [_dev(f, f"kernel{k}") for k, f in enumerate(kernels)]
+    idims, odims, R = _modes(Fk, "dense_cp_backward")
+    B = U.shape[0]
+    dU = torch.empty_like(U) if need_dx else None
+    dF = [torch.empty_like(f) for f in Fk] if need_dw else None
+    with torch.cuda.device(U.device):
+        wsb = lib.b200cp_dense_bwd_workspace_bytes(B, len(Fk), int_array(idims), int_array(odims), R, flags)
+        ws = torch.empty(max(wsb, 4) // 4, device=U.device, dtype=torch.float32)
+        check(lib.b200cp_dense_bwd(B, len(Fk), int_array(idims), int_array(odims), R, _p(U), _p(dV),
+                                   ptr_array([f.data_ptr() for f in Fk]), _p(dU) if need_dx else None,
+                                   ptr_array([f.data_ptr() for f in dF]) if need_dw else None, _p(ws),
+                                   ws.numel() * 4, _stream(), flags))
+    return dU, dF
+
+
+# ---- autograd wrappers ----------------------------------------------------------
+class CP4Conv2dFunction(torch.autograd.Function):
+    """y = CP4 conv2d(x; FT, FC, FY, FX) with the fused backward kernels."""
+
+    @staticmethod
+    def forward(ctx, x, FT, FC, FY, FX, pad=1, flags=0):
+        ctx.save_for_backward(x, FT, FC, FY, FX)
+        ctx.pad, ctx.flags = pad, flags
+        return cp4_conv2d_forward(x, FT, FC, FY, FX, pad, flags)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, FT, FC, FY, FX = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = cp4_conv2d_backward_data(dy, FT, FC, FY, FX, ctx.pad, ctx.flags) if ctx.needs_input_grad[0] else None
+        g = (None,) * 4
+        if any(ctx.needs_input_grad[1:5]):
+            g = cp4_conv2d_backward_filter(dy, x, FT, FC, FY, FX, ctx.pad, ctx.flags)
+        return (dx, *g, None, None)
+
+
+class RCPConv2dFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, KC, *A):
+        ctx.save_for_backward(x, KC, *A)
+        return conv2d_rcp_fused_nchw(x, *A, KC)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, KC, *A = ctx.saved_tensors
+        dx, dA, dS = rcp_conv2d_backward(x, dy.contiguous().view(x.shape[0], -1, x.shape[-2], x.shape[-1]), *A, KC)
+        return (dx, dS, *dA)
+
+
+class CPDenseFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, *Fk):
+        ctx.save_for_backward(x, *Fk)
+        return dense_cp(x, *Fk)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, *Fk = ctx.saved_tensors
+        dx, dF = dense_cp_backward(x.reshape(x.shape[0], -1), dy.contiguous().reshape(x.shape[0], -1), *Fk)
+        return (dx.view_as(x), *dF)
