@@ -1,0 +1,432 @@
+// CP4 conv2d backward-filter (and the dense filter gradient / recomposition helpers) on CUDA cores.
+#include "cp4_simt.cuh"
+
+namespace b200cp {
+
+// ===========================================================================
+// backward-filter
+// ===========================================================================
+//
+// Per tile (one CTA):
+//   Q = K0^T dU and P = K1^T X on the halo tile (phase-1 code above)
+//   per rank r, per pixel:  rows_i = sum_j KW[j] P[i][j],  cols_j = sum_i KH[i] P[i][j]
+//       Z  = sum_i KH[i] rows_i            -> Zs[r][px]
+//       Qt = sum_{i,j} KH[i] KW[j] Q[h-i+p][w-j+p]   -> Qts[r][px]
+//       dKH[i,r] += Q * rows_i,  dKW[j,r] += Q * cols_j     (warp shuffle + fixed-order smem sum)
+//   dK0[t,r] = sum_px dU[t,px] Zs[r][px],  dK1[c,r] = sum_px X[c,px] Qts[r][px]
+//       one warp per group of channels, lanes stride the pixels, butterfly reduction.
+// Each CTA writes its partial gradients to workspace[cta][...]; a second kernel
+// sums the partials in CTA order, so the result is bitwise reproducible.
+// Formulas: Cuda_kernels/cp4Conv2dBackwardFilter.cu:91-104,142-155,192-205,241-254.
+namespace {
+
+struct GeomF {
+  Geom g;      // Cin = C (X channels), Cout = T (dU channels)
+  int F;       // filter size
+  int nparam;  // (T + C + 2F) * R  floats per partial (R = ranks of this launch)
+  int OPXs;
+};
+
+// Reduce M values per lane across the warp so that every value's warp-sum lands
+// on exactly one lane.  After the call, lane l holds sums for indices
+// idx(l, j) = j + (M >> 5) * bitrev-free mapping computed by `owner_index`.
+template <int M>
+__device__ __forceinline__ void warp_transpose_reduce(float (&v)[M], int lane) {
+  // halving steps while more than one value per lane remains
+#pragma unroll
+  for (int off = 16, m = M / 2; off >= 1; off >>= 1, m >>= 1) {
+    if (m >= 1) {
+      const bool hi = lane & off;
+#pragma unroll
+      for (int i = 0; i < m; ++i) {
+        const float send = hi ? v[i] : v[i + m];
+        const float keep = hi ? v[i + m] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    } else {
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+    }
+  }
+}
+// index (0..M-1) of the j-th value lane `lane` owns after warp_transpose_reduce<M>
+template <int M>
+__device__ __forceinline__ int owner_index(int lane, int j) {
+  int idx = 0, m = M / 2;
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1, m >>= 1)
+    if (m >= 1 && (lane & off)) idx += m;
+  return idx + j;
+}
+
+// dK[ch, r] partial = sum over the tile's pixels of src[n, ch, px] * Vs[r][px]
+template <int RP, int CG>
+__device__ __forceinline__ void pixel_reduce(const Geom& g, int OPXs, const float* __restrict__ src_n, int nch,
+                                             const float* Vs, const int* pixoff, float* __restrict__ part, int tid,
+                                             int nt) {
+  const int lane = tid & 31, warp = tid >> 5, nwarp = nt >> 5;
+  const size_t HW = (size_t)g.H * g.W;
+  constexpr int M = CG * RP;
+  constexpr int PER = M >= 32 ? M / 32 : 1;  // values per lane after the reduction
+  for (int c0 = warp * CG; c0 < nch; c0 += nwarp * CG) {
+    float acc[M];
+#pragma unroll
+    for (int i = 0; i < M; ++i) acc[i] = 0.f;
+    const float* s[CG];
+#pragma unroll
+    for (int j = 0; j < CG; ++j) s[j] = src_n + (size_t)min(c0 + j, nch - 1) * HW;
+    for (int p = lane; p < g.OPX; p += 32) {
+      const int po = pixoff[p];
+      float d[CG];
+#pragma unroll
+      for (int j = 0; j < CG; ++j) d[j] = po >= 0 ? __ldg(s[j] + po) : 0.f;
+#pragma unroll
+      for (int r = 0; r < RP; ++r) {
+        const float z = Vs[r * OPXs + p];
+#pragma unroll
+        for (int j = 0; j < CG; ++j) acc[j * RP + r] = fmaf(d[j], z, acc[j * RP + r]);
+      }
+    }
+    warp_transpose_reduce<M>(acc, lane);
+    // M < 32: after log2(M) halving steps each group of 32/M lanes holds the same sum
+    const bool owner = M >= 32 || (lane & ((32 / (M < 32 ? M : 32)) - 1)) == 0;
+    if (owner) {
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int idx = owner_index<M>(lane, j);
+        const int cj = idx / RP, r = idx - cj * RP;
+        if (c0 + cj < nch && r < g.R) part[(size_t)(c0 + cj) * g.R + r] = acc[j];
+      }
+    }
+  }
+}
+
+// FMAX bounds the register arrays of the stencil phase; EXACT means F == FMAX at compile time.
+template <int RP, int PPT, int FMAX, bool EXACT>
+__global__ void __launch_bounds__(256) cp4_bwd_filter_kernel(const GeomF gf, const float* __restrict__ X,
+                                                             const float* __restrict__ dU,
+                                                             const float* __restrict__ K0,
+                                                             const float* __restrict__ K1,
+                                                             const float* __restrict__ KH,
+                                                             const float* __restrict__ KW,
+                                                             float* __restrict__ partial) {
+  const Geom& g = gf.g;
+  const int F = EXACT ? FMAX : gf.F;
+  extern __shared__ __align__(16) float smem[];
+  float* Fs = smem;                              // [cchunk][RP]
+  float* KHs = Fs + g.fcap;                      // [F][RP]
+  float* KWs = KHs + F * RP;                     // [F][RP]
+  float* red = KWs + F * RP;                     // [8 warps][2F]
+  float* Ps = red + 8 * 2 * F;                   // [RP][HPXs]
+  float* Qs = Ps + RP * g.HPXs;                  // [RP][HPXs]
+  float* Zs = Qs + RP * g.HPXs;                  // [RP][OPXs]
+  float* Qts = Zs + RP * gf.OPXs;                // [RP][OPXs]
+  int* pixoff = reinterpret_cast<int*>(Qts + RP * gf.OPXs);  // [OPXs]
+  float* Xst = reinterpret_cast<float*>(pixoff + gf.OPXs);   // [kStages*kKC][nt*PPT]  cp.async FIFO
+
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarp = nt >> 5;
+  int b = blockIdx.x;
+  const int tw = b % g.tilesW;
+  b /= g.tilesW;
+  const int th = b % g.tilesH;
+  const int n = b / g.tilesH;
+  const int h0 = th * g.TH, w0 = tw * g.TW;
+  const size_t HW = (size_t)g.H * g.W;
+  const float* Xn = X + (size_t)n * g.Cin * HW;
+  const float* dUn = dU + (size_t)n * g.Cout * HW;
+  float* part = partial + (size_t)blockIdx.x * gf.nparam;
+  float* part_K0 = part;
+  float* part_K1 = part_K0 + (size_t)g.Cout * g.R;
+  float* part_KH = part_K1 + (size_t)g.Cin * g.R;
+  float* part_KW = part_KH + (size_t)F * g.R;
+
+  for (int i = tid; i < F * RP; i += nt) {
+    const int r = i % RP, f = i / RP;
+    KHs[i] = r < g.R ? __ldg(KH + (size_t)f * g.Rs + g.r0 + r) : 0.f;
+    KWs[i] = r < g.R ? __ldg(KW + (size_t)f * g.Rs + g.r0 + r) : 0.f;
+  }
+  for (int p = tid; p < g.OPX; p += nt) {
+    const int oy = p / g.TW, ox = p - oy * g.TW;
+    const int gy = h0 + oy, gx = w0 + ox;
+    pixoff[p] = (gy < g.H && gx < g.W) ? gy * g.W + gx : -1;
+  }
+  contract_tile<RP, PPT>(g, Xn, g.Cin, K1, Fs, Xst, Ps, h0, w0, tid, nt);
+  contract_tile<RP, PPT>(g, dUn, g.Cout, K0, Fs, Xst, Qs, h0, w0, tid, nt);
+  __syncthreads();
+
+  // per-rank stencils and the small-factor gradients
+  const int p = g.pad;
+  for (int r = 0; r < g.R; ++r) {
+    float kh[FMAX], kw[FMAX], aH[FMAX], aW[FMAX];
+#pragma unroll
+    for (int i = 0; i < FMAX; ++i) {
+      const bool on = EXACT || i < F;
+      kh[i] = on ? KHs[i * RP + r] : 0.f;
+      kw[i] = on ? KWs[i * RP + r] : 0.f;
+      aH[i] = 0.f;
+      aW[i] = 0.f;
+    }
+    const float* Pr = Ps + r * g.HPXs;
+    const float* Qr = Qs + r * g.HPXs;
+    for (int op = tid; op < g.OPX; op += nt) {
+      const int oy = op / g.TW, ox = op - oy * g.TW;
+      float zv = 0.f, qt = 0.f;
+      if (pixoff[op] >= 0) {
+        // window origin (tap 0,0) in halo coordinates; mH == mW == pad here
+        const float* pw = Pr + oy * g.TWh + ox;
+        const float* qw = Qr + oy * g.TWh + ox;
+        const float q = qw[p * g.TWh + p];
+        float cols[FMAX];
+#pragma unroll
+        for (int j = 0; j < FMAX; ++j) cols[j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < FMAX; ++i) {
+          if (EXACT || i < F) {
+            float row = 0.f, qrow = 0.f;
+#pragma unroll
+            for (int j = 0; j < FMAX; ++j) {
+              if (EXACT || j < F) {
+                const float pv = pw[i * g.TWh + j];
+                row = fmaf(kw[j], pv, row);
+                cols[j] = fmaf(kh[i], pv, cols[j]);
+                // flipped window: Q[h - i + p][w - j + p]  -> halo (oy + 2p - i, ox + 2p - j)
+                qrow = fmaf(kw[j], qw[(2 * p - i) * g.TWh + (2 * p - j)], qrow);
+              }
+            }
+            zv = fmaf(kh[i], row, zv);
+            qt = fmaf(kh[i], qrow, qt);
+            aH[i] = fmaf(q, row, aH[i]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < FMAX; ++j) aW[j] = fmaf(q, cols[j], aW[j]);
+      }
+      Zs[r * gf.OPXs + op] = zv;
+      Qts[r * gf.OPXs + op] = qt;
+    }
+    // block reduction of aH, aW in a fixed order: lanes (shuffle tree), then warps
+#pragma unroll
+    for (int i = 0; i < FMAX; ++i) {
+      if (EXACT || i < F) {
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+          aH[i] += __shfl_xor_sync(0xffffffffu, aH[i], off);
+          aW[i] += __shfl_xor_sync(0xffffffffu, aW[i], off);
+        }
+      }
+    }
+    __syncthreads();  // previous rank's `red` fully consumed
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < FMAX; ++i)
+        if (EXACT || i < F) {
+          red[warp * 2 * F + i] = aH[i];
+          red[warp * 2 * F + F + i] = aW[i];
+        }
+    }
+    __syncthreads();
+    if (tid < 2 * F) {
+      float sum = 0.f;
+      for (int w = 0; w < nwarp; ++w) sum += red[w * 2 * F + tid];
+      if (tid < F) part_KH[(size_t)tid * g.R + r] = sum;
+      else part_KW[(size_t)(tid - F) * g.R + r] = sum;
+    }
+  }
+  __syncthreads();
+
+  constexpr int CG = (RP >= 64) ? 1 : (RP == 32 ? 2 : 4);
+  pixel_reduce<RP, CG>(g, gf.OPXs, dUn, g.Cout, Zs, pixoff, part_K0, tid, nt);
+  pixel_reduce<RP, CG>(g, gf.OPXs, Xn, g.Cin, Qts, pixoff, part_K1, tid, nt);
+}
+
+// out[j] = sum over CTAs of partial[cta][j].  32 parameters x 32 slices per block: slice s adds the
+// partials of its contiguous CTA range in order, then the slices are added in order (reproducible).
+__global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* __restrict__ partial, int nparts,
+                                                                   int nparam, int R, int Rs, int r0,
+                                                                   float* __restrict__ dK) {
+  __shared__ float red[32][33];
+  const int j = blockIdx.x * 32 + threadIdx.x, sl = threadIdx.y;
+  const int per = (nparts + 31) / 32;
+  const int i0 = sl * per, i1 = min(nparts, i0 + per);
+  float s0 = 0.f, s1 = 0.f;
+  if (j < nparam) {
+    int i = i0;
+    for (; i + 2 <= i1; i += 2) {
+      s0 += partial[(size_t)i * nparam + j];
+      s1 += partial[(size_t)(i + 1) * nparam + j];
+    }
+    if (i < i1) s0 += partial[(size_t)i * nparam + j];
+  }
+  red[sl][threadIdx.x] = s0 + s1;
+  __syncthreads();
+  if (sl == 0 && j < nparam) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) s += red[k][threadIdx.x];
+    // the packed output has the same T, C, F, F row sections, with rows of length Rs
+    const int row = j / R, r = j - row * R;
+    dK[(size_t)row * Rs + r0 + r] = s;
+  }
+}
+
+TileChoice bwdf_tile(int N, int H, int W, int F, int pad, int C, int T, int RP, const DeviceInfo& di) {
+  // halo pass over C + T channels, reductions over C + T channels (about 1.6x a contraction each), stencils
+  const double w1 = (double)(C + T) * RP, w3 = 1.6 * (C + T) * RP + 6.0 * F * F * RP;
+  return choose_tile(N, H, W, F, F, pad, w1, w3, RP, factor_cap(std::max(C, T), RP), 2, 2, 2 * F * RP + 16 * F, 1, true,
+                     di);
+}
+
+template <int RP, int PPT, int FMAX, bool EXACT>
+int launch_bwd_filter(const Cp4BwdFilterArgs& a, const TileChoice& t, const DeviceInfo& di, cudaStream_t st) {
+  const int F = a.F;
+  Cp4Args ca{};
+  ca.N = a.N; ca.Cin = a.C; ca.Cout = a.T; ca.H = a.H; ca.W = a.W; ca.Y = F; ca.X = F; ca.pad = a.pad;
+  ca.R = a.R; ca.Rs = a.Rs; ca.r0 = a.r0;
+  GeomF gf;
+  gf.g = make_geom(ca, t, RP, factor_cap(std::max(a.C, a.T), RP));
+  gf.F = F;
+  gf.nparam = (a.T + a.C + 2 * F) * a.R;
+  gf.OPXs = (int)align_up(gf.g.OPX, 4);
+  const size_t smem = sizeof(float) * ((size_t)gf.g.fcap + 2 * F * RP + 16 * F + 2 * (size_t)RP * gf.g.HPXs +
+                                       2 * (size_t)RP * gf.OPXs + gf.OPXs + (size_t)kStages * kKC * t.NT * PPT);
+  if ((int)smem > di.smem_optin) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: tile exceeds shared memory");
+  const long ctas = (long)a.N * gf.g.tilesH * gf.g.tilesW;
+  const size_t need = (size_t)ctas * gf.nparam * sizeof(float);
+  if (a.ws == nullptr || a.ws_bytes < need)
+    return fail(B200CP_ERR_WORKSPACE, "cp4 bwd-filter: workspace of %zu bytes needed, %zu given", need, a.ws_bytes);
+  auto kern = cp4_bwd_filter_kernel<RP, PPT, FMAX, EXACT>;
+  B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)ctas, t.NT, smem, st>>>(gf, a.X, a.dU, a.K0, a.K1, a.KH, a.KW, (float*)a.ws);
+  B200CP_LAUNCH_OK("cp4_bwd_filter_kernel");
+  cp4_reduce_partials_kernel<<<ceil_div(gf.nparam, 32), dim3(32, 32), 0, st>>>((const float*)a.ws, (int)ctas, gf.nparam,
+                                                                            a.R, a.Rs, a.r0, a.dK);
+  B200CP_LAUNCH_OK("cp4_reduce_partials_kernel");
+  return B200CP_OK;
+}
+
+template <int RP, int FMAX, bool EXACT>
+int dispatch_bwd_filter_ppt(const Cp4BwdFilterArgs& a, const DeviceInfo& di, cudaStream_t st) {
+  const TileChoice t = bwdf_tile(a.N, a.H, a.W, a.F, a.pad, a.C, a.T, RP, di);
+  if (t.NT == 0) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: no tile fits in shared memory");
+  switch (t.PPT1) {
+    case 1: return launch_bwd_filter<RP, 1, FMAX, EXACT>(a, t, di, st);
+    case 2: if constexpr (RP <= 32) return launch_bwd_filter<RP, 2, FMAX, EXACT>(a, t, di, st); break;
+    case 3: if constexpr (RP <= 16) return launch_bwd_filter<RP, 3, FMAX, EXACT>(a, t, di, st); break;
+    case 4: if constexpr (RP <= 16) return launch_bwd_filter<RP, 4, FMAX, EXACT>(a, t, di, st); break;
+  }
+  return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: internal: no kernel for PPT %d at rank tile %d", t.PPT1, RP);
+}
+
+template <int FMAX, bool EXACT>
+int dispatch_bwd_filter_rank(const Cp4BwdFilterArgs& a, const DeviceInfo& di, cudaStream_t st) {
+  switch (padded_rank(a.R)) {
+    case 4: return dispatch_bwd_filter_ppt<4, FMAX, EXACT>(a, di, st);
+    case 8: return dispatch_bwd_filter_ppt<8, FMAX, EXACT>(a, di, st);
+    case 16: return dispatch_bwd_filter_ppt<16, FMAX, EXACT>(a, di, st);
+    case 32: return dispatch_bwd_filter_ppt<32, FMAX, EXACT>(a, di, st);
+    default: return dispatch_bwd_filter_ppt<64, FMAX, EXACT>(a, di, st);
+  }
+}
+
+}  // namespace
+
+// One partial gradient set per CTA.  With a device present the tile the launch will pick is
+// known exactly; without one (argument checks on a CPU-only host) an upper bound is returned.
+size_t cp4_bwd_filter_simt_workspace(const b200cp_tensor_shape& s) {
+  const size_t R = std::min<unsigned>(s.Rank, 64);
+  const size_t nparam = ((size_t)s.T + s.C + 2 * s.Y) * R;
+  DeviceInfo di;
+  int dev_count = 0;
+  if (cudaGetDeviceCount(&dev_count) == cudaSuccess && dev_count > 0 && device_info(&di) == B200CP_OK) {
+    // ranks are processed in chunks of 64; the last chunk may use a narrower rank tile (and another spatial tile)
+    size_t need = 0;
+    for (unsigned r0 = 0; r0 < s.Rank; r0 += 64) {
+      const int rc = (int)std::min(64u, s.Rank - r0);
+      const TileChoice t = bwdf_tile(s.N, s.H, s.W, s.Y, s.pad, s.C, s.T, padded_rank(rc), di);
+      if (!t.NT) { need = 0; break; }
+      need = std::max(need, (size_t)s.N * ceil_div(s.H, t.TH) * ceil_div(s.W, t.TW) *
+                                ((size_t)s.T + s.C + 2 * s.Y) * rc * sizeof(float));
+    }
+    if (need) return need;
+  }
+  cudaGetLastError();
+  const size_t max_ctas = (size_t)s.N * s.H * ceil_div((int)s.W, 16);
+  return max_ctas * nparam * sizeof(float);
+}
+
+int cp4_bwd_filter_simt_launch(const Cp4BwdFilterArgs& a, cudaStream_t st) {
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  if (a.F == 3) return dispatch_bwd_filter_rank<3, true>(a, di, st);
+  if (a.F >= 1 && a.F <= 11 && (a.F & 1)) return dispatch_bwd_filter_rank<11, false>(a, di, st);
+  return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: filter size %d is not odd and <= 11", a.F);
+}
+
+// ===========================================================================
+// dense filter gradient and recomposition (helpers of the reference's tests)
+// ===========================================================================
+namespace {
+
+// dK[t,c,y,x] = sum_{n,h,w} dU[n,t,h,w] X[n,c,h+y-pad,w+x-pad]; one CTA per (t,c), fixed-order sum.
+__global__ void cp4_bwd_filter_full_kernel(b200cp_tensor_shape s, const float* __restrict__ X,
+                                           const float* __restrict__ dU, float* __restrict__ dK) {
+  const int t = blockIdx.x / s.C, c = blockIdx.x % s.C;
+  const int HW = s.H * s.W;
+  __shared__ float red[8];
+  for (unsigned yx = 0; yx < s.Y * s.X; ++yx) {
+    const int y = yx / s.X, x = yx % s.X;
+    float acc = 0.f;
+    for (unsigned n = 0; n < s.N; ++n) {
+      const float* du = dU + ((size_t)n * s.T + t) * HW;
+      const float* xi = X + ((size_t)n * s.C + c) * HW;
+      for (int p = threadIdx.x; p < HW; p += blockDim.x) {
+        const int h = p / s.W, w = p % s.W;
+        const int hh = h + y - (int)s.pad, ww = w + x - (int)s.pad;
+        if (hh >= 0 && hh < (int)s.H && ww >= 0 && ww < (int)s.W) acc = fmaf(du[p], xi[hh * s.W + ww], acc);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float sum = 0.f;
+      for (unsigned w = 0; w < blockDim.x / 32; ++w) sum += red[w];
+      dK[((size_t)(t * s.C + c) * s.Y + y) * s.X + x] = sum;
+    }
+  }
+}
+
+__global__ void cp4_recompose_kernel(b200cp_tensor_shape s, const float* __restrict__ K0,
+                                     const float* __restrict__ K1, const float* __restrict__ KH,
+                                     const float* __restrict__ KW, float* __restrict__ K) {
+  const size_t total = (size_t)s.T * s.C * s.Y * s.X;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const unsigned x = i % s.X, y = (i / s.X) % s.Y, c = (i / (s.X * s.Y)) % s.C, t = i / ((size_t)s.X * s.Y * s.C);
+    float acc = 0.f;
+    for (unsigned r = 0; r < s.Rank; ++r)
+      acc += K0[t * s.Rank + r] * K1[c * s.Rank + r] * KH[y * s.Rank + r] * KW[x * s.Rank + r];
+    K[i] = acc;
+  }
+}
+
+}  // namespace
+
+int cp4_bwd_filter_full_launch(const b200cp_tensor_shape& s, const float* X, const float* dU, float* dK,
+                               cudaStream_t st) {
+  cp4_bwd_filter_full_kernel<<<s.T * s.C, 256, 0, st>>>(s, X, dU, dK);
+  B200CP_LAUNCH_OK("cp4_bwd_filter_full_kernel");
+  return B200CP_OK;
+}
+
+int cp4_recompose_launch(const b200cp_tensor_shape& s, const float* K0, const float* K1, const float* KH,
+                         const float* KW, float* K, cudaStream_t st) {
+  const size_t total = (size_t)s.T * s.C * s.Y * s.X;
+  const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 4096);
+  cp4_recompose_kernel<<<blocks, 256, 0, st>>>(s, K0, K1, KH, KW, K);
+  B200CP_LAUNCH_OK("cp4_recompose_kernel");
+  return B200CP_OK;
+}
+
+}  // namespace b200cp
