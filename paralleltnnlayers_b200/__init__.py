@@ -2,12 +2,29 @@
 
 Host-side mirror of the reference's operator interface over the C ABI of
 ``libb200cp.so``; tensors are torch CUDA tensors used as device-memory handles.
-"""
-from ._lib import (B200CPError, LIB_PATH, PATH_AUTO, PATH_SIMT, PATH_TC1X, PATH_TC3X, TensorShape,
-                   launch_count)
-from .ops import (CP4Conv2dFunction, CPDenseFunction, RCPConv2dFunction, conv2d_rcp_fused_nchw,
-                  cp4_conv2d_backward_data, cp4_conv2d_backward_filter, cp4_conv2d_backward_filter_full,
-                  cp4_conv2d_forward, cp4_conv2d_nchw, cp4_conv2d_step_host, cp4recom, dense_cp,
-                  dense_cp_backward, rcp_conv2d_backward, tensor_shape)
 
-__all__ = [n for n in dir() if not n.startswith("_")]
+The shared library is loaded on first use of any operator (so that
+``paralleltnnlayers_b200.build`` can be imported to build it); a missing or stale
+library raises at that point -- there is no fallback implementation.
+"""
+import importlib
+
+_LIB_NAMES = ("B200CPError", "LIB_PATH", "PATH_AUTO", "PATH_SIMT", "PATH_TC1X", "PATH_TC3X", "TensorShape",
+              "launch_count")
+_OPS_NAMES = ("CP4Conv2dFunction", "CPDenseFunction", "RCPConv2dFunction", "conv2d_rcp_fused_nchw",
+              "cp4_conv2d_backward_data", "cp4_conv2d_backward_filter", "cp4_conv2d_backward_filter_full",
+              "cp4_conv2d_forward", "cp4_conv2d_nchw", "cp4_conv2d_step_host", "cp4recom", "dense_cp",
+              "dense_cp_backward", "debug_cp4_tc", "device_status", "rcp_conv2d_backward", "tensor_shape")
+__all__ = list(_LIB_NAMES + _OPS_NAMES)
+
+
+def __getattr__(name):
+    if name in _LIB_NAMES or name == "_lib":
+        mod = importlib.import_module("._lib", __name__)
+        return mod if name == "_lib" else getattr(mod, name)
+    if name in _OPS_NAMES or name == "ops":
+        mod = importlib.import_module(".ops", __name__)
+        return mod if name == "ops" else getattr(mod, name)
+    if name in ("build", "dist"):
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -52,6 +52,9 @@ def _load():
         "b200cp_dense_fwd": (i, [i, i, ip, ip, i, fp, pp, fp, vp, i]),
         "b200cp_dense_bwd_workspace_bytes": (sz, [i, i, ip, ip, i, i]),
         "b200cp_dense_bwd": (i, [i, i, ip, ip, i, fp, fp, pp, fp, pp, vp, sz, vp, i]),
+        "b200cp_device_status": (i, []),
+        "b200cp_debug_cp4_tc": (i, [sp, fp, fp, fp, fp, fp, fp, fp, i, vp]),
+        "b200cp_debug_tc_selftest": (i, [i, fp, fp, fp, vp, vp]),
         "b200cp_last_error_string": (C.c_char_p, []),
         "b200cp_status_string": (C.c_char_p, [i]),
         "b200cp_launch_count": (C.c_ulonglong, []),

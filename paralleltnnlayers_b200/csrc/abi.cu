@@ -1,5 +1,6 @@
 // extern "C" surface of libb200cp: argument validation, rank chunking, host-buffer helpers.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -66,11 +67,15 @@ int check_ptrs(const char* who, std::initializer_list<const void*> ps) {
 
 int path_of(int flags) { return flags & B200CP_PATH_MASK; }
 
+// B200CP_PATH_AUTO takes the tensor path where the shape allows it (B200CP_AUTO_TC=0 turns that off)
+const bool g_auto_tc = [] {
+  const char* e = getenv("B200CP_AUTO_TC");
+  return !(e && e[0] == '0');
+}();
+
 int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, const float* K1, const float* KH,
              const float* KW, float* out, cudaStream_t st, int flags, bool backward) {
   const int path = path_of(flags);
-  if (path == B200CP_PATH_TC3X || path == B200CP_PATH_TC1X)
-    return fail(B200CP_ERR_UNSUPPORTED, "cp4: the tcgen05 path is not available for this operation");
   Cp4Args a{};
   a.N = s->N; a.H = s->H; a.W = s->W; a.Y = s->Y; a.X = s->X; a.pad = s->pad;
   a.Cin = backward ? s->T : s->C;
@@ -80,6 +85,13 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
   a.KH = KH; a.KW = KW; a.in = in; a.out = out;
   a.flip = backward ? 1 : 0;
   a.Rs = s->Rank;
+  a.R = s->Rank;
+  if (path == B200CP_PATH_TC3X || path == B200CP_PATH_TC1X) return cp4_tc_launch(a, path == B200CP_PATH_TC3X ? 3 : 1, nullptr, st);
+  if (path == B200CP_PATH_AUTO && g_auto_tc) {
+    DeviceInfo di;
+    if (int rc = device_info(&di)) return rc;
+    if (cp4_tc_supported(a, di, nullptr)) return cp4_tc_launch(a, 3, nullptr, st);
+  }
   for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);
@@ -332,6 +344,31 @@ int b200cp_dense_bwd(int B, int order, const int* idims, const int* odims, int R
     if (int rc = contract_factors_launch(order, idims, odims, R, 1, F, nullptr, G, dF, nullptr, st)) return rc;
   }
   return B200CP_OK;
+}
+
+int b200cp_device_status(void) {
+  int v = 0;
+  if (int rc = tc_device_status(&v)) return rc;
+  if (v) return fail(B200CP_ERR_TIMEOUT, "a bounded wait ran out in block %d (code %d)", v & 0xffff, v >> 16);
+  return B200CP_OK;
+}
+
+int b200cp_debug_cp4_tc(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,
+                        const float* KH, const float* KW, float* U, float* P_block0, int terms, void* stream) {
+  if (int rc = check_shape(s, "b200cp_debug_cp4_tc")) return rc;
+  if (int rc = check_ptrs("b200cp_debug_cp4_tc", {X, K0, K1, KH, KW, U})) return rc;
+  Cp4Args a{};
+  a.N = s->N; a.H = s->H; a.W = s->W; a.Y = s->Y; a.X = s->X; a.pad = s->pad; a.Cin = s->C; a.Cout = s->T;
+  a.Fin = K1; a.Fout = K0; a.KH = KH; a.KW = KW; a.in = X; a.out = U; a.Rs = s->Rank; a.R = s->Rank;
+  return cp4_tc_launch(a, terms == 1 ? 1 : 3, P_block0, static_cast<cudaStream_t>(stream));
+}
+
+int b200cp_debug_tc_selftest(int mode, const float* A, const float* B, float* D, int* status, void* stream) {
+  if (int rc = check_ptrs("b200cp_debug_tc_selftest", {A, B, D, status})) return rc;
+  if (mode != 0 && mode != 1) return fail(B200CP_ERR_INVALID_ARG, "b200cp_debug_tc_selftest: mode must be 0 or 1");
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  return tc_selftest_launch(mode, A, B, D, status, static_cast<cudaStream_t>(stream));
 }
 
 const char* b200cp_last_error_string(void) { return last_error_buffer(); }

@@ -78,6 +78,15 @@ int cp4_recompose_launch(const b200cp_tensor_shape& s, const float* K0, const fl
                          const float* KW, float* K, cudaStream_t st);
 
 
+struct TcPlan {
+  int TH = 0, RP = 0;
+};
+bool cp4_tc_supported(const Cp4Args& a, const DeviceInfo& di, TcPlan* plan);
+// terms: 3 = hi/lo split (fp32-grade accuracy), 1 = single tf32 pass.  dbgP (nullable): CTA 0 dumps its P tile.
+int cp4_tc_launch(const Cp4Args& a, int terms, float* dbgP, cudaStream_t st);
+int tc_device_status(int* out);
+int tc_selftest_launch(int mode, const float* A, const float* B, float* D, int* status, cudaStream_t st);
+
 int rcp_chain_launch(int N, int H, int W, int order, const int* cdims, const int* tdims, int R, int FH, int FW,
                      const float* X, const float* const* A, const float* S, float* V, bool transposed,
                      cudaStream_t st);

@@ -135,6 +135,23 @@ def cp4_conv2d_step_host(X, dU, FT, FC, FY, FX, pad=1, flags=0, out=None):
     return U, dX, dK
 
 
+def device_status():
+    """Synchronise and raise if a tensor-path kernel gave up a bounded wait (``b200cp_device_status``)."""
+    check(lib.b200cp_device_status())
+
+
+def debug_cp4_tc(Input, FT, FC, FY, FX, pad=1, terms=3, p_floats=0):
+    """Diagnostic forward on the tensor path; also returns the first CTA's rank-R intermediate."""
+    Input, FT, FC, FY, FX = (_dev(t, n) for t, n in ((Input, "Input"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(Input, FT, FC, FY, FX, pad)
+    out = torch.empty((s.N, s.T, s.H, s.W), device=Input.device, dtype=torch.float32)
+    P = torch.zeros(max(p_floats, 1), device=Input.device, dtype=torch.float32)
+    with torch.cuda.device(Input.device):
+        check(lib.b200cp_debug_cp4_tc(C.byref(s), _p(Input), _p(FT), _p(FC), _p(FY), _p(FX), _p(out),
+                                      _p(P) if p_floats else None, terms, _stream()))
+    return out, P
+
+
 # ---- TF custom-op order -----------------------------------------------------
 def cp4_conv2d_nchw(U, K0, K1, K2, K3, flags=0):
     """``Cp4Conv2dNchw`` (Kernels/cp4_conv_nchw.cc:6-13): K0 [C,R], K1 [FH,R], K2 [FW,R], K3 [T,R],
