@@ -181,6 +181,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     flags = {"auto": P.PATH_AUTO, "simt": P.PATH_SIMT, "tc3x": P.PATH_TC3X}[args.path]
+    flags_f = P.PATH_AUTO if flags == P.PATH_TC3X else flags   # the factor-gradient kernel has no forced tensor path
 
     c = CFG
     n = c["N"]
@@ -200,25 +201,30 @@ def main():
     import ctypes as C
     s = P.tensor_shape(n, c["C"], c["H"], c["W"], c["T"], c["F"], c["F"], c["R"], c["pad"])
     lib = P._lib.lib
-    wsb = lib.b200cp_cp4_bwd_filter_workspace_bytes(C.byref(s), flags)
+    wsb = lib.b200cp_cp4_bwd_filter_workspace_bytes(C.byref(s), flags_f)
     ws = torch.empty(wsb // 4, device="cuda")
     ptr = lambda t: C.c_void_p(t.data_ptr())
-    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     fp = [ptr(f) for f in fac]
 
-    def step(i, ev=None):
+    def cur_stream():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def k_fwd(i, st):
         x, du, u, dx = sets[i % NSETS]
-        if ev:
-            ev[0].record()
         P._lib.check(lib.b200cp_cp4_fwd(C.byref(s), ptr(x), *fp, ptr(u), st, flags))
-        if ev:
-            ev[1].record()
+
+    def k_bwdd(i, st):
+        x, du, u, dx = sets[i % NSETS]
         P._lib.check(lib.b200cp_cp4_bwd_data(C.byref(s), ptr(du), *fp, ptr(dx), st, flags))
-        if ev:
-            ev[2].record()
-        P._lib.check(lib.b200cp_cp4_bwd_filter(C.byref(s), ptr(x), ptr(du), *fp, ptr(dK), ptr(ws), wsb, st, flags))
-        if ev:
-            ev[3].record()
+
+    def k_bwdf(i, st):
+        x, du, u, dx = sets[i % NSETS]
+        P._lib.check(lib.b200cp_cp4_bwd_filter(C.byref(s), ptr(x), ptr(du), *fp, ptr(dK), ptr(ws), wsb, st, flags_f))
+
+    def step(i, st):
+        k_fwd(i, st)
+        k_bwdd(i, st)
+        k_bwdf(i, st)
         if dist is not None:
             dist.all_reduce(dK)
 
@@ -227,27 +233,58 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def many(fn, k):
+        """k consecutive calls of fn as one CUDA graph (no host launch gaps); falls back to an eager loop."""
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g):
+                st = cur_stream()
+                for i in range(k):
+                    fn(i, st)
+            return g.replay, True
+        except Exception as e:  # capture not possible: time the eager loop instead
+            sys.stderr.write(f"[bench] graph capture failed ({e}); timing eager launches\n")
+            torch.cuda.synchronize()
+            return (lambda: [fn(i, cur_stream()) for i in range(k)]), False
+
     for i in range(args.warmup):
-        step(i)
+        step(i, cur_stream())
     barrier()
     K = args.steps
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K)]
+    l0 = P.launch_count()
+    run_steps, graphed = many(step, K)
+    launches = P.launch_count() - l0 if graphed else None
+    run_steps()                      # one untimed replay (graph upload, caches)
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
     barrier()
-    l0 = P.launch_count()
+    if launches is None:
+        l0 = P.launch_count()
     e0.record()
-    for i in range(K):
-        step(i, evs[i])
+    run_steps()
     e1.record()
     barrier()
-    launches = P.launch_count() - l0
+    if launches is None:
+        launches = P.launch_count() - l0
     ms = e0.elapsed_time(e1)
+    # the three kernels on their own, K back-to-back launches each, same rotating buffers, same run
+    kt = []
+    for fn in (k_fwd, k_bwdd, k_bwdf):
+        run_k, _ = many(fn, K)
+        run_k()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        run_k()
+        a1.record()
+        torch.cuda.synchronize()
+        kt.append(a0.elapsed_time(a1) / K)
     clocks = sampler.stop() if rank == 0 else None
-    kt = np.array([[evs[i][j].elapsed_time(evs[i][j + 1]) for j in range(3)] for i in range(K)])  # ms
+    mean_ms = np.array(kt)
     if dist is not None:
         tms = torch.tensor([ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
@@ -290,7 +327,6 @@ def main():
 
     # ---- roofline of the dominant kernel ---------------------------------------------------------
     names = ["cp4_fwd", "cp4_bwd_data", "cp4_bwd_filter"]
-    mean_ms = kt.mean(axis=0)
     dom = int(np.argmax(mean_ms))
     alg_bytes = 4 * n * HW * (c["C"] + c["T"]) + 4 * c["R"] * (c["T"] + c["C"] + 2 * c["F"])
     peak, peak_kind = hbm_peak()
@@ -319,6 +355,7 @@ def main():
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic (seeded; X~U[-1,1], factors~N(0,1/sqrt(9C)), dU~N(0,1))",
         "config": {"workload": WORKLOAD, "images_per_step_per_gpu": n, "path": args.path,
+                   "timing": "K steps replayed as one CUDA graph between two events" if graphed else "K eager steps between two events",
                    "l2": f"{NSETS} rotating buffer sets ({NSETS * 4 * n * HW * 64 * 4 / 1e6:.0f} MB) > 126 MB L2",
                    "collective": "allreduce of %d packed factor-gradient floats" % nK if world > 1 else "none"},
         "roofline": roofline, "cpu_baseline": cpu,

@@ -43,7 +43,10 @@ using namespace tc;
 constexpr int kKC = 16;          // channels per TMA stage
 constexpr int kStagesHi = 4;     // TMA stages in flight
 constexpr int kStageBytes = 4 * kKC * 128;  // four 32-pixel groups of kKC rows of 128 B
-constexpr int kNT = 256;
+constexpr int kWorkers = 256;    // 8 worker warps: tf32 split, TMEM read-out, stencil, stores
+constexpr int kNT = kWorkers + 64;  // + warp 8 (issues every tcgen05.mma) + warp 9 (issues every TMA load)
+constexpr int kD1Stride = 96;    // TMEM columns between the two GEMM-1 accumulator sets
+constexpr int kD2Col = 192;      // first TMEM column of the GEMM-2 accumulator
 
 struct TcGeom {
   int N, Cin, Cout, H, W, HW, Y, X, pad, R, Rs, r0, flip, terms;
@@ -55,7 +58,82 @@ struct TcGeom {
 
 __device__ __forceinline__ int floor4(int v) { return v - (((v % 4) + 4) % 4); }
 
-template <int RP>
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait shared by the three roles: gives up after about a second, or as soon as another
+// role has given up (the flag), so that every thread reaches the common exit.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t a = smem_u32(bar);
+  const long long t0 = clock64();
+  for (int it = 0;; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((it & 31) == 31) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 1500000000ll) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// barrier 1 over the 256 worker threads with an OR-reduction of `pred`
+__device__ __forceinline__ bool workers_sync_or(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %1, 0;\n"
+      "bar.red.or.pred p, 1, 256, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
+// Z[4 ranks] of one output pixel: per-rank Y x X stencil over Ps, columns outside the image masked
+template <int FS>
+__device__ __forceinline__ void stencil4(const TcGeom& g, const float* __restrict__ Ws, const float* __restrict__ p0,
+                                         int RP, int rbase, int w, float (&z)[4]) {
+  const int Y = FS ? FS : g.Y, X = FS ? FS : g.X;
+  z[0] = z[1] = z[2] = z[3] = 0.f;
+#pragma unroll
+  for (int y = 0; y < (FS ? FS : 1); ++y) {
+    for (int yy = FS ? y : 0; yy < (FS ? y + 1 : Y); ++yy) {
+#pragma unroll
+      for (int x = 0; x < (FS ? FS : 1); ++x) {
+        for (int xx = FS ? x : 0; xx < (FS ? x + 1 : X); ++xx) {
+          const int wx = w + xx - g.pad;
+          const float msk = (wx >= 0 && wx < g.W) ? 1.f : 0.f;
+          const float4 wt = *reinterpret_cast<const float4*>(Ws + (yy * X + xx) * RP + rbase);
+          const float* p = p0 + yy * g.W + xx;
+          z[0] = fmaf(wt.x * msk, p[0], z[0]);
+          z[1] = fmaf(wt.y * msk, p[g.Mmax], z[1]);
+          z[2] = fmaf(wt.z * msk, p[2 * g.Mmax], z[2]);
+          z[3] = fmaf(wt.w * msk, p[3 * g.Mmax], z[3]);
+        }
+      }
+    }
+  }
+}
+
+// Warp-specialised: warp 9 streams the input through TMA, warps 0-7 split each stage into tf32 hi / lo,
+// warp 8 issues the MMAs; the roles meet only through mbarriers, so loads, conversion and tensor work overlap.
+template <int RP, int FS>
 __global__ void __launch_bounds__(kNT) cp4_tc_kernel(const TcGeom g, const __grid_constant__ CUtensorMap xmap,
                                                      const float* __restrict__ Fin, const float* __restrict__ Fout,
                                                      const float* __restrict__ KH, const float* __restrict__ KW,
@@ -65,13 +143,16 @@ __global__ void __launch_bounds__(kNT) cp4_tc_kernel(const TcGeom g, const __gri
   float* Ws = reinterpret_cast<float*>(sm + g.oWs);
   float* Ps = reinterpret_cast<float*>(sm + g.oPs);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + g.oBar);
-  uint64_t* full = bars;                    // [kStagesHi] TMA landed
-  uint64_t* freeb = bars + kStagesHi;       // [kStagesHi] MMAs that read the stage are done
-  uint64_t* lofree = bars + 2 * kStagesHi;  // [2]
-  uint64_t* d1full = lofree + 2;
-  uint64_t* d2full = d1full + 1;
+  uint64_t* full = bars;                      // [kStagesHi] TMA landed                      (tx bytes)
+  uint64_t* ready = full + kStagesHi;         // [kStagesHi] stage split into hi / lo        (8 warp arrivals)
+  uint64_t* freeb = ready + kStagesHi;        // [kStagesHi] MMAs that read the stage done   (commit)
+  uint64_t* lofree = freeb + kStagesHi;       // [2] MMAs that read the lo buffer done       (commit)
+  uint64_t* d1full = lofree + 2;              // [2] GEMM-1 accumulator complete             (commit)
+  uint64_t* d1free = d1full + 2;              // [2] GEMM-1 accumulator read out             (8 warp arrivals)
+  uint64_t* a2ready = d1free + 2;             // GEMM-2 operand written                      (8 warp arrivals)
+  uint64_t* d2full = a2ready + 1;             // GEMM-2 accumulator complete                 (commit)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d2full + 1);
-  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int band = blockIdx.x % g.bands, n = blockIdx.x / g.bands;
@@ -88,17 +169,21 @@ __global__ void __launch_bounds__(kNT) cp4_tc_kernel(const TcGeom g, const __gri
   if (tid == 0) {
     for (int i = 0; i < kStagesHi; ++i) {
       mbar_init(&full[i], 1);
+      mbar_init(&ready[i], kWorkers / 32);
       mbar_init(&freeb[i], 1);
     }
-    mbar_init(&lofree[0], 1);
-    mbar_init(&lofree[1], 1);
-    mbar_init(d1full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&lofree[i], 1);
+      mbar_init(&d1full[i], 1);
+      mbar_init(&d1free[i], kWorkers / 32);
+    }
+    mbar_init(a2ready, kWorkers / 32);
     mbar_init(d2full, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&xmap);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, (uint32_t)g.ncols);
+  if (warp == 8) tmem_alloc(tmem_slot, (uint32_t)g.ncols);
   // factor operands (K-major, no swizzle): element (n, k) at (n/8)*SBO + (k/4)*128 + (n%8)*16 + (k%4)*4
   {
     uint8_t *b1h = sm + g.oB1hi, *b1l = sm + g.oB1lo, *b2h = sm + g.oB2hi, *b2l = sm + g.oB2lo;
@@ -130,39 +215,139 @@ __global__ void __launch_bounds__(kNT) cp4_tc_kernel(const TcGeom g, const __gri
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tD1 = tmem_base, tD2 = tmem_base + 64;  // D1: columns [0, RP), D2: columns [64, 64 + Tpad)
-  const uint32_t idesc1 = make_idesc_tf32(RP, 1, 0);
-  const uint32_t idesc2 = make_idesc_tf32((uint32_t)g.Tpad, 0, 0);
-  bool ok = true;
+  const uint32_t tD2 = tmem_base + kD2Col;
+  // diagnostic cycle stamps of one CTA: worker thread 0 at [0, 512), the MMA thread at [512, 1024), the TMA thread at [1024, 1536)
+  float* dbgT = (dbgP != nullptr && blockIdx.x == gridDim.x / 2 && (tid == 0 || tid == 256 || tid == 288))
+                    ? dbgP + RP * g.Mmax + (tid == 0 ? 0 : tid == 256 ? 512 : 1024) : nullptr;
+  const long long tstart = clock64();
+  auto stamp = [&](int idx) { if (dbgT) dbgT[idx] = (float)(clock64() - tstart); };
 
-  auto issue_tma = [&](int s) {  // thread 0 only
-    const int b = s / g.NKC, kc = s - b * g.NKC, slot = s % kStagesHi;
-    uint8_t* dst = sm + g.oXhi + slot * kStageBytes;
-    mbar_expect_tx(&full[slot], kStageBytes);
+  if (warp == 9) {
+    // ================= TMA producer ===================================================================
+    if (lane == 0) {
+      for (int t = 0; t < NS; ++t) {
+        const int b = t / g.NKC, kc = t - b * g.NKC, slot = t % kStagesHi;
+        if (t >= kStagesHi && !wait_or_abort(&freeb[slot], ((t / kStagesHi) - 1) & 1, abort_flag)) break;
+        if (t < 100) stamp(t);
+        uint8_t* dst = sm + g.oXhi + slot * kStageBytes;
+        mbar_expect_tx(&full[slot], kStageBytes);
 #pragma unroll
-    for (int grp = 0; grp < 4; ++grp)
-      tma_load_3d(dst + grp * (kKC * 128), &xmap, &full[slot], s0 + b * 128 + grp * 32, kc * kKC, n);
-  };
-
-  if (tid == 0)
-    for (int s = 0; s < min(kStagesHi - 1, NS); ++s) issue_tma(s);
-
-  // ---- GEMM 1: P = in^T * Fin, one 128-position block at a time ---------------------------------------
-  for (int s = 0; s < NS; ++s) {
-    const int b = s / g.NKC, kc = s - b * g.NKC, slot = s % kStagesHi, l = s & 1;
-    if (tid == 0) {
-      const int t = s + kStagesHi - 1;
-      if (t < NS) {
-        if (t >= kStagesHi) ok = mbar_wait(&freeb[t % kStagesHi], ((t / kStagesHi) - 1) & 1) && ok;
-        if (ok) issue_tma(t);
+        for (int grp = 0; grp < 4; ++grp)
+          tma_load_3d(dst + grp * (kKC * 128), &xmap, &full[slot], s0 + b * 128 + grp * 32, kc * kKC, n);
       }
     }
-    ok = mbar_wait(&full[slot], (s / kStagesHi) & 1) && ok;
-    if (g.terms == 3 && s >= 2) ok = mbar_wait(&lofree[l], ((s >> 1) - 1) & 1) && ok;
-    float4* hi4 = reinterpret_cast<float4*>(sm + g.oXhi + slot * kStageBytes);
-    float4* lo4 = reinterpret_cast<float4*>(sm + g.oXlo + l * kStageBytes);
-    if (ok) {
-      for (int i = tid; i < kStageBytes / 16; i += kNT) {
+  } else if (warp == 8) {
+    // ================= MMA issuer ======================================================================
+    if (lane == 0) {
+      const uint32_t idesc1 = make_idesc_tf32(RP, 1, 0);
+      const uint32_t idesc2 = make_idesc_tf32((uint32_t)g.Tpad, 0, 0);
+      // MN-major tf32 operand: rows of 32 pixels (128 B), one row per channel, 32-byte chunks swizzled within
+      // groups of 4 rows (the only MN-major layout tf32 has).  LBO: next 32-pixel group, SBO: next 4 rows.
+      const uint64_t dA0 = make_smem_desc(0, kKC * 128, 512, kSwizzle128B_32B);
+      const uint64_t dB1 = make_smem_desc(0, 128, g.Cpad * 32, kSwizzleNone);
+      const uint32_t xhi = smem_u32(sm + g.oXhi), xlo = smem_u32(sm + g.oXlo);
+      const uint32_t b1h = smem_u32(sm + g.oB1hi), b1l = smem_u32(sm + g.oB1lo);
+      bool ok = true;
+      for (int s = 0; s < NS && ok; ++s) {
+        const int b = s / g.NKC, kc = s - b * g.NKC, slot = s % kStagesHi, l = s & 1;
+        const uint32_t tD1 = tmem_base + (b & 1) * kD1Stride;
+        if (kc == 0 && b >= 2) ok = wait_or_abort(&d1free[b & 1], ((b >> 1) - 1) & 1, abort_flag);
+        if (s < 40) stamp(6 * s + 5);
+        ok = ok && wait_or_abort(&ready[slot], (s / kStagesHi) & 1, abort_flag);
+        if (!ok) break;
+        if (s < 40) stamp(6 * s);
+        tc_fence_after_sync();
+        if (s < 40) stamp(6 * s + 1);
+#pragma unroll
+        for (int kk = 0; kk < kKC / 8; ++kk) {
+          const uint64_t dah = dA0 + (uint64_t)((xhi + slot * kStageBytes + kk * 1024) >> 4);
+          const uint64_t dal = dA0 + (uint64_t)((xlo + l * kStageBytes + kk * 1024) >> 4);
+          const uint32_t koff = (uint32_t)(kc * (kKC / 4) + kk * 2) * 128;
+          const uint64_t dbh = dB1 + (uint64_t)((b1h + koff) >> 4);
+          const uint64_t dbl = dB1 + (uint64_t)((b1l + koff) >> 4);
+          // one accumulator per (term, K half): the MMAs of a stage do not depend on each other
+          const uint32_t tA = tD1 + (RP == 16 ? kk * 48 : 0);
+          const bool first = (kc == 0) && (RP == 16 || kk == 0);
+          mma_tf32_ss(tA, dah, dbh, idesc1, !first);
+          if (g.terms == 3) {
+            mma_tf32_ss(tA + (RP == 16 ? 16 : 0), dal, dbh, idesc1, RP == 16 ? !first : true);
+            mma_tf32_ss(tA + (RP == 16 ? 32 : 0), dah, dbl, idesc1, RP == 16 ? !first : true);
+          }
+        }
+        if (s < 40) stamp(6 * s + 2);
+        mma_commit(&freeb[slot]);
+        if (s < 40) stamp(6 * s + 3);
+        if (g.terms == 3) mma_commit(&lofree[l]);
+        if (kc == g.NKC - 1) mma_commit(&d1full[b & 1]);
+        if (s < 40) stamp(6 * s + 4);
+      }
+      // GEMM 2, one block of 128 output pixels at a time
+      const uint64_t dA2 = make_smem_desc(0, 2048, 128, kSwizzleNone);
+      const uint64_t dB2 = make_smem_desc(0, 128, RP * 32, kSwizzleNone);
+      const uint32_t a2h = smem_u32(sm + g.oA2hi), a2l = smem_u32(sm + g.oA2lo);
+      const uint32_t b2h = smem_u32(sm + g.oB2hi), b2l = smem_u32(sm + g.oB2lo);
+      for (int ob = 0; ob < OB && ok; ++ob) {
+        ok = wait_or_abort(a2ready, ob & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < RP / 8; ++kk) {
+          const uint64_t dah = dA2 + (uint64_t)((a2h + kk * 4096) >> 4), dal = dA2 + (uint64_t)((a2l + kk * 4096) >> 4);
+          const uint64_t dbh = dB2 + (uint64_t)((b2h + kk * 256) >> 4), dbl = dB2 + (uint64_t)((b2l + kk * 256) >> 4);
+          mma_tf32_ss(tD2, dah, dbh, idesc2, kk != 0);
+          if (g.terms == 3) {
+            mma_tf32_ss(tD2, dal, dbh, idesc2, true);
+            mma_tf32_ss(tD2, dah, dbl, idesc2, true);
+          }
+        }
+        mma_commit(d2full);
+      }
+    }
+  } else {
+    // ================= workers ============================================================================
+    bool ok = true;
+    const int qd = warp & 3, hf = warp >> 2;
+    // TMEM accumulator of block b -> Ps[r][b*128 + position]
+    auto epilogue1 = [&](int b) {
+      ok = ok && wait_or_abort(&d1full[b & 1], (b >> 1) & 1, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        const uint32_t tD1 = tmem_base + (b & 1) * kD1Stride + ((uint32_t)(qd * 32) << 16);
+        const int m = b * 128 + qd * 32 + lane;
+#pragma unroll
+        for (int c8 = 0; c8 < RP / 16; ++c8) {
+          const int col = hf * (RP / 2) + c8 * 8;
+          float v[8];
+          tmem_ld8(tD1 + col, v);
+          if (RP == 16) {  // six partial accumulators: (term, K half) at columns 16 * i
+            const int nacc = g.terms == 3 ? 6 : 2;
+            for (int a = 1; a < nacc; ++a) {
+              float u[8];
+              tmem_ld8(tD1 + col + (g.terms == 3 ? 16 * a : 48 * a), u);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] += u[i];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) Ps[(size_t)(col + i) * g.Mmax + m] = v[i];
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&d1free[b & 1]);
+      }
+    };
+    stamp(0);
+    for (int s = 0; s < NS && ok; ++s) {
+      const int b = s / g.NKC, kc = s - b * g.NKC, slot = s % kStagesHi, l = s & 1;
+      ok = wait_or_abort(&full[slot], (s / kStagesHi) & 1, abort_flag);
+      if (s < 60) stamp(16 + 4 * s);
+      if (ok && g.terms == 3 && s >= 2) ok = wait_or_abort(&lofree[l], ((s >> 1) - 1) & 1, abort_flag);
+      if (s < 60) stamp(16 + 4 * s + 1);
+      if (!ok) break;
+      float4* hi4 = reinterpret_cast<float4*>(sm + g.oXhi + slot * kStageBytes);
+      float4* lo4 = reinterpret_cast<float4*>(sm + g.oXlo + l * kStageBytes);
+#pragma unroll
+      for (int i = tid; i < kStageBytes / 16; i += kWorkers) {
         const float4 v = hi4[i];
         float4 h, d;
         h.x = tf32_hi(v.x); h.y = tf32_hi(v.y); h.z = tf32_hi(v.z); h.w = tf32_hi(v.w);
@@ -170,93 +355,32 @@ __global__ void __launch_bounds__(kNT) cp4_tc_kernel(const TcGeom g, const __gri
         hi4[i] = h;
         if (g.terms == 3) lo4[i] = d;
       }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ready[slot]);
+      if (s < 60) stamp(16 + 4 * s + 2);
+      if (kc == g.NKC - 1 && b >= 1) epilogue1(b - 1);
+      if (s < 60) stamp(16 + 4 * s + 3);  // one block behind, so the tensor pipe is never waited on
     }
-    fence_proxy_async();
-    if (__syncthreads_or(!ok)) { ok = false; break; }
-    if (dbgP != nullptr && blockIdx.x == 0 && s == 0) {  // diagnostic: first stage and the factor operand as the MMA sees them
-      float* d1 = dbgP + RP * g.Mmax;
-      for (int i = tid; i < kStageBytes / 4; i += kNT) d1[i] = reinterpret_cast<const float*>(hi4)[i];
-      for (int i = tid; i < 512; i += kNT) d1[kStageBytes / 4 + i] = reinterpret_cast<const float*>(sm + g.oB1hi)[i];
-      if (tid == 0) {
-        float* d3 = d1 + kStageBytes / 4 + 512;
-        d3[0] = (float)tmem_base; d3[1] = (float)MB; d3[2] = (float)NS; d3[3] = (float)s0; d3[4] = (float)(idesc1 >> 16);
-        d3[5] = (float)(idesc1 & 0xffff); d3[6] = (float)smem_u32(hi4); d3[7] = (float)smem_u32(sm + g.oB1hi);
-      }
-    }
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t ahi = smem_u32(hi4), alo = smem_u32(lo4);
-      const uint32_t bhi = smem_u32(sm + g.oB1hi), blo = smem_u32(sm + g.oB1lo);
-#pragma unroll
-      for (int kk = 0; kk < kKC / 8; ++kk) {
-        // MN-major tf32 operand: rows of 32 pixels (128 B), one row per channel, 32-byte chunks swizzled within
-        // groups of 4 rows (the only MN-major layout tf32 has).  LBO: next 32-pixel group, SBO: next 4 rows.
-        const uint64_t dah = make_smem_desc(ahi + kk * 1024, kKC * 128, 512, kSwizzle128B_32B);
-        const uint64_t dal = make_smem_desc(alo + kk * 1024, kKC * 128, 512, kSwizzle128B_32B);
-        const uint32_t koff = (uint32_t)(kc * (kKC / 4) + kk * 2) * 128;
-        const uint64_t dbh = make_smem_desc(bhi + koff, 128, g.Cpad * 32, kSwizzleNone);
-        const uint64_t dbl = make_smem_desc(blo + koff, 128, g.Cpad * 32, kSwizzleNone);
-        mma_tf32_ss(tD1, dah, dbh, idesc1, !(kc == 0 && kk == 0));
-        if (g.terms == 3) {
-          mma_tf32_ss(tD1, dal, dbh, idesc1, true);
-          mma_tf32_ss(tD1, dah, dbl, idesc1, true);
-        }
-      }
-      mma_commit(&freeb[slot]);
-      if (g.terms == 3) mma_commit(&lofree[l]);
-      if (kc == g.NKC - 1) mma_commit(d1full);
-    }
-    if (kc == g.NKC - 1) {
-      // epilogue 1: TMEM accumulators of block b -> Ps[r][b*128 + position]
-      ok = mbar_wait(d1full, b & 1) && ok;
-      if (__syncthreads_or(!ok)) { ok = false; break; }
-      tc_fence_after_sync();
-      {
-        const int qd = warp & 3, hf = warp >> 2;
-        const int m = b * 128 + qd * 32 + lane;
-#pragma unroll
-        for (int c8 = 0; c8 < RP / 16; ++c8) {
-          const int col = hf * (RP / 2) + c8 * 8;
-          float v[8];
-          tmem_ld8(tD1 + ((uint32_t)(qd * 32) << 16) + col, v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) Ps[(size_t)(col + i) * g.Mmax + m] = v[i];
-        }
-      }
-      tc_fence_before_sync();
-      if (__syncthreads_or(!ok)) { ok = false; break; }
-    }
-  }
+    if (ok) epilogue1(MB - 1);
+    stamp(1);
+    ok = !workers_sync_or(!ok);
+    if (ok && dbgP != nullptr && blockIdx.x == 0)
+      for (int i = tid; i < RP * g.Mmax; i += kWorkers) dbgP[i] = Ps[i];
 
-  if (ok && dbgP != nullptr && blockIdx.x == 0)
-    for (int i = tid; i < RP * g.Mmax; i += kNT) dbgP[i] = Ps[i];
-
-  // ---- stencil + GEMM 2 + store, one block of 128 output pixels at a time ----------------------------------
-  if (ok) {
-    const int j = tid & 127, hf = tid >> 7;
+    // ---- stencil + GEMM 2 + store, one block of 128 output pixels at a time ------------------------------------
+    const int j = tid & 127, rhalf = tid >> 7;
     uint8_t *a2h = sm + g.oA2hi, *a2l = sm + g.oA2lo;
-    for (int ob = 0; ob < OB; ++ob) {
+    for (int ob = 0; ob < OB && ok; ++ob) {
       const int q = q0 + ob * 128 + j;
       const bool valid = q < q1;
       const int w = q % g.W;
       const float* pbase = Ps + (q - g.pad * g.W - g.pad - s0);
 #pragma unroll
       for (int r4 = 0; r4 < RP / 8; ++r4) {
-        const int rbase = hf * (RP / 2) + r4 * 4;
+        const int rbase = rhalf * (RP / 2) + r4 * 4;
         float z[4] = {0.f, 0.f, 0.f, 0.f};
-        if (valid) {
-          for (int y = 0; y < g.Y; ++y)
-            for (int x = 0; x < g.X; ++x) {
-              const int wx = w + x - g.pad;
-              if (wx < 0 || wx >= g.W) continue;
-              const float4 wt = *reinterpret_cast<const float4*>(Ws + (y * g.X + x) * RP + rbase);
-              const float* p = pbase + y * g.W + x + (size_t)rbase * g.Mmax;
-              z[0] = fmaf(wt.x, p[0], z[0]);
-              z[1] = fmaf(wt.y, p[g.Mmax], z[1]);
-              z[2] = fmaf(wt.z, p[2 * g.Mmax], z[2]);
-              z[3] = fmaf(wt.w, p[3 * g.Mmax], z[3]);
-            }
-        }
+        if (valid) stencil4<FS>(g, Ws, pbase + (size_t)rbase * g.Mmax, RP, rbase, w, z);
         float4 h, d;
         h.x = tf32_hi(z[0]); h.y = tf32_hi(z[1]); h.z = tf32_hi(z[2]); h.w = tf32_hi(z[3]);
         d.x = z[0] - h.x; d.y = z[1] - h.y; d.z = z[2] - h.z; d.w = z[3] - h.w;
@@ -266,30 +390,15 @@ __global__ void __launch_bounds__(kNT) cp4_tc_kernel(const TcGeom g, const __gri
         *reinterpret_cast<float4*>(a2l + o) = d;
       }
       fence_proxy_async();
-      __syncthreads();
-      if (tid == 0) {
-        tc_fence_after_sync();
-        const uint32_t ah = smem_u32(a2h), al = smem_u32(a2l);
-        const uint32_t bh = smem_u32(sm + g.oB2hi), bl = smem_u32(sm + g.oB2lo);
-#pragma unroll
-        for (int kk = 0; kk < RP / 8; ++kk) {
-          const uint64_t dah = make_smem_desc(ah + kk * 4096, 2048, 128, kSwizzleNone);
-          const uint64_t dal = make_smem_desc(al + kk * 4096, 2048, 128, kSwizzleNone);
-          const uint64_t dbh = make_smem_desc(bh + kk * 256, 128, RP * 32, kSwizzleNone);
-          const uint64_t dbl = make_smem_desc(bl + kk * 256, 128, RP * 32, kSwizzleNone);
-          mma_tf32_ss(tD2, dah, dbh, idesc2, kk != 0);
-          if (g.terms == 3) {
-            mma_tf32_ss(tD2, dal, dbh, idesc2, true);
-            mma_tf32_ss(tD2, dah, dbl, idesc2, true);
-          }
-        }
-        mma_commit(d2full);
-      }
-      ok = mbar_wait(d2full, ob & 1) && ok;
-      if (__syncthreads_or(!ok)) { ok = false; break; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a2ready);
+      if (ob < 8) stamp(300 + 4 * ob);
+      ok = wait_or_abort(d2full, ob & 1, abort_flag);
+      if (ob < 8) stamp(300 + 4 * ob + 1);
+      if (!ok) break;
       tc_fence_after_sync();
       {
-        const int qd = warp & 3, ch = warp >> 2;
+        const int ch = hf;
         const int qq = q0 + ob * 128 + qd * 32 + lane;
         float* dst = out + (size_t)n * g.Cout * g.HW + qq;
         for (int c16 = ch; c16 < g.Tpad / 16; c16 += 2) {
@@ -305,20 +414,22 @@ __global__ void __launch_bounds__(kNT) cp4_tc_kernel(const TcGeom g, const __gri
         }
       }
       tc_fence_before_sync();
-      if (__syncthreads_or(!ok)) { ok = false; break; }
+      // no barrier here: the next GEMM 2 starts only after all eight warps have arrived on a2ready again,
+      // which each does after its own read-out above
+      if (ob < 8) stamp(300 + 4 * ob + 2);
     }
   }
 
   // ---- exit ---------------------------------------------------------------------------------------------------
-  if (!ok) {
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
     if (tid == 0) atomicCAS(&g_tc_status, 0, (1 << 16) | (int)(blockIdx.x & 0xffff));
     // give bulk copies that may still be in flight towards this CTA's shared memory time to land
     const long long t0 = clock64();
     while (clock64() - t0 < 400000) {}
   }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) {
+  if (warp == 8) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, (uint32_t)g.ncols);
   }
@@ -357,11 +468,13 @@ bool cp4_tc_supported(const Cp4Args& a, const DeviceInfo& di, TcPlan* plan) {
     if ((int)sm > di.smem_optin) break;
     const int bands = ceil_div(a.H, TH);
     const long ctas = (long)a.N * bands;
-    const int occ = std::max(1, std::min((int)((228 * 1024) / (sm + 1024)), 512 / next_pow2(64 + Tpad)));
+    const int occ = std::max(1, std::min((int)((228 * 1024) / (sm + 1024)), 512 / next_pow2(kD2Col + Tpad)));
     const long waves = (ctas + (long)di.sm_count * occ - 1) / ((long)di.sm_count * occ);
-    // per CTA: GEMM-1 blocks + output blocks (weighted), a fixed set-up cost
-    const double per = (double)(Mmax / 128) * (Cpad / 16.0 + 2.0) + ceil_div(TH * a.W, 128) * (RP / 8.0 + Tpad / 16.0) + 6.0;
-    const double cost = (double)waves * per * occ;
+    // measured on B200: a GEMM-1 stage costs about 1.5k cycles of the MMA-issuing thread, an output block about 6k
+    // (stencil, GEMM 2, stores); resident CTAs overlap each other's phases
+    const int MBf = Mmax / 128, OBf = ceil_div(std::min(TH, a.H) * a.W, 128);
+    const double per = MBf * (Cpad / (double)kKC) * 1.5 * (RP / 16.0 > 2 ? 2.0 : 1.0) + OBf * (4.0 + RP / 8.0 + Tpad / 64.0) + 3.0;
+    const double cost = (double)waves * per * (occ > 1 ? 1.0 + 0.15 * (occ - 1) : 1.0);
     if (cost < bestCost) { bestCost = cost; bestTH = TH; }
   }
   if (!bestTH) return false;
@@ -392,7 +505,7 @@ int cp4_tc_launch(const Cp4Args& a, int terms, float* dbgP, cudaStream_t st) {
   g.bands = ceil_div(a.H, g.TH);
   g.NKC = g.Cpad / kKC;
   g.Mmax = (int)align_up((size_t)((g.TH + a.Y - 1) * a.W + a.X - 1 + 3), 128);
-  g.ncols = next_pow2(64 + g.Tpad);
+  g.ncols = next_pow2(kD2Col + g.Tpad);
   const int a2 = 128 * g.RP * 4;
   int o = 0;
   g.oXhi = 0;
@@ -429,7 +542,7 @@ int cp4_tc_launch(const Cp4Args& a, int terms, float* dbgP, cudaStream_t st) {
             g.bands, g.RP, g.Cpad, g.Tpad, g.Mmax, g.ncols, g.smem, ctas, terms);
 #define LAUNCH_TC(RPV)                                                                                            \
   do {                                                                                                            \
-    auto kern = cp4_tc_kernel<RPV>;                                                                               \
+    auto kern = (a.Y == 3 && a.X == 3) ? cp4_tc_kernel<RPV, 3> : cp4_tc_kernel<RPV, 0>;                           \
     B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));         \
     kern<<<(unsigned)ctas, kNT, g.smem, st>>>(g, map, a.Fin, a.Fout, a.KH, a.KW, a.out, dbgP);                    \
   } while (0)

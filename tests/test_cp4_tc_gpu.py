@@ -59,13 +59,8 @@ def test_tc_intermediate_of_first_band():
         H = W = 16
         TH, Y, Xf, RP = 4, 3, 3, 16
         Mmax = ((TH + Y - 1) * W + Xf - 1 + 3 + 127) // 128 * 128
-        U, Pd = P.debug_cp4_tc(*dev(X, K0, K1, KH, KW), pad, 3, RP * Mmax + 2048 + 512 + 16)
+        U, Pd = P.debug_cp4_tc(*dev(X, K0, K1, KH, KW), pad, 3, RP * Mmax + 64)
         P.device_status()
-        raw = Pd.cpu().numpy()
-        st0, b1, misc = raw[RP * Mmax:RP * Mmax + 2048], raw[RP * Mmax + 2048:RP * Mmax + 2560], raw[RP * Mmax + 2560:]
-        print("stage0 nonzero", int((st0 != 0).sum()), "absmax", float(np.abs(st0).max()), "B1 nonzero", int((b1 != 0).sum()),
-              "misc", misc[:8], "P nonzero", int((raw[:RP * Mmax] != 0).sum()), "U absmax", float(U.abs().max()))
-        print("stage0 head", st0[:40])
         Pd = Pd[:RP * Mmax]
         ha = -pad * W - pad
         s0 = ha - ((ha % 4) + 4) % 4
