@@ -80,6 +80,22 @@ int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const fl
                           const float* K1, const float* KH, const float* KW, float* dK_packed, void* workspace,
                           size_t workspace_bytes, void* stream, int flags);
 
+/* The same four factor gradients for callers that must not allocate device memory and have no
+ * workspace to hand over: code running inside another framework's stream-ordered section, a
+ * real-time loop, or a plugin whose host forbids cudaMalloc after initialisation.  It has no
+ * counterpart in the reference.  The per-tile partial sums go to a fixed 8 MiB array inside the
+ * library's device image (every GPU that loads the library holds it until the process exits), so
+ *   - shapes whose partial sums need more than 8 MiB are refused with B200CP_ERR_UNSUPPORTED
+ *     (b200cp_cp4_bwd_filter_workspace_bytes tells the need; e.g. N=32, C=T=64, 56x56, R=16 needs 5.5 MB);
+ *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating library routine;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call before any stream capture begins on that device;
+ *   - all calls on a device share the one array: two calls that may overlap on the GPU (different
+ *     streams, no dependency between them) race and give wrong gradients.  Nothing in the array has to
+ *     be cleared between calls: every launch overwrites all the partial sums it later reads. */
+int b200cp_cp4_bwd_filter_noalloc(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                                  const float* K1, const float* KH, const float* KW, float* dK_packed, void* stream);
+
 /* Dense filter gradient dK[t,c,y,x] = sum_{n,h,w} dU[n,t,h,w] Xpad[n,c,h+y,w+x].
  * Replaces cp4_conv2d_backward_filter_full_gpu (Cuda_kernels/cp4Conv2dBackwardFilter.cuh:7-11). */
 int b200cp_cp4_bwd_filter_full(const b200cp_tensor_shape* s, const float* X, const float* dU, float* dK, void* stream);

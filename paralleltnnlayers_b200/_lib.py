@@ -42,6 +42,7 @@ def _load():
         "b200cp_cp4_bwd_data": (i, [sp, fp, fp, fp, fp, fp, fp, vp, i]),
         "b200cp_cp4_bwd_filter_workspace_bytes": (sz, [sp, i]),
         "b200cp_cp4_bwd_filter": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp, sz, vp, i]),
+        "b200cp_cp4_bwd_filter_noalloc": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp]),
         "b200cp_cp4_bwd_filter_full": (i, [sp, fp, fp, fp, vp]),
         "b200cp_cp4_recompose": (i, [sp, fp, fp, fp, fp, fp, vp]),
         "b200cp_cp4_fwd_host": (i, [sp, fp, fp, fp, fp, fp, fp, i]),

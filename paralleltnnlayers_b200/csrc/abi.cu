@@ -178,6 +178,30 @@ int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const fl
   return B200CP_OK;
 }
 
+int b200cp_cp4_bwd_filter_noalloc(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                                  const float* K1, const float* KH, const float* KW, float* dK_packed, void* stream) {
+  if (int rc = check_shape(s, "b200cp_cp4_bwd_filter_noalloc")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_bwd_filter_noalloc", {X, dU, K0, K1, KH, KW, dK_packed})) return rc;
+  if (s->Y != s->X || (s->Y & 1) == 0 || s->pad != (s->Y - 1) / 2)
+    return fail(B200CP_ERR_UNSUPPORTED,
+                "b200cp_cp4_bwd_filter_noalloc: needs Y == X odd and pad == (Y-1)/2 (Y=%u X=%u pad=%u)", s->Y, s->X, s->pad);
+  const size_t need = cp4_bwd_filter_simt_workspace(*s), cap = cp4_bwd_filter_static_scratch_bytes();
+  if (need > cap)
+    return fail(B200CP_ERR_UNSUPPORTED,
+                "b200cp_cp4_bwd_filter_noalloc: this shape needs %zu bytes of scratch, the built-in array holds %zu; "
+                "use b200cp_cp4_bwd_filter with a caller-provided workspace", need, cap);
+  Cp4BwdFilterArgs a{};
+  a.N = s->N; a.C = s->C; a.T = s->T; a.H = s->H; a.W = s->W; a.F = s->Y; a.pad = s->pad;
+  a.Rs = s->Rank;
+  a.X = X; a.dU = dU; a.K0 = K0; a.K1 = K1; a.KH = KH; a.KW = KW; a.dK = dK_packed;
+  for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
+    a.r0 = r0;
+    a.R = std::min(64u, s->Rank - r0);
+    if (int rc = cp4_bwd_filter_static_launch(a, static_cast<cudaStream_t>(stream))) return rc;
+  }
+  return B200CP_OK;
+}
+
 int b200cp_cp4_bwd_filter_full(const b200cp_tensor_shape* s, const float* X, const float* dU, float* dK,
                                void* stream) {
   if (int rc = check_shape(s, "b200cp_cp4_bwd_filter_full")) return rc;

@@ -72,6 +72,8 @@ struct Cp4BwdFilterArgs {
 };
 size_t cp4_bwd_filter_simt_workspace(const b200cp_tensor_shape& s);
 int cp4_bwd_filter_simt_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
+size_t cp4_bwd_filter_static_scratch_bytes();
+int cp4_bwd_filter_static_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
 int cp4_bwd_filter_full_launch(const b200cp_tensor_shape& s, const float* X, const float* dU, float* dK,
                                cudaStream_t st);
 int cp4_recompose_launch(const b200cp_tensor_shape& s, const float* K0, const float* K1, const float* KH,

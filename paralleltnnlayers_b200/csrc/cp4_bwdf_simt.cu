@@ -1,4 +1,6 @@
 // CP4 conv2d backward-filter (and the dense filter gradient / recomposition helpers) on CUDA cores.
+#include <mutex>
+
 #include "cp4_simt.cuh"
 
 namespace b200cp {
@@ -360,6 +362,41 @@ int cp4_bwd_filter_simt_launch(const Cp4BwdFilterArgs& a, cudaStream_t st) {
   if (a.F == 3) return dispatch_bwd_filter_rank<3, true>(a, di, st);
   if (a.F >= 1 && a.F <= 11 && (a.F & 1)) return dispatch_bwd_filter_rank<11, false>(a, di, st);
   return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: filter size %d is not odd and <= 11", a.F);
+}
+
+// ===========================================================================
+// backward-filter without any allocation: the per-CTA partial gradients go to a fixed array that
+// lives in the library's device image instead of a caller-provided workspace.
+// ===========================================================================
+namespace {
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;  // 8 MiB per device that loads the library
+}
+static __device__ __align__(256) float g_bwdf_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+size_t cp4_bwd_filter_static_scratch_bytes() { return kStaticScratchBytes; }
+
+// In host code `g_bwdf_static_scratch` is only a handle of the symbol, not a device address; the address on
+// the current device comes from cudaGetSymbolAddress, once per device (kept in a small table).
+int cp4_bwd_filter_static_launch(const Cp4BwdFilterArgs& a_in, cudaStream_t st) {
+  static std::mutex mu;
+  static float* table[64] = {nullptr};
+  int dev = 0;
+  B200CP_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200CP_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+  float* ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!table[dev]) {
+      void* p = nullptr;
+      B200CP_CUDA_OK(cudaGetSymbolAddress(&p, g_bwdf_static_scratch));
+      table[dev] = static_cast<float*>(p);
+    }
+    ptr = table[dev];
+  }
+  Cp4BwdFilterArgs a = a_in;
+  a.ws = ptr;
+  a.ws_bytes = kStaticScratchBytes;
+  return cp4_bwd_filter_simt_launch(a, st);
 }
 
 // ===========================================================================

@@ -21,7 +21,7 @@ def test_python_binding_covers_header(lib_built):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     hdr = re.sub(r"/\*.*?\*/", "", open(os.path.join(root, "include", "b200cp.h")).read(), flags=re.S)
     declared = set(re.findall(r"\b(b200cp_[a-z0-9_]+)\s*\(", hdr))
-    assert declared <= set(_lib.EXPORTS) | {"b200cp_cp4_step_noalloc"} or declared == set(_lib.EXPORTS)
+    assert declared == set(_lib.EXPORTS)
 
 
 def test_shape_struct_layout():
