@@ -162,7 +162,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc3x"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--watchdog", type=int, default=420, help="seconds after which a stuck run dumps its stacks and exits")
     args = ap.parse_args()
+    import faulthandler
+    faulthandler.dump_traceback_later(args.watchdog, exit=True)
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -320,9 +323,17 @@ def main():
     d2h = 4 * sum(a.numel() for a in hout)
     e2e = world * n * Ks / e2e_s
 
-    if rank != 0:
+    def leave():
+        # CUDA graphs that captured NCCL work keep the communicator busy and make destroy_process_group() wait for
+        # ever; all results are out, so leave without tearing NCCL down
+        sys.stdout.flush()
+        sys.stderr.flush()
         if dist is not None:
-            dist.destroy_process_group()
+            torch.cuda.synchronize()
+            os._exit(0)
+
+    if rank != 0:
+        leave()
         return
 
     # ---- roofline of the dominant kernel ---------------------------------------------------------
@@ -363,8 +374,7 @@ def main():
         "gpu_launches": launches, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    leave()
 
 
 if __name__ == "__main__":
