@@ -27,6 +27,10 @@ NVCC_FLAGS = [
 ]
 
 
+# extra nvcc flags for experiments, e.g. B200CP_NVCC_FLAGS="-DB200CP_TRACE" (forces nothing by itself: use --force)
+NVCC_FLAGS += os.environ.get("B200CP_NVCC_FLAGS", "").split()
+
+
 def _newest_header():
     hs = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
         glob.glob(os.path.join(ROOT, "include", "*.h"))

@@ -22,6 +22,8 @@ namespace b200cp {
 // Formulas: Cuda_kernels/cp4Conv2dBackwardFilter.cu:91-104,142-155,192-205,241-254.
 namespace {
 
+constexpr int kRedFloats = 8 * 64;  // block-reduction staging: 8 warps x 64 sums (>= 8 x 2F for F <= 11)
+
 struct GeomF {
   Geom g;      // Cin = C (X channels), Cout = T (dU channels)
   int F;       // filter size
@@ -76,16 +78,25 @@ __device__ __forceinline__ void pixel_reduce(const Geom& g, int OPXs, const floa
     const float* s[CG];
 #pragma unroll
     for (int j = 0; j < CG; ++j) s[j] = src_n + (size_t)min(c0 + j, nch - 1) * HW;
-    for (int p = lane; p < g.OPX; p += 32) {
-      const int po = pixoff[p];
-      float d[CG];
+    // eight pixel rows of the warp are fetched before any is used, so the loads overlap
+    for (int pb = 0; pb < g.OPX; pb += 32 * 8) {
+      float d[8][CG];
 #pragma unroll
-      for (int j = 0; j < CG; ++j) d[j] = po >= 0 ? __ldg(s[j] + po) : 0.f;
+      for (int it = 0; it < 8; ++it) {
+        const int p = pb + it * 32 + lane;
+        const int po = p < g.OPX ? pixoff[p] : -1;
 #pragma unroll
-      for (int r = 0; r < RP; ++r) {
-        const float z = Vs[r * OPXs + p];
+        for (int j = 0; j < CG; ++j) d[it][j] = po >= 0 ? __ldg(s[j] + po) : 0.f;
+      }
 #pragma unroll
-        for (int j = 0; j < CG; ++j) acc[j * RP + r] = fmaf(d[j], z, acc[j * RP + r]);
+      for (int it = 0; it < 8; ++it) {
+        const int p = min(pb + it * 32 + lane, g.OPX - 1);  // d is zero beyond the tile
+#pragma unroll
+        for (int r = 0; r < RP; ++r) {
+          const float z = Vs[r * OPXs + p];
+#pragma unroll
+          for (int j = 0; j < CG; ++j) acc[j * RP + r] = fmaf(d[it][j], z, acc[j * RP + r]);
+        }
       }
     }
     warp_transpose_reduce<M>(acc, lane);
@@ -99,6 +110,77 @@ __device__ __forceinline__ void pixel_reduce(const Geom& g, int OPXs, const floa
         if (c0 + cj < nch && r < g.R) part[(size_t)(c0 + cj) * g.R + r] = acc[j];
       }
     }
+  }
+}
+
+// 3x3 stencil phase: one pass over the thread's pixels per chunk of RC ranks; the dKH / dKW contributions stay in
+// registers and are reduced once per chunk (butterfly over the warp, then warps in a fixed order).
+template <int RP>
+__device__ __forceinline__ void stencil_phase_3x3(const GeomF& gf, const float* Ps, const float* Qs, float* Zs, float* Qts,
+                                                  const float* KHs, const float* KWs, const int* pixoff, float* red,
+                                                  float* part_KH, float* part_KW, int tid, int nt) {
+  const Geom& g = gf.g;
+  constexpr int RC = RP < 8 ? RP : 8;
+  constexpr int M = RC * 8;  // per rank: 3 row sums, 3 column sums, 2 unused (power-of-two butterfly)
+  const int lane = tid & 31, warp = tid >> 5, nwarp = nt >> 5;
+  const int p = g.pad;
+  for (int rc = 0; rc < RP; rc += RC) {
+    float acc[M];
+#pragma unroll
+    for (int i = 0; i < M; ++i) acc[i] = 0.f;
+    for (int op = tid; op < g.OPX; op += nt) {
+      const int oy = op / g.TW, ox = op - oy * g.TW;
+      const bool in = pixoff[op] >= 0;
+      const int wo = oy * g.TWh + ox;
+#pragma unroll
+      for (int rr = 0; rr < RC; ++rr) {
+        const int r = rc + rr;
+        float zv = 0.f, qt = 0.f;
+        if (in) {
+          const float* pw = Ps + r * g.HPXs + wo;
+          const float* qw = Qs + r * g.HPXs + wo;
+          float kh[3], kw[3], cols[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+          for (int i = 0; i < 3; ++i) {
+            kh[i] = KHs[i * RP + r];
+            kw[i] = KWs[i * RP + r];
+          }
+          const float q = qw[p * g.TWh + p];
+#pragma unroll
+          for (int i = 0; i < 3; ++i) {
+            float row = 0.f, qrow = 0.f;
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+              const float pv = pw[i * g.TWh + j];
+              row = fmaf(kw[j], pv, row);
+              cols[j] = fmaf(kh[i], pv, cols[j]);
+              qrow = fmaf(kw[j], qw[(2 * p - i) * g.TWh + (2 * p - j)], qrow);
+            }
+            zv = fmaf(kh[i], row, zv);
+            qt = fmaf(kh[i], qrow, qt);
+            acc[rr * 8 + i] = fmaf(q, row, acc[rr * 8 + i]);
+          }
+#pragma unroll
+          for (int j = 0; j < 3; ++j) acc[rr * 8 + 3 + j] = fmaf(q, cols[j], acc[rr * 8 + 3 + j]);
+        }
+        Zs[r * gf.OPXs + op] = zv;
+        Qts[r * gf.OPXs + op] = qt;
+      }
+    }
+    warp_transpose_reduce<M>(acc, lane);
+#pragma unroll
+    for (int j = 0; j < M / 32; ++j) red[warp * M + owner_index<M>(lane, j)] = acc[j];
+    __syncthreads();
+    if (tid < M) {
+      float sum = 0.f;
+      for (int w = 0; w < nwarp; ++w) sum += red[w * M + tid];
+      const int r = rc + tid / 8, k = tid & 7;
+      if (r < g.R && k < 6) {
+        if (k < 3) part_KH[(size_t)k * g.R + r] = sum;
+        else part_KW[(size_t)(k - 3) * g.R + r] = sum;
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -117,8 +199,8 @@ __global__ void __launch_bounds__(256) cp4_bwd_filter_kernel(const GeomF gf, con
   float* Fs = smem;                              // [cchunk][RP]
   float* KHs = Fs + g.fcap;                      // [F][RP]
   float* KWs = KHs + F * RP;                     // [F][RP]
-  float* red = KWs + F * RP;                     // [8 warps][2F]
-  float* Ps = red + 8 * 2 * F;                   // [RP][HPXs]
+  float* red = KWs + F * RP;                     // [8 warps][max(2F, 64)]
+  float* Ps = red + kRedFloats;                  // [RP][HPXs]
   float* Qs = Ps + RP * g.HPXs;                  // [RP][HPXs]
   float* Zs = Qs + RP * g.HPXs;                  // [RP][OPXs]
   float* Qts = Zs + RP * gf.OPXs;                // [RP][OPXs]
@@ -152,12 +234,25 @@ __global__ void __launch_bounds__(256) cp4_bwd_filter_kernel(const GeomF gf, con
     const int gy = h0 + oy, gx = w0 + ox;
     pixoff[p] = (gy < g.H && gx < g.W) ? gy * g.W + gx : -1;
   }
+#ifdef B200CP_TRACE
+  float* trace = (blockIdx.x == gridDim.x / 2 && tid == 0) ? partial + (size_t)gridDim.x * gf.nparam : nullptr;
+  const long long tr0 = clock64();
+#define TRACE(i) do { if (trace) trace[i] = (float)(clock64() - tr0); } while (0)
+#else
+#define TRACE(i) do {} while (0)
+#endif
+  TRACE(0);
   contract_tile<RP, PPT>(g, Xn, g.Cin, K1, Fs, Xst, Ps, h0, w0, tid, nt);
+  TRACE(1);
   contract_tile<RP, PPT>(g, dUn, g.Cout, K0, Fs, Xst, Qs, h0, w0, tid, nt);
   __syncthreads();
+  TRACE(2);
 
   // per-rank stencils and the small-factor gradients
   const int p = g.pad;
+  if (EXACT && FMAX == 3) {
+    stencil_phase_3x3<RP>(gf, Ps, Qs, Zs, Qts, KHs, KWs, pixoff, red, part_KH, part_KW, tid, nt);
+  } else
   for (int r = 0; r < g.R; ++r) {
     float kh[FMAX], kw[FMAX], aH[FMAX], aW[FMAX];
 #pragma unroll
@@ -236,9 +331,12 @@ __global__ void __launch_bounds__(256) cp4_bwd_filter_kernel(const GeomF gf, con
   }
   __syncthreads();
 
+  TRACE(3);
   constexpr int CG = (RP >= 64) ? 1 : (RP == 32 ? 2 : 4);
   pixel_reduce<RP, CG>(g, gf.OPXs, dUn, g.Cout, Zs, pixoff, part_K0, tid, nt);
+  TRACE(4);
   pixel_reduce<RP, CG>(g, gf.OPXs, Xn, g.Cin, Qts, pixoff, part_K1, tid, nt);
+  TRACE(5);
 }
 
 // out[j] = sum over CTAs of partial[cta][j].  32 parameters x 32 slices per block: slice s adds the
@@ -274,7 +372,7 @@ __global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* 
 TileChoice bwdf_tile(int N, int H, int W, int F, int pad, int C, int T, int RP, const DeviceInfo& di) {
   // halo pass over C + T channels, reductions over C + T channels (about 1.6x a contraction each), stencils
   const double w1 = (double)(C + T) * RP, w3 = 1.6 * (C + T) * RP + 6.0 * F * F * RP;
-  return choose_tile(N, H, W, F, F, pad, w1, w3, RP, factor_cap(std::max(C, T), RP), 2, 2, 2 * F * RP + 16 * F, 1, true,
+  return choose_tile(N, H, W, F, F, pad, w1, w3, RP, factor_cap(std::max(C, T), RP), 2, 2, 2 * F * RP + kRedFloats, 1, true,
                      di);
 }
 
@@ -289,7 +387,7 @@ int launch_bwd_filter(const Cp4BwdFilterArgs& a, const TileChoice& t, const Devi
   gf.F = F;
   gf.nparam = (a.T + a.C + 2 * F) * a.R;
   gf.OPXs = (int)align_up(gf.g.OPX, 4);
-  const size_t smem = sizeof(float) * ((size_t)gf.g.fcap + 2 * F * RP + 16 * F + 2 * (size_t)RP * gf.g.HPXs +
+  const size_t smem = sizeof(float) * ((size_t)gf.g.fcap + 2 * F * RP + kRedFloats + 2 * (size_t)RP * gf.g.HPXs +
                                        2 * (size_t)RP * gf.OPXs + gf.OPXs + (size_t)kStages * kKC * t.NT * PPT);
   if ((int)smem > di.smem_optin) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: tile exceeds shared memory");
   const long ctas = (long)a.N * gf.g.tilesH * gf.g.tilesW;

@@ -252,10 +252,23 @@ inline TileChoice choose_tile(int N, int H, int W, int Y, int X, int pad, double
   if (const char* e = getenv("B200CP_TILE")) {  // "TH,TW,NT": restrict the search (experiments)
     if (sscanf(e, "%d,%d,%d", &fTH, &fTW, &fNT) != 3) fTH = fTW = fNT = 0;
   }
-  const int tws[4] = {W, 64, 32, 16};
-  for (int twi = 0; twi < 4; ++twi) {
+  // candidate tile widths: the full width, powers of two, and the widths that divide W exactly (no ragged last column)
+  int tws[16];
+  int ntw = 0;
+  auto add_tw = [&](int v) {
+    if (v < 8 && v != W) return;
+    if (v > W || v > 128) return;
+    for (int i = 0; i < ntw; ++i)
+      if (tws[i] == v) return;
+    if (ntw < 16) tws[ntw++] = v;
+  };
+  add_tw(W);
+  add_tw(64); add_tw(32); add_tw(16);
+  for (int parts = 2; parts <= 8; ++parts)
+    if (W % parts == 0) add_tw(W / parts);
+  if (ntw == 0) tws[ntw++] = std::min(W, 64);
+  for (int twi = 0; twi < ntw; ++twi) {
     const int TW = tws[twi];
-    if (TW > W || (twi == 0 && W > 128) || (twi > 0 && TW >= W)) continue;
     if (fTW && std::min(fTW, W) != TW) continue;
     for (int TH = 1; TH <= std::min(H, 64); ++TH) {
       if (fTH && std::min(fTH, H) != TH) continue;
@@ -284,7 +297,9 @@ inline TileChoice choose_tile(int N, int H, int W, int Y, int X, int pad, double
         const double lat = warps >= 16 ? 1.0 : std::sqrt(16.0 / warps);
         // narrow per-thread work (small PPT) re-reads factors from smem more often per FMA
         const double ilp = 1.0 + 0.25 / p1;
-        const double cost = (double)per_sm * per_cta * NT * lat * ilp;
+        // measured on B200: small CTAs pay their factor staging, barriers and halo set-up per few pixels
+        const double small = 1.0 + 96.0 / NT;
+        const double cost = (double)per_sm * per_cta * NT * lat * ilp * small;
         if (cost < best.cost) { best.TH = TH; best.TW = TW; best.NT = NT; best.PPT1 = p1; best.PPT3 = p3; best.smem = sm; best.cost = cost; }
       }
     }
