@@ -321,6 +321,12 @@ int rcp_chain_launch(int N, int H, int W, int order, const int* cdims, const int
   if (FH < 1 || FW < 1 || FH > 31 || FW > 31 || !(FH & 1) || !(FW & 1))
     return fail(B200CP_ERR_UNSUPPORTED, "rcp: filter %dx%d must be odd and at most 31", FH, FW);
   if (N < 1 || H < 1 || W < 1) return fail(B200CP_ERR_INVALID_ARG, "rcp: non-positive N/H/W");
+  {
+    bool done = false;
+    if (int rc = rcp_fast_launch(N, H, W, order, g.din, g.dout, g.fsi, g.fso, R, FH, FW, X, A, S, V, transposed, st, &done))
+      return rc;
+    if (done) return B200CP_OK;
+  }
   g.conv = 1; g.N = N; g.H = H; g.W = W; g.FH = FH; g.FW = FW; g.flip = transposed ? 1 : 0;
   g.mH = (FH - 1) / 2; g.mW = (FW - 1) / 2;  // "same" padding per axis (test/test_conv2d_rcp.py:11)
   g.pad = g.mH;

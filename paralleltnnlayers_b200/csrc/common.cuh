@@ -92,6 +92,10 @@ int tc_selftest_launch(int mode, const float* A, const float* B, float* D, int* 
 int rcp_chain_launch(int N, int H, int W, int order, const int* cdims, const int* tdims, int R, int FH, int FW,
                      const float* X, const float* const* A, const float* S, float* V, bool transposed,
                      cudaStream_t st);
+// register-tiled kernel for the shapes it is compiled for; *done = false means "not this shape, use the chain kernel"
+int rcp_fast_launch(int N, int H, int W, int order, const int* din, const int* dout, const int* fsi, const int* fso,
+                    int R, int FH, int FW, const float* X, const float* const* A, const float* S, float* V, bool flip,
+                    cudaStream_t st, bool* done);
 int dense_chain_launch(int B, int order, const int* idims, const int* odims, int R, const float* X,
                        const float* const* F, float* Y, bool transposed, cudaStream_t st);
 // G[t][c][tap] = sum_{n,h,w} dV[n,t,h,w] * Xpad[n,c,h+y,w+x]

@@ -16,6 +16,7 @@ RCP_CASES = [
     (72, 1, (6,), (10,), 7, 7, 5, 3),
     (73, 2, (2, 2, 2, 2), (2, 3, 2, 2), 8, 8, 1, 6),
     (74, 2, (4, 8, 8), (4, 8, 8), 14, 14, 3, 16),  # BASELINE config 4 channels at a reduced image
+    (75, 1, (4, 8, 8), (4, 8, 8), 10, 12, 3, 5),   # same modes, tiles ragged in both directions
 ]
 
 
@@ -34,6 +35,25 @@ def test_rcp_forward_backward(case):
     for k, (a, b) in enumerate(zip(gA, rA)):
         check(a, b, f"rcp dA{k}", atol=1e-5 * max(1.0, float(np.abs(b).max())))
     check(gS, rS, "rcp dS", atol=1e-5 * max(1.0, float(np.abs(rS).max())))
+
+
+@pytest.mark.parametrize("tile", ["7", "8"])
+def test_rcp_register_tiled_kernel_tiles(tile, monkeypatch):
+    """Both tile sizes of the register-tiled order-3 kernel, forward and data gradient, against the chain kernel."""
+    import paralleltnnlayers_b200 as P
+    X, A, S, dV = O.make_rcp_inputs(76, 2, (4, 8, 8), (4, 8, 8), 17, 9, 3, 3, 3)
+    dX_, dS_, ddV = dev(X, S, dV)
+    dA_ = dev(*A)
+    monkeypatch.setenv("B200CP_RCP_TILE", tile)
+    V = P.conv2d_rcp_fused_nchw(dX_, *dA_, dS_)
+    gX, _, _ = P.rcp_conv2d_backward(dX_, ddV, *dA_, dS_, need_dw=False)
+    monkeypatch.delenv("B200CP_RCP_TILE")
+    monkeypatch.setenv("B200CP_NO_FAST", "1")
+    V0 = P.conv2d_rcp_fused_nchw(dX_, *dA_, dS_)
+    g0, _, _ = P.rcp_conv2d_backward(dX_, ddV, *dA_, dS_, need_dw=False)
+    check(V, O.rcp_forward(X, A, S), "rcp forward", atol=1e-4)
+    check(gX, O.rcp_backward(X, dV, A, S)[0], "rcp dX", atol=1e-4)
+    assert float((V - V0).abs().max()) < 1e-4 and float((gX - g0).abs().max()) < 1e-4
 
 
 def test_rcp_reference_op_layout():
