@@ -294,11 +294,14 @@ int b200cp_rcp_fwd(int N, int H, int W, int order, const int* cdims, const int* 
 
 size_t b200cp_rcp_bwd_workspace_bytes(int N, int H, int W, int order, const int* cdims, const int* tdims, int R,
                                       int FH, int FW, int flags) {
-  (void)N; (void)H; (void)W; (void)R; (void)flags;
+  (void)R; (void)flags;
   if (order < 1 || order > 4 || !cdims || !tdims || FH < 1 || FW < 1) return 0;
   size_t C = 1, T = 1;
   for (int k = 0; k < order; ++k) { C *= (size_t)cdims[k]; T *= (size_t)tdims[k]; }
-  return T * C * FH * FW * sizeof(float);
+  // G itself, then the split-K partial tiles of the GEMM that produces it
+  const size_t gemm = dense_grad_scratch_floats(N, (int)T, (int)C, H, W, FH, FW);
+  const size_t contr = contract_scratch_floats(order, cdims, tdims, R, FH * FW, true);
+  return (T * C * FH * FW + std::max(gemm, contr)) * sizeof(float);
 }
 
 int b200cp_rcp_bwd(int N, int H, int W, int order, const int* cdims, const int* tdims, int R, int FH, int FW,
@@ -321,8 +324,9 @@ int b200cp_rcp_bwd(int N, int H, int W, int order, const int* cdims, const int* 
     int C = 1, T = 1;
     for (int k = 0; k < order; ++k) { C *= cdims[k]; T *= tdims[k]; }
     float* G = static_cast<float*>(workspace);
-    if (int rc = dense_grad_launch(N, T, C, H, W, FH, FW, dV, X, G, st)) return rc;
-    if (int rc = contract_factors_launch(order, cdims, tdims, R, FH * FW, A, S, G, dA, dS, st)) return rc;
+    if (int rc = dense_grad_launch(N, T, C, H, W, FH, FW, dV, X, G, G + (size_t)T * C * FH * FW, st)) return rc;
+    if (int rc = contract_factors_launch(order, cdims, tdims, R, FH * FW, A, S, G, dA, dS, G + (size_t)T * C * FH * FW, st))
+      return rc;
   }
   return B200CP_OK;
 }
@@ -337,11 +341,13 @@ int b200cp_dense_fwd(int B, int order, const int* idims, const int* odims, int R
 }
 
 size_t b200cp_dense_bwd_workspace_bytes(int B, int order, const int* idims, const int* odims, int R, int flags) {
-  (void)B; (void)R; (void)flags;
+  (void)R; (void)flags;
   if (order < 1 || order > 4 || !idims || !odims) return 0;
   size_t I = 1, O = 1;
   for (int k = 0; k < order; ++k) { I *= (size_t)idims[k]; O *= (size_t)odims[k]; }
-  return I * O * sizeof(float);
+  const size_t gemm = dense_grad_scratch_floats(B, (int)O, (int)I, 1, 1, 1, 1);
+  const size_t contr = contract_scratch_floats(order, idims, odims, R, 1, false);
+  return (I * O + std::max(gemm, contr)) * sizeof(float);
 }
 
 int b200cp_dense_bwd(int B, int order, const int* idims, const int* odims, int R, const float* X, const float* dY,
@@ -364,8 +370,9 @@ int b200cp_dense_bwd(int B, int order, const int* idims, const int* odims, int R
     int I = 1, O = 1;
     for (int k = 0; k < order; ++k) { I *= idims[k]; O *= odims[k]; }
     float* G = static_cast<float*>(workspace);  // G[o][i] = sum_b dY[b,o] X[b,i]
-    if (int rc = dense_grad_launch(B, O, I, 1, 1, 1, 1, dY, X, G, st)) return rc;
-    if (int rc = contract_factors_launch(order, idims, odims, R, 1, F, nullptr, G, dF, nullptr, st)) return rc;
+    if (int rc = dense_grad_launch(B, O, I, 1, 1, 1, 1, dY, X, G, G + (size_t)I * O, st)) return rc;
+    if (int rc = contract_factors_launch(order, idims, odims, R, 1, F, nullptr, G, dF, nullptr, G + (size_t)I * O, st))
+      return rc;
   }
   return B200CP_OK;
 }

@@ -98,10 +98,13 @@ int rcp_fast_launch(int N, int H, int W, int order, const int* din, const int* d
                     cudaStream_t st, bool* done);
 int dense_chain_launch(int B, int order, const int* idims, const int* odims, int R, const float* X,
                        const float* const* F, float* Y, bool transposed, cudaStream_t st);
-// G[t][c][tap] = sum_{n,h,w} dV[n,t,h,w] * Xpad[n,c,h+y,w+x]
+// G[tap][t][c] = sum_{n,h,w} dV[n,t,h,w] * Xpad[n,c,h+y,w+x]; scratch holds dense_grad_scratch_floats() floats
+size_t dense_grad_scratch_floats(int N, int T, int C, int H, int W, int FH, int FW);
 int dense_grad_launch(int N, int T, int C, int H, int W, int FH, int FW, const float* dV, const float* X, float* G,
-                      cudaStream_t st);
+                      float* scratch, cudaStream_t st);
+size_t contract_scratch_floats(int order, const int* cdims, const int* tdims, int R, int taps, bool has_s);
 int contract_factors_launch(int order, const int* cdims, const int* tdims, int R, int taps, const float* const* A,
-                            const float* S, const float* G, float* const* dA, float* dS, cudaStream_t st);
+                            const float* S, const float* G, float* const* dA, float* dS, float* scratch,
+                            cudaStream_t st);
 
 }  // namespace b200cp
