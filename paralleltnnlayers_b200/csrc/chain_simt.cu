@@ -373,6 +373,11 @@ int dense_chain_launch(int B, int order, const int* idims, const int* odims, int
   ChainGeom g{};
   if (int rc = fill_modes(g, order, idims, odims, R, transposed, "dense_cp")) return rc;
   if (B < 1) return fail(B200CP_ERR_INVALID_ARG, "dense_cp: batch must be positive");
+  {
+    bool done = false;
+    if (int rc = dense_fast_launch(B, order, g.din, g.dout, g.fsi, g.fso, R, X, F, Y, st, &done)) return rc;
+    if (done) return B200CP_OK;
+  }
   g.conv = 0; g.B = B;
   const int Alast = g.Cout / g.dout[g.m - 1];
   int pix = 0;

@@ -96,6 +96,8 @@ int rcp_chain_launch(int N, int H, int W, int order, const int* cdims, const int
 int rcp_fast_launch(int N, int H, int W, int order, const int* din, const int* dout, const int* fsi, const int* fso,
                     int R, int FH, int FW, const float* X, const float* const* A, const float* S, float* V, bool flip,
                     cudaStream_t st, bool* done);
+int dense_fast_launch(int B, int order, const int* din, const int* dout, const int* fsi, const int* fso, int R,
+                      const float* X, const float* const* F, float* Y, cudaStream_t st, bool* done);
 int dense_chain_launch(int B, int order, const int* idims, const int* odims, int R, const float* X,
                        const float* const* F, float* Y, bool transposed, cudaStream_t st);
 // G[tap][t][c] = sum_{n,h,w} dV[n,t,h,w] * Xpad[n,c,h+y,w+x]; scratch holds dense_grad_scratch_floats() floats

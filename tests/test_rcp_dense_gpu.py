@@ -73,6 +73,7 @@ DENSE_CASES = [
     (81, 33, (8, 8), (4, 16), 7),
     (82, 7, (12,), (9,), 3),
     (83, 64, (8, 8, 8, 8), (8, 8, 8, 8), 4),       # BASELINE config 5 modes at reduced batch and rank
+    (84, 5, (8, 8, 8, 8), (8, 8, 8, 8), 3),        # same modes, odd batch (half-empty last CTA)
 ]
 
 
@@ -91,6 +92,20 @@ def test_dense_forward_backward(case):
     check(gX, rX, "dense dX", atol=1e-5 * max(1.0, float(np.abs(rX).max())))
     for k, (a, b) in enumerate(zip(gF, rF)):
         check(a, b, f"dense dF{k}", atol=1e-5 * max(1.0, float(np.abs(b).max())))
+
+
+def test_dense_register_tiled_kernel_matches_chain_kernel(monkeypatch):
+    import paralleltnnlayers_b200 as P
+    X, F, dY = O.make_dense_inputs(85, 9, (8, 8, 8, 8), (8, 8, 8, 8), 6)
+    dX_, ddY = dev(X, dY)
+    dF_ = dev(*F)
+    Y = P.dense_cp(dX_, *dF_)
+    gX, _ = P.dense_cp_backward(dX_, ddY, *dF_, need_dw=False)
+    monkeypatch.setenv("B200CP_NO_FAST", "1")
+    Y0 = P.dense_cp(dX_, *dF_)
+    g0, _ = P.dense_cp_backward(dX_, ddY, *dF_, need_dw=False)
+    scale = float(Y0.abs().max())
+    assert float((Y - Y0).abs().max()) < 1e-5 * scale and float((gX - g0).abs().max()) < 1e-5 * float(g0.abs().max())
 
 
 def test_dense_reference_op_layout():
