@@ -114,6 +114,17 @@ int b200cp_cp4_step_host(const b200cp_tensor_shape* s, const float* X, const flo
                          const float* K1, const float* KH, const float* KW, float* U, float* dX, float* dK_packed,
                          int flags);
 
+/* The same step, queued: `submit` returns once the copies and kernels of one step are on the library's
+ * copy-in, compute and copy-out streams; `wait` blocks until that slot's results are in U / dX / dK_packed.
+ * Two slots (0 and 1) with their own device buffers let a caller submit step i+1 while step i drains, so the
+ * host-to-device copy of one step, the kernels of another and the device-to-host copy of a third overlap.
+ * Host buffers should be pinned and must stay untouched until `wait` returns.  Submitting to a slot that is
+ * still pending waits for it first.  No counterpart in the reference (its launchers synchronise the device). */
+int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                                const float* K1, const float* KH, const float* KW, float* U, float* dX,
+                                float* dK_packed, int flags, int slot);
+int b200cp_cp4_step_host_wait(int slot);
+
 /* ---- reshaped-CP (rCP) conv2d, order m (1..4) ------------------------- */
 
 /* V[n,t,h,w] = sum_r sum_{i,j} S[i,j,r] sum_c (prod_k A_k[c_k,t_k,r]) X[n,c,h+i-p,w+j-p],

@@ -47,6 +47,8 @@ def _load():
         "b200cp_cp4_recompose": (i, [sp, fp, fp, fp, fp, fp, vp]),
         "b200cp_cp4_fwd_host": (i, [sp, fp, fp, fp, fp, fp, fp, i]),
         "b200cp_cp4_step_host": (i, [sp, fp, fp, fp, fp, fp, fp, fp, fp, fp, i]),
+        "b200cp_cp4_step_host_submit": (i, [sp, fp, fp, fp, fp, fp, fp, fp, fp, fp, i, i]),
+        "b200cp_cp4_step_host_wait": (i, [i]),
         "b200cp_rcp_fwd": (i, [i, i, i, i, ip, ip, i, i, i, fp, pp, fp, fp, vp, i]),
         "b200cp_rcp_bwd_workspace_bytes": (sz, [i, i, i, i, ip, ip, i, i, i, i]),
         "b200cp_rcp_bwd": (i, [i, i, i, i, ip, ip, i, i, i, fp, fp, pp, fp, fp, pp, fp, vp, sz, vp, i]),

@@ -105,7 +105,11 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
 struct HostCtx {
   std::vector<void*> bufs;
   std::vector<size_t> sizes;
-  cudaStream_t stream = nullptr;
+  // copy-in, compute and copy-out streams: the two copy directions and the kernels overlap
+  cudaStream_t s_in = nullptr, s_cmp = nullptr, s_out = nullptr;
+  // per slot: X and factors in, dU in, forward / backward-data / backward-filter done, results out
+  cudaEvent_t ev[2][6] = {};
+  bool pending[2] = {false, false};
 };
 std::mutex g_host_mu;
 HostCtx g_host_ctx[64];
@@ -217,55 +221,115 @@ int b200cp_cp4_recompose(const b200cp_tensor_shape* s, const float* K0, const fl
   return cp4_recompose_launch(*s, K0, K1, KH, KW, K, static_cast<cudaStream_t>(stream));
 }
 
-int b200cp_cp4_step_host(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
-                         const float* K1, const float* KH, const float* KW, float* U, float* dX, float* dK_packed,
-                         int flags) {
-  if (int rc = check_shape(s, "b200cp_cp4_step_host")) return rc;
-  if (int rc = check_ptrs("b200cp_cp4_step_host", {X, K0, K1, KH, KW})) return rc;
+static int host_ctx_ready(HostCtx& c) {
+  if (c.s_in) return B200CP_OK;
+  B200CP_CUDA_OK(cudaStreamCreateWithFlags(&c.s_in, cudaStreamNonBlocking));
+  B200CP_CUDA_OK(cudaStreamCreateWithFlags(&c.s_cmp, cudaStreamNonBlocking));
+  B200CP_CUDA_OK(cudaStreamCreateWithFlags(&c.s_out, cudaStreamNonBlocking));
+  for (int sl = 0; sl < 2; ++sl)
+    for (int e = 0; e < 6; ++e) B200CP_CUDA_OK(cudaEventCreateWithFlags(&c.ev[sl][e], cudaEventDisableTiming));
+  return B200CP_OK;
+}
+
+int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                                const float* K1, const float* KH, const float* KW, float* U, float* dX,
+                                float* dK_packed, int flags, int slot) {
+  if (int rc = check_shape(s, "b200cp_cp4_step_host_submit")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_step_host_submit", {X, K0, K1, KH, KW})) return rc;
+  if (slot < 0 || slot > 1) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_submit: slot must be 0 or 1");
   const bool bwd = dU != nullptr;
-  if (!U && !bwd) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host: nothing to compute");
-  if (bwd && (!dX || !dK_packed)) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host: dX and dK_packed required with dU");
+  if (!U && !bwd) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_submit: nothing to compute");
+  if (bwd && (!dX || !dK_packed))
+    return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_submit: dX and dK_packed required with dU");
   int dev = 0;
   B200CP_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(B200CP_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
   std::lock_guard<std::mutex> lk(g_host_mu);
   HostCtx& c = g_host_ctx[dev];
-  if (!c.stream) B200CP_CUDA_OK(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  if (int rc = host_ctx_ready(c)) return rc;
+  if (c.pending[slot]) {  // the slot's buffers are still in use by its previous submission
+    B200CP_CUDA_OK(cudaEventSynchronize(c.ev[slot][5]));
+    c.pending[slot] = false;
+  }
   const size_t HW = (size_t)s->H * s->W, R = s->Rank;
   const size_t nX = (size_t)s->N * s->C * HW, nU = (size_t)s->N * s->T * HW;
   const size_t nK0 = s->T * R, nK1 = s->C * R, nKH = s->Y * R, nKW = s->X * R, nK = nK0 + nK1 + nKH + nKW;
   float *dXin, *dUout, *dF, *ddU = nullptr, *ddX = nullptr, *ddK = nullptr, *ws = nullptr;
-  if (int rc = host_buffer(c, 0, nX * 4, &dXin)) return rc;
-  if (int rc = host_buffer(c, 1, nU * 4, &dUout)) return rc;
-  if (int rc = host_buffer(c, 2, nK * 4, &dF)) return rc;
+  const size_t b0 = (size_t)slot * 8;
   size_t wsb = 0;
-  if (bwd) {
-    wsb = b200cp_cp4_bwd_filter_workspace_bytes(s, flags);
-    if (int rc = host_buffer(c, 3, nU * 4, &ddU)) return rc;
-    if (int rc = host_buffer(c, 4, nX * 4, &ddX)) return rc;
-    if (int rc = host_buffer(c, 5, nK * 4, &ddK)) return rc;
-    if (int rc = host_buffer(c, 6, wsb, &ws)) return rc;
+  if (bwd) wsb = b200cp_cp4_bwd_filter_workspace_bytes(s, flags);
+  // a (re)allocation frees a buffer the other slot's queued work may still use: drain first
+  {
+    const size_t want[7] = {nX * 4, nU * 4, nK * 4, bwd ? nU * 4 : 0, bwd ? nX * 4 : 0, bwd ? nK * 4 : 0, 0};
+    bool grow = c.bufs.size() <= 16 || c.sizes[16] < wsb;
+    for (int k = 0; k < 7 && !grow; ++k) grow = c.sizes[b0 + k] < want[k];
+    if (grow && c.pending[slot ^ 1]) {
+      B200CP_CUDA_OK(cudaEventSynchronize(c.ev[slot ^ 1][5]));
+      c.pending[slot ^ 1] = false;
+    }
   }
-  cudaStream_t st = c.stream;
+  if (int rc = host_buffer(c, b0 + 0, nX * 4, &dXin)) return rc;
+  if (int rc = host_buffer(c, b0 + 1, nU * 4, &dUout)) return rc;
+  if (int rc = host_buffer(c, b0 + 2, nK * 4, &dF)) return rc;
+  if (bwd) {
+    if (int rc = host_buffer(c, b0 + 3, nU * 4, &ddU)) return rc;
+    if (int rc = host_buffer(c, b0 + 4, nX * 4, &ddX)) return rc;
+    if (int rc = host_buffer(c, b0 + 5, nK * 4, &ddK)) return rc;
+    if (int rc = host_buffer(c, 16, wsb, &ws)) return rc;  // one workspace: the compute stream is serial
+  }
+  cudaEvent_t* ev = c.ev[slot];
   float *dK0 = dF, *dK1 = dK0 + nK0, *dKH = dK1 + nK1, *dKW = dKH + nKH;
-  B200CP_CUDA_OK(cudaMemcpyAsync(dXin, X, nX * 4, cudaMemcpyHostToDevice, st));
-  B200CP_CUDA_OK(cudaMemcpyAsync(dK0, K0, nK0 * 4, cudaMemcpyHostToDevice, st));
-  B200CP_CUDA_OK(cudaMemcpyAsync(dK1, K1, nK1 * 4, cudaMemcpyHostToDevice, st));
-  B200CP_CUDA_OK(cudaMemcpyAsync(dKH, KH, nKH * 4, cudaMemcpyHostToDevice, st));
-  B200CP_CUDA_OK(cudaMemcpyAsync(dKW, KW, nKW * 4, cudaMemcpyHostToDevice, st));
-  if (bwd) B200CP_CUDA_OK(cudaMemcpyAsync(ddU, dU, nU * 4, cudaMemcpyHostToDevice, st));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dXin, X, nX * 4, cudaMemcpyHostToDevice, c.s_in));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dK0, K0, nK0 * 4, cudaMemcpyHostToDevice, c.s_in));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dK1, K1, nK1 * 4, cudaMemcpyHostToDevice, c.s_in));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dKH, KH, nKH * 4, cudaMemcpyHostToDevice, c.s_in));
+  B200CP_CUDA_OK(cudaMemcpyAsync(dKW, KW, nKW * 4, cudaMemcpyHostToDevice, c.s_in));
+  B200CP_CUDA_OK(cudaEventRecord(ev[0], c.s_in));
+  if (bwd) {
+    B200CP_CUDA_OK(cudaMemcpyAsync(ddU, dU, nU * 4, cudaMemcpyHostToDevice, c.s_in));
+    B200CP_CUDA_OK(cudaEventRecord(ev[1], c.s_in));
+  }
+  B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_cmp, ev[0], 0));
   if (U) {
-    if (int rc = b200cp_cp4_fwd(s, dXin, dK0, dK1, dKH, dKW, dUout, st, flags)) return rc;
-    B200CP_CUDA_OK(cudaMemcpyAsync(U, dUout, nU * 4, cudaMemcpyDeviceToHost, st));
+    if (int rc = b200cp_cp4_fwd(s, dXin, dK0, dK1, dKH, dKW, dUout, c.s_cmp, flags)) return rc;
+    B200CP_CUDA_OK(cudaEventRecord(ev[2], c.s_cmp));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_out, ev[2], 0));
+    B200CP_CUDA_OK(cudaMemcpyAsync(U, dUout, nU * 4, cudaMemcpyDeviceToHost, c.s_out));
   }
   if (bwd) {
-    if (int rc = b200cp_cp4_bwd_data(s, ddU, dK0, dK1, dKH, dKW, ddX, st, flags)) return rc;
-    B200CP_CUDA_OK(cudaMemcpyAsync(dX, ddX, nX * 4, cudaMemcpyDeviceToHost, st));
-    if (int rc = b200cp_cp4_bwd_filter(s, dXin, ddU, dK0, dK1, dKH, dKW, ddK, ws, wsb, st, flags)) return rc;
-    B200CP_CUDA_OK(cudaMemcpyAsync(dK_packed, ddK, nK * 4, cudaMemcpyDeviceToHost, st));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_cmp, ev[1], 0));
+    if (int rc = b200cp_cp4_bwd_data(s, ddU, dK0, dK1, dKH, dKW, ddX, c.s_cmp, flags)) return rc;
+    B200CP_CUDA_OK(cudaEventRecord(ev[3], c.s_cmp));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_out, ev[3], 0));
+    B200CP_CUDA_OK(cudaMemcpyAsync(dX, ddX, nX * 4, cudaMemcpyDeviceToHost, c.s_out));
+    if (int rc = b200cp_cp4_bwd_filter(s, dXin, ddU, dK0, dK1, dKH, dKW, ddK, ws, wsb, c.s_cmp, flags)) return rc;
+    B200CP_CUDA_OK(cudaEventRecord(ev[4], c.s_cmp));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_out, ev[4], 0));
+    B200CP_CUDA_OK(cudaMemcpyAsync(dK_packed, ddK, nK * 4, cudaMemcpyDeviceToHost, c.s_out));
   }
-  B200CP_CUDA_OK(cudaStreamSynchronize(st));
+  B200CP_CUDA_OK(cudaEventRecord(ev[5], c.s_out));
+  c.pending[slot] = true;
   return B200CP_OK;
+}
+
+int b200cp_cp4_step_host_wait(int slot) {
+  if (slot < 0 || slot > 1) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_wait: slot must be 0 or 1");
+  int dev = 0;
+  B200CP_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200CP_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_host_mu);
+  HostCtx& c = g_host_ctx[dev];
+  if (!c.s_in || !c.pending[slot]) return B200CP_OK;
+  B200CP_CUDA_OK(cudaEventSynchronize(c.ev[slot][5]));
+  c.pending[slot] = false;
+  return B200CP_OK;
+}
+
+int b200cp_cp4_step_host(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                         const float* K1, const float* KH, const float* KW, float* U, float* dX, float* dK_packed,
+                         int flags) {
+  if (int rc = b200cp_cp4_step_host_submit(s, X, dU, K0, K1, KH, KW, U, dX, dK_packed, flags, 0)) return rc;
+  return b200cp_cp4_step_host_wait(0);
 }
 
 int b200cp_cp4_fwd_host(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,

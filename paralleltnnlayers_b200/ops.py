@@ -135,6 +135,28 @@ def cp4_conv2d_step_host(X, dU, FT, FC, FY, FX, pad=1, flags=0, out=None):
     return U, dX, dK
 
 
+def cp4_conv2d_step_host_submit(X, dU, FT, FC, FY, FX, out, pad=1, flags=0, slot=0):
+    """Queue one step on ``slot`` (0 or 1) through ``b200cp_cp4_step_host_submit``; ``out`` holds the pinned
+    ``(U, dX, dK_packed)`` that ``cp4_conv2d_step_host_wait(slot)`` fills.  Inputs and outputs must stay
+    alive and untouched until that wait returns."""
+    ts = [X, dU, FT, FC, FY, FX] + list(out)
+    for t in ts:
+        if t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+            raise TypeError("host entry point takes contiguous float32 CPU tensors")
+    s = tensor_shape(X.shape[0], FC.shape[0], X.shape[2], X.shape[3], FT.shape[0], FY.shape[0], FX.shape[0],
+                     FT.shape[1], pad)
+    U, dX, dK = out
+    if U.numel() != s.N * s.T * s.H * s.W or dX.numel() != X.numel() or dK.numel() != (s.T + s.C + s.Y + s.X) * s.Rank:
+        raise ValueError("out must be (U [N,T,H,W], dX [N,C,H,W], dK_packed [(T+C+Y+X)*R])")
+    check(lib.b200cp_cp4_step_host_submit(C.byref(s), _p(X), _p(dU), _p(FT), _p(FC), _p(FY), _p(FX), _p(U), _p(dX),
+                                          _p(dK), flags, slot))
+
+
+def cp4_conv2d_step_host_wait(slot=0):
+    """Block until the step queued on ``slot`` has its results in the host tensors."""
+    check(lib.b200cp_cp4_step_host_wait(slot))
+
+
 def device_status():
     """Synchronise and raise if a tensor-path kernel gave up a bounded wait (``b200cp_device_status``)."""
     check(lib.b200cp_device_status())

@@ -125,6 +125,27 @@ def test_host_entry_point():
     check(dK, ref, "host dK", atol=1e-4)
 
 
+def test_host_entry_point_two_slots_in_flight():
+    """Three different steps queued on alternating slots; every result must belong to its own inputs."""
+    import paralleltnnlayers_b200 as P
+    cases = [_inputs((64 + k, 3, 8, 6, 12, 12, 3, 4, 1, 0.3)) for k in range(3)]
+    pins, outs = [], []
+    for (X, K0, K1, KH, KW, dU), pad in cases:
+        pins.append([torch.from_numpy(a).pin_memory() for a in (X, dU, K0, K1, KH, KW)])
+        outs.append((torch.empty(X.shape[0], K0.shape[0], 12, 12).pin_memory(), torch.empty(X.shape).pin_memory(),
+                     torch.empty((K0.shape[0] + K1.shape[0] + 6) * 4).pin_memory()))
+    for k in range(3):
+        P.cp4_conv2d_step_host_submit(*pins[k], outs[k], pad=1, slot=k % 2)
+        if k >= 1:
+            P.cp4_conv2d_step_host_wait((k - 1) % 2)
+    P.cp4_conv2d_step_host_wait(0)
+    for ((X, K0, K1, KH, KW, dU), pad), (U, dX, dK) in zip(cases, outs):
+        check(U, O.cp4_forward(X, K0, K1, KH, KW, pad), "queued fwd")
+        check(dX, O.cp4_backward_data(dU, K0, K1, KH, KW, pad), "queued bwd-data")
+        ref = np.concatenate([a.ravel() for a in O.cp4_backward_filter(X, dU, K0, K1, KH, KW, pad)])
+        check(dK, ref, "queued dK", atol=1e-4)
+
+
 def test_errors_are_status_codes():
     import paralleltnnlayers_b200 as P
     x = torch.zeros(1, 4, 8, 8, device="cuda")
