@@ -160,7 +160,7 @@ def main():
     ap.add_argument("--steps", type=int, default=60)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc3x"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc3x", "mma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--watchdog", type=int, default=420, help="seconds after which a stuck run dumps its stacks and exits")
     args = ap.parse_args()
@@ -183,7 +183,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    flags = {"auto": P.PATH_AUTO, "simt": P.PATH_SIMT, "tc3x": P.PATH_TC3X}[args.path]
+    flags = {"auto": P.PATH_AUTO, "simt": P.PATH_SIMT, "tc3x": P.PATH_TC3X, "mma": P.PATH_MMA}[args.path]
     flags_f = P.PATH_AUTO if flags == P.PATH_TC3X else flags   # the factor-gradient kernel has no forced tensor path
 
     c = CFG

@@ -44,10 +44,11 @@ typedef enum b200cp_status {
 
 /* flags: which arithmetic path runs the two channel contractions. */
 enum {
-  B200CP_PATH_AUTO = 0,   /* tensor path where the shape allows it, else SIMT */
+  B200CP_PATH_AUTO = 0,   /* the fastest fp32-grade path for the shape (mma.sync today)  */
   B200CP_PATH_SIMT = 1,   /* exact fp32 FFMA                                        */
   B200CP_PATH_TC3X = 2,   /* tcgen05 kind::tf32, 3-term split (fp32-grade accuracy) */
   B200CP_PATH_TC1X = 3,   /* tcgen05 kind::tf32, single pass (about 1e-3 relative)  */
+  B200CP_PATH_MMA = 4,    /* warp-level mma.sync tf32, 3-term split (fp32-grade)    */
   B200CP_PATH_MASK = 7
 };
 

@@ -9,7 +9,7 @@ library raises at that point -- there is no fallback implementation.
 """
 import importlib
 
-_LIB_NAMES = ("B200CPError", "LIB_PATH", "PATH_AUTO", "PATH_SIMT", "PATH_TC1X", "PATH_TC3X", "TensorShape",
+_LIB_NAMES = ("B200CPError", "LIB_PATH", "PATH_AUTO", "PATH_MMA", "PATH_SIMT", "PATH_TC1X", "PATH_TC3X", "TensorShape",
               "launch_count")
 _OPS_NAMES = ("CP4Conv2dFunction", "CPDenseFunction", "RCPConv2dFunction", "conv2d_rcp_fused_nchw",
               "cp4_conv2d_backward_data", "cp4_conv2d_backward_filter", "cp4_conv2d_backward_filter_full",

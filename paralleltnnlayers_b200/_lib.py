@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200cp.so")
 
 # flags (include/b200cp.h)
-PATH_AUTO, PATH_SIMT, PATH_TC3X, PATH_TC1X = 0, 1, 2, 3
+PATH_AUTO, PATH_SIMT, PATH_TC3X, PATH_TC1X, PATH_MMA = 0, 1, 2, 3, 4
 
 
 class TensorShape(C.Structure):

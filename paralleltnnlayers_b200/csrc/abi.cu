@@ -67,9 +67,15 @@ int check_ptrs(const char* who, std::initializer_list<const void*> ps) {
 
 int path_of(int flags) { return flags & B200CP_PATH_MASK; }
 
-// B200CP_PATH_AUTO takes the tensor path where the shape allows it (B200CP_AUTO_TC=0 turns that off)
+// B200CP_PATH_AUTO takes the warp-level tensor path (mma.sync): at every measured size it is at least as fast as the
+// tcgen05 path, which needs larger tiles than these layers offer per SM.  B200CP_AUTO_TC=1 prefers tcgen05 where
+// the shape allows it; B200CP_AUTO_MMA=0 falls back to the CUDA-core kernels.
 const bool g_auto_tc = [] {
   const char* e = getenv("B200CP_AUTO_TC");
+  return e && e[0] == '1';
+}();
+const bool g_auto_mma = [] {
+  const char* e = getenv("B200CP_AUTO_MMA");
   return !(e && e[0] == '0');
 }();
 
@@ -96,7 +102,8 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);
     a.accumulate = r0 > 0;
-    if (int rc = cp4_simt_launch(a, st)) return rc;
+    const bool mma = path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma);
+    if (int rc = (mma ? cp4_mma_launch(a, st) : cp4_simt_launch(a, st))) return rc;
   }
   return B200CP_OK;
 }

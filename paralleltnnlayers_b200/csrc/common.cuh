@@ -61,6 +61,8 @@ struct Cp4Args {
   float* out;
 };
 int cp4_simt_launch(const Cp4Args& a, cudaStream_t st);
+// same arguments; channel contractions on the warp-level tensor path (mma.sync, three tf32 terms)
+int cp4_mma_launch(const Cp4Args& a, cudaStream_t st);
 
 struct Cp4BwdFilterArgs {
   int N, C, T, H, W, F, pad;

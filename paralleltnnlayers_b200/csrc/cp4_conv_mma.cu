@@ -1,0 +1,514 @@
+// CP4 conv2d forward and backward-data with warp-level tensor-core contractions (mma.sync, tf32 in three
+// terms, fp32 accumulation: fp32-grade results).
+//
+// One CTA of 8 warps owns a TH x TW tile of output pixels of one image; the rank-R intermediate never
+// leaves the SM:
+//   phase 1  P[r, halo px] = sum_c Fin[c, r] * in[n, c, halo px]
+//            GEMM with M = pixels (16 per mma), K = channels (8 per mma), N = ranks (8 per mma).  Each warp
+//            owns some 16-pixel blocks of the halo tile and streams its own pixels of every channel through a
+//            warp-private cp.async FIFO in shared memory (8 channels per group), so no CTA barrier is
+//            needed in the channel loop; factors sit in shared memory already split into tf32 hi / lo.
+//   phase 2  Z[r, px] = sum_{y,x} KH[y,r] KW[x,r] P[r, px + (y,x)]       (CUDA cores, weights in registers)
+//   phase 3  out[n, t, px] = sum_r Fout[t, r] * Z[r, px]
+//            GEMM with M = pixels, K = ranks, N = output channels; results go straight to global memory.
+// Every product x*f is computed as hi(x)*hi(f) + lo(x)*hi(f) + hi(x)*lo(f) with hi = the value rounded to
+// tf32 and lo = the remainder, which keeps the error near 2^-21 relative.
+// Forward uses Fin = K1, Fout = K0; backward-data swaps them and flips the taps
+// (formulas: Cuda_kernels/cp4Conv2dForward.cu:84-133, cp4Conv2dBackwardData.cu:57-108).
+#include <algorithm>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "mma_util.cuh"
+
+namespace b200cp {
+
+namespace {
+
+using namespace mma;
+
+constexpr int kNT = 256, kWarps = 8;
+constexpr int kGC = 8;       // channels per cp.async group = one mma k-step
+constexpr int kFifo = 3;     // cp.async groups per warp (one being consumed)
+constexpr int kFChunk = 128; // channels of factor planes staged at a time
+
+struct MmaGeom {
+  int N, Cin, Cout, H, W, Y, X, pad, R, Rs, r0, flip, accumulate;
+  int TH, TW, THh, TWh, HPX, OPX, tilesH, tilesW;
+  int MB1, MBW1, MB3, MBW3;   // 16-pixel blocks of the halo / output tile, and blocks per warp
+  int xpitch;                 // FIFO row pitch (floats), = 8 mod 32
+  int ppitch;                 // P row pitch  (floats)
+  int zpitch;                 // Z row pitch, = 8 mod 32
+  int fch;                    // channels of factor planes staged at a time (multiple of 8, <= kFChunk)
+  int early_fout;             // 1: all channels fit one chunk and the output-side planes have their own space,
+                              //    so both factor sets are staged at the start, behind the first pixel copies
+};
+
+inline int pitch_mod32(int n, int want) {  // smallest p >= n with p % 32 == want
+  int p = n;
+  while (p % 32 != want) ++p;
+  return p;
+}
+
+// row pitches of the factor planes, chosen so that the B-fragment loads of a warp hit 32 different banks
+template <int RP>
+struct Planes {
+  static constexpr int FIN = RP == 8 ? 24 : RP + 8;  // phase-1 B element (k = c, n = r) at [c][r]: 4 rows x 8 ranks
+  static constexpr int FOUT = RP + 4;                // phase-3 B element (k = r, n = t) at [t][r]: 8 rows x 4 ranks
+};
+
+template <int RP>
+size_t mma_smem_floats(const MmaGeom& g) {
+  const size_t fifo = (size_t)kFifo * kGC * (kWarps * g.MBW1 * 16 + 8);
+  const size_t P = (size_t)RP * g.ppitch;
+  const size_t Z = (size_t)RP * (kWarps * g.MBW3 * 16 + 8);   // lives in the FIFO's space once phase 1 is over
+  const size_t planes = 2 * (size_t)g.fch * Planes<RP>::FIN;  // FIN >= FOUT
+  const size_t planes_out = g.early_fout ? 2 * (size_t)g.fch * Planes<RP>::FOUT : 0;
+  const size_t W = (size_t)g.Y * g.X * RP;
+  return std::max(fifo, Z) + P + planes + planes_out + W;
+}
+
+template <int RP, int FS, int MBW1, int MBW3>
+__global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv_mma_kernel(const MmaGeom g, const float* __restrict__ in,
+                                                             const float* __restrict__ Fin,
+                                                             const float* __restrict__ Fout,
+                                                             const float* __restrict__ KH,
+                                                             const float* __restrict__ KW, float* __restrict__ out) {
+  constexpr int NB = RP / 8;                    // rank blocks (n of phase 1, k of phase 3)
+  constexpr int XP = kWarps * MBW1 * 16 + 8;    // FIFO row pitch:  8 mod 32
+  constexpr int ZP = kWarps * MBW3 * 16 + 8;    // Z row pitch:     8 mod 32
+  constexpr int FIN = Planes<RP>::FIN, FOUT = Planes<RP>::FOUT;
+  static_assert(FIN >= FOUT, "the output-side planes reuse the input-side planes' space");
+  const int kFin = g.fch * FIN, kFout = g.fch * FOUT;   // floats per plane
+  const int PP = g.ppitch;                      // P row pitch:     1 mod 32
+  extern __shared__ __align__(16) float smem[];
+  float* Xf = smem;                             // [kFifo][kGC][XP]
+  float* Zs = smem;                             // [RP][ZP]: phase 2 and 3 only, over the FIFO
+  constexpr int kXZ = kFifo * kGC * XP > RP * ZP ? kFifo * kGC * XP : RP * ZP;
+  float* Ps = smem + kXZ;                       // [RP][PP]
+  float* Fh = Ps + (size_t)RP * PP;             // input-side factor planes hi | lo
+  float* Fo = g.early_fout ? Fh + 2 * kFin : Fh;  // output-side planes: own space, or the input side's after phase 1
+  float* Ws = Fo + 2 * (g.early_fout ? kFout : kFin);  // [Y*X][RP]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, tq = lane & 3;      // mma "groupID" and "threadID in group"
+
+  int b = blockIdx.x;
+  const int tw = b % g.tilesW;
+  b /= g.tilesW;
+  const int th = b % g.tilesH;
+  const int n = b / g.tilesH;
+  const int h0 = th * g.TH, w0 = tw * g.TW;
+  const size_t HW = (size_t)g.H * g.W;
+  const float* in_n = in + (size_t)n * g.Cin * HW;
+
+  // stencil weights (phase 2)
+  for (int i = tid; i < g.Y * g.X * RP; i += kNT) {
+    const int r = i % RP, yx = i / RP, y = yx / g.X, x = yx - y * g.X;
+    const int yy = g.flip ? g.Y - 1 - y : y, xx = g.flip ? g.X - 1 - x : x;
+    Ws[i] = r < g.R ? __ldg(KH + (size_t)yy * g.Rs + g.r0 + r) * __ldg(KW + (size_t)xx * g.Rs + g.r0 + r) : 0.f;
+  }
+
+  auto stage_fout = [&](int t0) {
+    const int tc = min(g.fch, g.Cout - t0);
+    const int tcp = (tc + 7) / 8 * 8;
+    for (int i = tid; i < tcp * RP; i += kNT) {
+      const int t = i / RP, r = i % RP;
+      const float v = (r < g.R && t < tc) ? __ldg(Fout + (size_t)(t0 + t) * g.Rs + g.r0 + r) : 0.f;
+      const float hi = tf32_round(v);
+      Fo[t * FOUT + r] = hi;
+      Fo[kFout + t * FOUT + r] = tf32_round(v - hi);
+    }
+  };
+
+  // ---------------- phase 1 ----------------
+  // warp-private columns: block j of this warp is halo block (j*kWarps + warp); column = warp*MBW1*16 + j*16 + i
+  constexpr int WCOLS = MBW1 * 16;          // columns per warp
+  constexpr int CPL = (WCOLS + 31) / 32;    // columns copied per lane
+  const float* gp[CPL];                     // this lane's pixel of channel 0 (any valid address when masked)
+  int gsz[CPL];                             // cp.async source size: 4, or 0 = zero fill
+#pragma unroll
+  for (int q = 0; q < CPL; ++q) {
+    const int wc = lane + 32 * q;           // column within the warp's range
+    const int jb = wc >> 4, i = wc & 15;
+    const int hp = (jb * kWarps + warp) * 16 + i;
+    const int hy = hp / g.TWh, hx = hp - hy * g.TWh;
+    const int gy = h0 - g.pad + hy, gx = w0 - g.pad + hx;
+    const bool ok = wc < WCOLS && hp < g.HPX && gy >= 0 && gy < g.H && gx >= 0 && gx < g.W;
+    gp[q] = in_n + (ok ? gy * g.W + gx : 0);
+    gsz[q] = ok ? 4 : 0;
+  }
+  float acc[MBW1][NB][4];
+#pragma unroll
+  for (int j = 0; j < MBW1; ++j)
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[j][nb][e] = 0.f;
+
+  const unsigned xw_s = (unsigned)__cvta_generic_to_shared(Xf + warp * WCOLS + lane);  // this lane's first column
+  const float* xw = Xf + warp * WCOLS;
+  for (int c0 = 0; c0 < g.Cin; c0 += g.fch) {
+    const int cc = min(g.fch, g.Cin - c0);
+    const int ccp = (cc + kGC - 1) / kGC * kGC;
+    const int ng = ccp / kGC;
+    auto issue = [&](int grp) {
+      if (grp < ng) {
+        const unsigned dst = xw_s + (unsigned)((grp % kFifo) * kGC * XP * 4);
+        const size_t coff = (size_t)(c0 + grp * kGC) * HW;
+        if (grp * kGC + kGC <= cc) {      // all 8 channels exist
+#pragma unroll
+          for (int q = 0; q < CPL; ++q)
+            if (CPL * 32 == WCOLS || lane + 32 * q < WCOLS) {
+              const float* sp = gp[q] + coff;
+#pragma unroll
+              for (int jc = 0; jc < kGC; ++jc) {
+                cp_async4_s(dst + (unsigned)((jc * XP + 32 * q) * 4), sp, gsz[q]);
+                sp += HW;
+              }
+            }
+        } else {
+#pragma unroll
+          for (int q = 0; q < CPL; ++q)
+            if (CPL * 32 == WCOLS || lane + 32 * q < WCOLS) {
+#pragma unroll
+              for (int jc = 0; jc < kGC; ++jc) {
+                const bool cin = grp * kGC + jc < cc;
+                cp_async4_s(dst + (unsigned)((jc * XP + 32 * q) * 4), cin ? gp[q] + coff + (size_t)jc * HW : in_n,
+                            cin ? gsz[q] : 0);
+              }
+            }
+        }
+      }
+      cp_async_commit();
+    };
+    // the first pixel copies go out before the factors are staged: their latency hides behind that work
+    // (the FIFO stages are free: the previous chunk has been consumed by every lane of this warp)
+#pragma unroll
+    for (int s = 0; s < kFifo - 1; ++s) issue(s);
+    __syncthreads();   // every warp is done with the previous chunk's factor planes
+    for (int i = tid; i < ccp * RP; i += kNT) {
+      const int c = i / RP, r = i % RP;
+      const float v = (r < g.R && c < cc) ? __ldg(Fin + (size_t)(c0 + c) * g.Rs + g.r0 + r) : 0.f;
+      const float hi = tf32_round(v);
+      Fh[c * FIN + r] = hi;
+      Fh[kFin + c * FIN + r] = tf32_round(v - hi);
+    }
+    if (g.early_fout && c0 == 0) stage_fout(0);
+    __syncthreads();
+    for (int grp = 0; grp < ng; ++grp) {
+      issue(grp + kFifo - 1);
+      cp_async_wait<kFifo - 1>();
+      __syncwarp();
+      const float* xs = xw + (grp % kFifo) * kGC * XP;
+      // B fragments of this k-step: element (k = channel, n = rank)
+      uint32_t bh[NB][2], bl[NB][2];
+      {
+        const float* f = Fh + (grp * kGC + tq) * FIN + gq;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          bh[nb][0] = __float_as_uint(f[nb * 8]);
+          bh[nb][1] = __float_as_uint(f[nb * 8 + 4 * FIN]);
+          bl[nb][0] = __float_as_uint(f[nb * 8 + kFin]);
+          bl[nb][1] = __float_as_uint(f[nb * 8 + kFin + 4 * FIN]);
+        }
+      }
+      // A fragments: element (m = pixel, k = channel) at xs[channel][column]
+      uint32_t ah[MBW1][4], al[MBW1][4];
+      {
+        const float* xa = xs + tq * XP + gq;
+#pragma unroll
+        for (int j = 0; j < MBW1; ++j) {
+          split_tf32(xa[j * 16], ah[j][0], al[j][0]);
+          split_tf32(xa[j * 16 + 8], ah[j][1], al[j][1]);
+          split_tf32(xa[j * 16 + 4 * XP], ah[j][2], al[j][2]);
+          split_tf32(xa[j * 16 + 4 * XP + 8], ah[j][3], al[j][3]);
+        }
+      }
+      __syncwarp();  // every lane has read this FIFO stage: a later group may overwrite it
+#pragma unroll
+      for (int j = 0; j < MBW1; ++j)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) mma_tf32(acc[j][nb], al[j], bh[nb]);
+#pragma unroll
+      for (int j = 0; j < MBW1; ++j)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) mma_tf32(acc[j][nb], ah[j], bl[nb]);
+#pragma unroll
+      for (int j = 0; j < MBW1; ++j)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) mma_tf32(acc[j][nb], ah[j], bh[nb]);
+    }
+    cp_async_wait<0>();
+  }
+  // P fragments -> Ps[r][halo px]
+#pragma unroll
+  for (int j = 0; j < MBW1; ++j) {
+    float* p = Ps + (size_t)(2 * tq) * PP + (j * kWarps + warp) * 16 + gq;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      p[(nb * 8) * PP] = acc[j][nb][0];
+      p[(nb * 8 + 1) * PP] = acc[j][nb][1];
+      p[(nb * 8) * PP + 8] = acc[j][nb][2];
+      p[(nb * 8 + 1) * PP + 8] = acc[j][nb][3];
+    }
+  }
+  __syncthreads();
+
+  if (!g.early_fout) stage_fout(0);
+
+  // ---------------- phase 2 ----------------
+  {
+    const int r = tid % RP;           // fixed per thread (kNT is a multiple of RP)
+    if (FS == 3) {
+      float w[9];
+#pragma unroll
+      for (int t = 0; t < 9; ++t) w[t] = Ws[t * RP + r];
+      constexpr int SW = 8;
+      const int spr = (g.TW + SW - 1) / SW;
+      const int items = g.TH * spr;
+      for (int it = tid / RP; it < items; it += kNT / RP) {
+        const int oy = it / spr, x0 = (it - oy * spr) * SW;
+        float z[SW];
+#pragma unroll
+        for (int j = 0; j < SW; ++j) z[j] = 0.f;
+        // reads past the tile's last column stay inside the padded row and feed only outputs that are not stored
+        const float* p = Ps + (size_t)r * PP + oy * g.TWh + x0;
+#pragma unroll
+        for (int dy = 0; dy < 3; ++dy) {
+          float v[SW + 2];
+#pragma unroll
+          for (int j = 0; j < SW + 2; ++j) v[j] = p[j];
+          p += g.TWh;
+#pragma unroll
+          for (int j = 0; j < SW; ++j) {
+            z[j] = fmaf(w[dy * 3 + 0], v[j], z[j]);
+            z[j] = fmaf(w[dy * 3 + 1], v[j + 1], z[j]);
+            z[j] = fmaf(w[dy * 3 + 2], v[j + 2], z[j]);
+          }
+        }
+        float* zd = Zs + r * ZP + oy * g.TW + x0;
+        if (x0 + SW <= g.TW) {
+#pragma unroll
+          for (int j = 0; j < SW; ++j) zd[j] = z[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < SW; ++j)
+            if (x0 + j < g.TW) zd[j] = z[j];
+        }
+      }
+    } else {
+      for (int op = tid / RP; op < g.OPX; op += kNT / RP) {
+        const int oy = op / g.TW, ox = op - oy * g.TW;
+        const float* p = Ps + (size_t)r * PP + oy * g.TWh + ox;
+        float z = 0.f;
+        for (int y = 0; y < g.Y; ++y)
+          for (int x = 0; x < g.X; ++x) z = fmaf(Ws[(y * g.X + x) * RP + r], p[y * g.TWh + x], z);
+        Zs[r * ZP + op] = z;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---------------- phase 3 ----------------
+  // this warp's output blocks: block j is output block (j*kWarps + warp).  A fragments: element (m = pixel,
+  // k = rank) at Zs[rank][pixel]; B fragments: element (k = rank, n = channel) at Fh[channel][rank].
+  float* out_n = out + (size_t)n * g.Cout * HW;
+  float* op_ptr[MBW3][2];   // this thread's two pixels of channel 2*tq (null: outside the tile or the image)
+#pragma unroll
+  for (int j = 0; j < MBW3; ++j)
+#pragma unroll
+    for (int hlf = 0; hlf < 2; ++hlf) {
+      const int op = (j * kWarps + warp) * 16 + gq + 8 * hlf;
+      const int oy = op / g.TW, ox = op - oy * g.TW;
+      const int gy = h0 + oy, gx = w0 + ox;
+      op_ptr[j][hlf] = (op < g.OPX && gy < g.H && gx < g.W) ? out_n + (size_t)(2 * tq) * HW + gy * g.W + gx : nullptr;
+    }
+  constexpr bool kAllBlocks = MBW3 * NB <= 8;   // A fragments of every block fit in registers
+  uint32_t zh[kAllBlocks ? MBW3 : 1][NB][4], zl[kAllBlocks ? MBW3 : 1][NB][4];
+  auto load_a = [&](int j, int slot) {
+    const float* za = Zs + tq * ZP + (j * kWarps + warp) * 16 + gq;
+#pragma unroll
+    for (int kb = 0; kb < NB; ++kb) {
+      split_tf32(za[kb * 8 * ZP], zh[slot][kb][0], zl[slot][kb][0]);
+      split_tf32(za[kb * 8 * ZP + 8], zh[slot][kb][1], zl[slot][kb][1]);
+      split_tf32(za[(kb * 8 + 4) * ZP], zh[slot][kb][2], zl[slot][kb][2]);
+      split_tf32(za[(kb * 8 + 4) * ZP + 8], zh[slot][kb][3], zl[slot][kb][3]);
+    }
+  };
+  auto store_d = [&](const float (&d)[4], float* p0, float* p1, size_t toff, bool two) {
+    if (g.accumulate) {
+      if (p0) { p0[toff] += d[0]; if (two) p0[toff + HW] += d[1]; }
+      if (p1) { p1[toff] += d[2]; if (two) p1[toff + HW] += d[3]; }
+    } else {
+      if (p0) { p0[toff] = d[0]; if (two) p0[toff + HW] = d[1]; }
+      if (p1) { p1[toff] = d[2]; if (two) p1[toff + HW] = d[3]; }
+    }
+  };
+  if (kAllBlocks) {
+#pragma unroll
+    for (int j = 0; j < MBW3; ++j) load_a(j, j);
+  }
+  for (int t0 = 0; t0 < g.Cout; t0 += g.fch) {
+    const int tc = min(g.fch, g.Cout - t0);
+    if (t0 > 0) {
+      __syncthreads();
+      stage_fout(t0);
+      __syncthreads();
+    }
+    const int nbs = (tc + 7) / 8;
+    if (kAllBlocks) {
+#pragma unroll 2
+      for (int nb = 0; nb < nbs; ++nb) {
+        uint32_t bh[NB][2], bl[NB][2];
+        const float* f = Fo + (nb * 8 + gq) * FOUT + tq;
+#pragma unroll
+        for (int kb = 0; kb < NB; ++kb) {
+          bh[kb][0] = __float_as_uint(f[kb * 8]);
+          bh[kb][1] = __float_as_uint(f[kb * 8 + 4]);
+          bl[kb][0] = __float_as_uint(f[kb * 8 + kFout]);
+          bl[kb][1] = __float_as_uint(f[kb * 8 + kFout + 4]);
+        }
+        float d[MBW3][4];
+#pragma unroll
+        for (int j = 0; j < MBW3; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < NB; ++kb) {
+#pragma unroll
+          for (int j = 0; j < MBW3; ++j) mma_tf32(d[j], zl[j][kb], bh[kb]);
+#pragma unroll
+          for (int j = 0; j < MBW3; ++j) mma_tf32(d[j], zh[j][kb], bl[kb]);
+#pragma unroll
+          for (int j = 0; j < MBW3; ++j) mma_tf32(d[j], zh[j][kb], bh[kb]);
+        }
+        const int t = nb * 8 + 2 * tq;          // channel of d[.][0] within the chunk
+        if (t < tc) {
+          const size_t toff = (size_t)(t0 + nb * 8) * HW;
+#pragma unroll
+          for (int j = 0; j < MBW3; ++j) store_d(d[j], op_ptr[j][0], op_ptr[j][1], toff, t + 1 < tc);
+        }
+      }
+    } else {
+#pragma unroll 1
+      for (int j = 0; j < MBW3; ++j) {
+        load_a(j, 0);
+        for (int nb = 0; nb < nbs; ++nb) {
+          const float* f = Fo + (nb * 8 + gq) * FOUT + tq;
+          float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int kb = 0; kb < NB; ++kb) {
+            const uint32_t bh[2] = {__float_as_uint(f[kb * 8]), __float_as_uint(f[kb * 8 + 4])};
+            const uint32_t bl[2] = {__float_as_uint(f[kb * 8 + kFout]), __float_as_uint(f[kb * 8 + kFout + 4])};
+            mma_tf32(d, zl[0][kb], bh);
+            mma_tf32(d, zh[0][kb], bl);
+            mma_tf32(d, zh[0][kb], bh);
+          }
+          const int t = nb * 8 + 2 * tq;
+          if (t < tc) store_d(d, op_ptr[j][0], op_ptr[j][1], (size_t)(t0 + nb * 8) * HW, t + 1 < tc);
+        }
+      }
+    }
+  }
+}
+
+template <int RP, int FS, int M1, int M3>
+int launch_mma(const MmaGeom& g, const Cp4Args& a, cudaStream_t st) {
+  auto kern = cp4_conv_mma_kernel<RP, FS, M1, M3>;
+  const size_t smem = sizeof(float) * mma_smem_floats<RP>(g);
+  B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const long ctas = (long)a.N * g.tilesH * g.tilesW;
+  if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4: too many tiles");
+  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.in, a.Fin, a.Fout, a.KH, a.KW, a.out);
+  B200CP_LAUNCH_OK("cp4_conv_mma_kernel");
+  return B200CP_OK;
+}
+
+template <int RP, int FS>
+int dispatch_blocks(const MmaGeom& g, const Cp4Args& a, cudaStream_t st) {
+  switch (g.MBW1 * 10 + g.MBW3) {
+    case 11: return launch_mma<RP, FS, 1, 1>(g, a, st);
+    case 21: return launch_mma<RP, FS, 2, 1>(g, a, st);
+    case 22: return launch_mma<RP, FS, 2, 2>(g, a, st);
+    case 32: return launch_mma<RP, FS, 3, 2>(g, a, st);
+    case 33: return launch_mma<RP, FS, 3, 3>(g, a, st);
+    case 43: return launch_mma<RP, FS, 4, 3>(g, a, st);
+    case 44: return launch_mma<RP, FS, 4, 4>(g, a, st);
+  }
+  return fail(B200CP_ERR_UNSUPPORTED, "cp4: internal: no mma kernel for %d/%d blocks per warp", g.MBW1, g.MBW3);
+}
+
+template <int RP>
+bool plan_tile(const Cp4Args& a, const DeviceInfo& di, MmaGeom* out) {
+  MmaGeom best{};
+  double best_cost = 1e300;
+  int fTH = 0, fTW = 0;
+  if (const char* e = getenv("B200CP_MMA_TILE")) {  // "TH,TW": experiments
+    if (sscanf(e, "%d,%d", &fTH, &fTW) != 2) fTH = fTW = 0;
+  }
+  for (int TW = 1; TW <= std::min(a.W, 64); ++TW) {
+    if (fTW ? TW != std::min(fTW, a.W) : (TW != a.W && a.W % TW != 0 && TW % 8 != 0)) continue;
+    for (int TH = 1; TH <= std::min(a.H, 64); ++TH) {
+      if (fTH && TH != std::min(fTH, a.H)) continue;
+      MmaGeom g{};
+      g.TH = TH; g.TW = TW; g.THh = TH + a.Y - 1; g.TWh = TW + a.X - 1;
+      g.HPX = g.THh * g.TWh; g.OPX = TH * TW;
+      g.MB1 = ceil_div(g.HPX, 16); g.MB3 = ceil_div(g.OPX, 16);
+      g.MBW1 = ceil_div(g.MB1, kWarps); g.MBW3 = ceil_div(g.MB3, kWarps);
+      if (g.MBW1 > 4 || g.MBW1 * (RP / 8) > 16) break;   // phase-1 accumulators: 4 * MBW1 * RP/8 registers
+      if (g.MBW3 > g.MBW1 || g.MBW3 < g.MBW1 - 1) continue;  // instantiated pairs
+      g.xpitch = pitch_mod32(kWarps * g.MBW1 * 16, 8);
+      g.ppitch = (kWarps * g.MBW1 * 16 + a.X + 8) | 1;   // odd: the ranks of a warp hit different banks; the slack
+                                                          // keeps the strips' reads past the last column inside the row
+      g.zpitch = pitch_mod32(kWarps * g.MBW3 * 16, 8);
+      g.Y = a.Y; g.X = a.X;
+      g.fch = std::min(kFChunk, (std::max(a.Cin, a.Cout) + 7) / 8 * 8);
+      g.early_fout = std::max(a.Cin, a.Cout) <= g.fch ? 1 : 0;
+      const size_t smem = sizeof(float) * mma_smem_floats<RP>(g);
+      if ((int)smem > di.smem_optin) break;
+      const int cps_max = (RP <= 16 && g.MBW1 <= 2) ? 3 : 2;
+      const int cps = std::max(1, std::min(cps_max, (int)((228 * 1024) / (smem + 1024))));
+      const long ctas = (long)a.N * ceil_div(a.H, TH) * ceil_div(a.W, TW);
+      const long rounds = (ctas + (long)di.sm_count * cps - 1) / ((long)di.sm_count * cps);
+      // issue slots per warp and tile: k-steps * blocks * (3 mma per rank block + fragment work), plus fixed work
+      const double c1 = (double)ceil_div(a.Cin, 8) * (g.MBW1 * (3.0 * RP / 8 + 14) + 4.0 * RP / 8 + 12 + 10.0 * g.MBW1);
+      const double c3 = (double)ceil_div(a.Cout, 8) * (g.MBW3 * (3.0 * RP / 8 + 10) + 4.0 * RP / 8);
+      const double c2 = (double)ceil_div(TH * ceil_div(TW, 8) * RP, kNT) * 90.0;
+      const double tile = c1 + c2 + c3;
+      // measured on B200: throughput grows with the warps resident per SM (24 = three CTAs), and every round of
+      // CTAs pays the latency of one tile's dependent chain (copies, barriers, stores)
+      const double occupancy = 24.0 / (cps * kWarps);
+      const double cost = (double)ctas * tile / di.sm_count * occupancy + 1200.0 * rounds;
+      if (cost < best_cost) { best_cost = cost; best = g; }
+    }
+  }
+  if (best.TH == 0) return false;
+  *out = best;
+  return true;
+}
+
+template <int RP>
+int run_mma(const Cp4Args& a, const DeviceInfo& di, cudaStream_t st) {
+  MmaGeom g{};
+  if (!plan_tile<RP>(a, di, &g)) return fail(B200CP_ERR_UNSUPPORTED, "cp4 (mma path): no tile of this filter fits in shared memory");
+  g.N = a.N; g.Cin = a.Cin; g.Cout = a.Cout; g.H = a.H; g.W = a.W; g.Y = a.Y; g.X = a.X; g.pad = a.pad;
+  g.R = a.R; g.Rs = a.Rs; g.r0 = a.r0; g.flip = a.flip; g.accumulate = a.accumulate;
+  g.tilesH = ceil_div(a.H, g.TH); g.tilesW = ceil_div(a.W, g.TW);
+  if (getenv("B200CP_DEBUG"))
+    fprintf(stderr, "[b200cp] mma tile TH=%d TW=%d blocks %d/%d per warp %d/%d smem=%zu RP=%d\n", g.TH, g.TW, g.MB1, g.MB3,
+            g.MBW1, g.MBW3, sizeof(float) * mma_smem_floats<RP>(g), RP);
+  if (a.Y == 3 && a.X == 3) return dispatch_blocks<RP, 3>(g, a, st);
+  return dispatch_blocks<RP, 0>(g, a, st);
+}
+
+}  // namespace
+
+int cp4_mma_launch(const Cp4Args& a, cudaStream_t st) {
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  const int rp = padded_rank(a.R);
+  if (rp <= 8) return run_mma<8>(a, di, st);
+  if (rp == 16) return run_mma<16>(a, di, st);
+  if (rp == 32) return run_mma<32>(a, di, st);
+  return run_mma<64>(a, di, st);
+}
+
+}  // namespace b200cp

@@ -24,7 +24,10 @@ namespace {
 
 constexpr int kFactorCap = 4096;  // most floats of smem used to stage one factor chunk
 constexpr int kKC = 4;            // channels per cp.async group
-constexpr int kStages = 4;        // cp.async groups in flight per thread (one being consumed)
+#ifndef B200CP_STAGES
+#define B200CP_STAGES 4
+#endif
+constexpr int kStages = B200CP_STAGES;  // cp.async groups in flight per thread (one being consumed)
 
 // floats of smem reserved for a factor chunk of a layer with `maxch` channels
 inline int factor_cap(int maxch, int RP) {

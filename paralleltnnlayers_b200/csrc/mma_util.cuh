@@ -1,0 +1,50 @@
+// Warp-level tensor-core helpers (mma.sync m16n8k8, tf32 operands, fp32 accumulation) and cp.async wrappers.
+//
+// Fragment layout of mma.sync.aligned.m16n8k8.row.col (g = lane / 4, t = lane % 4):
+//   A (16 x 8): a0 = (row g, col t), a1 = (row g+8, col t), a2 = (row g, col t+4), a3 = (row g+8, col t+4)
+//   B ( 8 x 8): b0 = (row t, col g), b1 = (row t+4, col g)
+//   D (16 x 8): d0 = (row g, col 2t), d1 = (row g, col 2t+1), d2 = (row g+8, col 2t), d3 = (row g+8, col 2t+1)
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace b200cp {
+namespace mma {
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+// hi = x rounded to tf32; lo = x - hi (exact in fp32; the tensor core reads its upper 19 bits)
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  lo = __float_as_uint(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  // not volatile: the instruction only touches its register operands, so the compiler may interleave
+  // independent accumulator chains
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* gsrc, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int sz = valid ? 4 : 0;  // src-size 0: the destination is zero-filled, nothing is read
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gsrc), "r"(sz) : "memory");
+}
+// same with the destination given as a shared-memory address and the source size (4, or 0 = zero fill)
+__device__ __forceinline__ void cp_async4_s(unsigned smem_dst, const float* gsrc, int src_size) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_size) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+}  // namespace mma
+}  // namespace b200cp

@@ -1,0 +1,41 @@
+"""Parity of the CP4 kernels on the warp-level tensor path (mma.sync, three tf32 terms) with the float64 oracle,
+at the fp32 tolerance: rtol 1e-4, atol 1e-5."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cp_oracle as O
+from tests.gpu_util import check, dev
+from tests.test_cp4_gpu import FWD_SHAPES, _inputs
+
+pytestmark = pytest.mark.gpu
+
+MMA_SHAPES = FWD_SHAPES + [
+    (53, 2, 64, 64, 56, 56, 3, 16, 1, 1.0 / 24),   # BASELINE config 2 at N = 2
+    (54, 2, 128, 128, 28, 28, 3, 32, 1, 0.03),     # config 3 shapes at a reduced batch
+    (55, 2, 256, 256, 14, 14, 3, 64, 1, 0.02),
+    (56, 2, 512, 512, 7, 7, 3, 8, 1, 0.015),       # more channels than one staged factor chunk
+]
+
+
+@pytest.mark.parametrize("case", MMA_SHAPES, ids=lambda c: "s%d" % c[0])
+def test_forward_and_backward_data_mma(case):
+    import paralleltnnlayers_b200 as P
+    (X, K0, K1, KH, KW, dU), pad = _inputs(case)
+    dX_, dK0, dK1, dKH, dKW, ddU = dev(X, K0, K1, KH, KW, dU)
+    n0 = P.launch_count()
+    U = P.cp4_conv2d_forward(dX_, dK0, dK1, dKH, dKW, pad, flags=P.PATH_MMA)
+    assert P.launch_count() > n0
+    check(U, O.cp4_forward(X, K0, K1, KH, KW, pad), "forward (mma)")
+    dX = P.cp4_conv2d_backward_data(ddU, dK0, dK1, dKH, dKW, pad, flags=P.PATH_MMA)
+    check(dX, O.cp4_backward_data(dU, K0, K1, KH, KW, pad), "backward-data (mma)")
+
+
+def test_mma_path_close_to_exact_path():
+    """The three-term tf32 products stay within a few fp32 ulps of the FFMA path."""
+    import paralleltnnlayers_b200 as P
+    (X, K0, K1, KH, KW, dU), pad = _inputs((57, 2, 64, 64, 28, 28, 3, 16, 1, 1.0 / 24))
+    t = dev(X, K0, K1, KH, KW)
+    a = P.cp4_conv2d_forward(*t, pad, flags=P.PATH_MMA)
+    b = P.cp4_conv2d_forward(*t, pad, flags=P.PATH_SIMT)
+    assert float((a - b).abs().max()) <= 2e-6 * float(b.abs().max())
