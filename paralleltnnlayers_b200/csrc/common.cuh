@@ -74,6 +74,13 @@ struct Cp4BwdFilterArgs {
 };
 size_t cp4_bwd_filter_simt_workspace(const b200cp_tensor_shape& s);
 int cp4_bwd_filter_simt_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
+// warp-level tensor path (mma.sync, three tf32 terms); 3x3 filters with pad 1
+bool cp4_bwd_filter_mma_supported(const Cp4BwdFilterArgs& a);
+size_t cp4_bwd_filter_mma_workspace(const b200cp_tensor_shape& s);
+int cp4_bwd_filter_mma_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
+// dK[row*Rs + r0 + r] = sum over parts of partial[part][row*R + r], in a fixed order
+int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
+                               cudaStream_t st);
 size_t cp4_bwd_filter_static_scratch_bytes();
 int cp4_bwd_filter_static_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
 int cp4_bwd_filter_full_launch(const b200cp_tensor_shape& s, const float* X, const float* dU, float* dK,

@@ -1,0 +1,522 @@
+// CP4 conv2d backward-filter (3x3 filters) with warp-level tensor-core contractions (mma.sync, tf32 in three
+// terms, fp32 accumulation: fp32-grade results).
+//
+// One CTA of 8 warps owns a TH x TW tile of one image and works on its halo tile ((TH+2) x (TW+2) pixels, the
+// columns of every shared-memory plane; warp w owns a contiguous range of them).  Three streaming passes over
+// the channels, each through a warp-private cp.async FIFO (16 channels per group):
+//   pass 1 (X):   P[r, px]  = sum_c K1[c, r] X[c, px]                      M = pixels, K = channels, N = ranks
+//   stencil A:    Z[r, px]  = sum_{y,x} KH[y,r] KW[x,r] P[r, px + (y-1, x-1)]   interior pixels; 0 on the halo ring
+//   pass 2 (dU):  Q[r, px]  = sum_t K0[t, r] dU[t, px]                     same GEMM shape
+//                 dK0[t, r] += sum_px dU[t, px] Z[r, px]                   M = channels, K = pixels, N = ranks
+//   stencil B:    Qt[r, px] = sum_{y,x} KH[y,r] KW[x,r] Q[r, px - (y-1, x-1)]  interior pixels; 0 on the halo ring
+//                 dKH[y, r] += Q[r, px] * sum_x KW[x,r] P[r, px + (y-1, x-1)],  dKW[x, r] likewise   (CUDA cores)
+//   pass 3 (X):   dK1[c, r] += sum_px X[c, px] Qt[r, px]
+// Both orientations of a channel group (pixels x channels for the contraction, channels x pixels for the
+// reduction) are read as mma fragments from the same FIFO stage.  Pixels outside the image are zero-filled by
+// the copies, which is the zero padding of the convolution.  Each CTA writes its partial gradients to
+// workspace[cta][...]; a second kernel sums the partials in CTA order, so results are bitwise reproducible.
+// Formulas: Cuda_kernels/cp4Conv2dBackwardFilter.cu:91-104,142-155,192-205,241-254.
+#include <algorithm>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "mma_util.cuh"
+
+namespace b200cp {
+
+namespace {
+
+using namespace mma;
+
+constexpr int kNT = 256, kWarps = 8;
+constexpr int kGC = 16;    // channels per cp.async group: two contraction k-steps, one reduction m-block
+constexpr int kFifo = 2;   // cp.async groups per warp (one being consumed)
+
+struct BGeom {
+  int N, C, T, H, W, R, Rs, r0;
+  int TH, TW, TWh, HPX, tilesH, tilesW;
+  int MBW;     // 16-pixel blocks of the halo tile per warp
+  int nparam;  // (T + C + 6) * R floats per partial
+  int pp;      // row pitch of the P and Q planes (odd)
+};
+
+template <int RP>
+struct BCfg {
+  static constexpr int NB = RP / 8;
+  static constexpr int MB2 = NB <= 2 ? 4 : NB == 4 ? 2 : 1;  // channel blocks whose gradient sums stay in registers
+  static constexpr int CHA = MB2 * 16;                       // channels per accumulation chunk
+  static constexpr int FIN = RP == 8 ? 24 : RP + 8;          // factor plane pitch (see the forward kernel)
+};
+
+template <int RP>
+size_t bwdf_mma_smem_floats(const BGeom& g) {
+  using K = BCfg<RP>;
+  const int cols = kWarps * g.MBW * 16;
+  const size_t fifo = (size_t)kFifo * kGC * (cols + 12);
+  const size_t red = (size_t)kWarps * K::CHA * RP;
+  const size_t planes = 2 * (size_t)RP * g.pp + (size_t)RP * (cols + 4);
+  const size_t fac = 2 * (size_t)K::CHA * K::FIN;
+  return std::max(fifo, red) + planes + fac + 6 * RP + kNT * 6;
+}
+
+// One pass over the channels of `src_n`.  CONTRACT: Out[r][px] = sum_ch F[ch][r] src[ch][px].
+// REDUCE: part[ch][r] = sum_px src[ch][px] * Zh[r][px] (over this CTA's halo tile).
+template <int RP, int MBW, bool CONTRACT, bool REDUCE>
+__device__ __forceinline__ void stream_pass(const BGeom& g, const float* __restrict__ src_n, int nch,
+                                            const float* __restrict__ Fg, float* Xf, float* Fh, float* Out,
+                                            const float* Zh, float* __restrict__ part, const float* const (&gp)[(MBW + 1) / 2],
+                                            const int (&gsz)[(MBW + 1) / 2], int tid) {
+  using K = BCfg<RP>;
+  constexpr int NB = K::NB, MB2 = K::MB2, CHA = K::CHA, FIN = K::FIN;
+  constexpr int WCOLS = MBW * 16, COLS = kWarps * WCOLS, CPL = (MBW + 1) / 2;
+  constexpr int XP = COLS + 12;   // 12 mod 32: the channel-major fragment loads are conflict-free, the
+                                  // pixel-major ones two-way on a quarter of the lanes
+  constexpr int ZP = COLS + 4;    // 4 mod 32
+  constexpr int kFpl = CHA * FIN; // floats per factor plane
+  const int lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+  const size_t HW = (size_t)g.H * g.W;
+  const unsigned xw_s = (unsigned)__cvta_generic_to_shared(Xf + warp * WCOLS + lane);
+  const float* xw = Xf + warp * WCOLS;
+
+  float cacc[MBW][NB][4];
+  if (CONTRACT) {
+#pragma unroll
+    for (int j = 0; j < MBW; ++j)
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) cacc[j][nb][0] = cacc[j][nb][1] = cacc[j][nb][2] = cacc[j][nb][3] = 0.f;
+  }
+
+  for (int c0 = 0; c0 < nch; c0 += CHA) {
+    const int cc = min(CHA, nch - c0);
+    const int ng = (cc + kGC - 1) / kGC;
+    auto issue = [&](int grp) {
+      if (grp < ng) {
+        const unsigned dst = xw_s + (unsigned)((grp % kFifo) * kGC * XP * 4);
+        const size_t coff = (size_t)(c0 + grp * kGC) * HW;
+        if (grp * kGC + kGC <= cc) {
+#pragma unroll
+          for (int q = 0; q < CPL; ++q)
+            if (CPL * 32 == WCOLS || lane + 32 * q < WCOLS) {
+              const float* sp = gp[q] + coff;
+#pragma unroll
+              for (int jc = 0; jc < kGC; ++jc) {
+                cp_async4_s(dst + (unsigned)((jc * XP + 32 * q) * 4), sp, gsz[q]);
+                sp += HW;
+              }
+            }
+        } else {
+#pragma unroll
+          for (int q = 0; q < CPL; ++q)
+            if (CPL * 32 == WCOLS || lane + 32 * q < WCOLS) {
+#pragma unroll
+              for (int jc = 0; jc < kGC; ++jc) {
+                const bool cin = grp * kGC + jc < cc;
+                cp_async4_s(dst + (unsigned)((jc * XP + 32 * q) * 4), cin ? gp[q] + coff + (size_t)jc * HW : src_n,
+                            cin ? gsz[q] : 0);
+              }
+            }
+        }
+      }
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < kFifo - 1; ++s) issue(s);
+    if (CONTRACT) {
+      __syncthreads();  // every warp is done with the previous chunk's factor planes
+      for (int i = tid; i < ng * kGC * RP; i += kNT) {
+        const int c = i / RP, r = i % RP;
+        const float v = (r < g.R && c < cc) ? __ldg(Fg + (size_t)(c0 + c) * g.Rs + g.r0 + r) : 0.f;
+        const float hi = tf32_round(v);
+        Fh[c * FIN + r] = hi;
+        Fh[kFpl + c * FIN + r] = tf32_round(v - hi);
+      }
+      __syncthreads();
+    }
+    float racc[MB2][NB][4];
+    if (REDUCE) {
+#pragma unroll
+      for (int m = 0; m < MB2; ++m)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) racc[m][nb][0] = racc[m][nb][1] = racc[m][nb][2] = racc[m][nb][3] = 0.f;
+    }
+#pragma unroll
+    for (int grp = 0; grp < MB2; ++grp) {
+      if (grp < ng) {
+        issue(grp + kFifo - 1);
+        cp_async_wait<kFifo - 1>();
+        __syncwarp();
+        const float* xs = xw + (grp % kFifo) * kGC * XP;
+        if (CONTRACT) {
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            // B fragments: element (k = channel, n = rank)
+            uint32_t bh[NB][2], bl[NB][2];
+            const float* f = Fh + (grp * kGC + ks * 8 + tq) * FIN + gq;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+              bh[nb][0] = __float_as_uint(f[nb * 8]);
+              bh[nb][1] = __float_as_uint(f[nb * 8 + 4 * FIN]);
+              bl[nb][0] = __float_as_uint(f[nb * 8 + kFpl]);
+              bl[nb][1] = __float_as_uint(f[nb * 8 + kFpl + 4 * FIN]);
+            }
+            // A fragments: element (m = pixel, k = channel)
+            uint32_t ah[MBW][4], al[MBW][4];
+            const float* xa = xs + (ks * 8 + tq) * XP + gq;
+#pragma unroll
+            for (int j = 0; j < MBW; ++j) {
+              split_tf32(xa[j * 16], ah[j][0], al[j][0]);
+              split_tf32(xa[j * 16 + 8], ah[j][1], al[j][1]);
+              split_tf32(xa[j * 16 + 4 * XP], ah[j][2], al[j][2]);
+              split_tf32(xa[j * 16 + 4 * XP + 8], ah[j][3], al[j][3]);
+            }
+#pragma unroll
+            for (int j = 0; j < MBW; ++j)
+#pragma unroll
+              for (int nb = 0; nb < NB; ++nb) mma_tf32(cacc[j][nb], al[j], bh[nb]);
+#pragma unroll
+            for (int j = 0; j < MBW; ++j)
+#pragma unroll
+              for (int nb = 0; nb < NB; ++nb) mma_tf32(cacc[j][nb], ah[j], bl[nb]);
+#pragma unroll
+            for (int j = 0; j < MBW; ++j)
+#pragma unroll
+              for (int nb = 0; nb < NB; ++nb) mma_tf32(cacc[j][nb], ah[j], bh[nb]);
+          }
+        }
+        if (REDUCE) {
+          const float* zb = Zh + gq * ZP + warp * WCOLS + tq;
+#pragma unroll
+          for (int kp = 0; kp < 2 * MBW; ++kp) {
+            // A fragment: element (m = channel, k = pixel);  B fragment: element (k = pixel, n = rank)
+            uint32_t ah[4], al[4];
+            const float* xa = xs + gq * XP + kp * 8 + tq;
+            split_tf32(xa[0], ah[0], al[0]);
+            split_tf32(xa[8 * XP], ah[1], al[1]);
+            split_tf32(xa[4], ah[2], al[2]);
+            split_tf32(xa[8 * XP + 4], ah[3], al[3]);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+              uint32_t bh[2], bl[2];
+              split_tf32(zb[nb * 8 * ZP + kp * 8], bh[0], bl[0]);
+              split_tf32(zb[nb * 8 * ZP + kp * 8 + 4], bh[1], bl[1]);
+              mma_tf32(racc[grp][nb], al, bh);
+              mma_tf32(racc[grp][nb], ah, bl);
+              mma_tf32(racc[grp][nb], ah, bh);
+            }
+          }
+        }
+        __syncwarp();  // every lane has read this FIFO stage: a later group may overwrite it
+      }
+    }
+    cp_async_wait<0>();
+    if (REDUCE) {
+      // the warps' partial sums meet in shared memory (over the FIFO) and are added in warp order
+      float* red = Xf;
+      __syncthreads();
+#pragma unroll
+      for (int m = 0; m < MB2; ++m)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          float* d = red + ((size_t)warp * CHA + m * 16 + gq) * RP + nb * 8 + 2 * tq;
+          d[0] = racc[m][nb][0];
+          d[1] = racc[m][nb][1];
+          d[8 * RP] = racc[m][nb][2];
+          d[8 * RP + 1] = racc[m][nb][3];
+        }
+      __syncthreads();
+      for (int i = tid; i < cc * RP; i += kNT) {
+        const int r = i % RP;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) s += red[(size_t)w * CHA * RP + i];
+        if (r < g.R) part[(size_t)(c0 + i / RP) * g.R + r] = s;
+      }
+      __syncthreads();
+    }
+  }
+  if (CONTRACT) {
+#pragma unroll
+    for (int j = 0; j < MBW; ++j) {
+      float* p = Out + (size_t)(2 * tq) * g.pp + warp * WCOLS + j * 16 + gq;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        p[(nb * 8) * g.pp] = cacc[j][nb][0];
+        p[(nb * 8 + 1) * g.pp] = cacc[j][nb][1];
+        p[(nb * 8) * g.pp + 8] = cacc[j][nb][2];
+        p[(nb * 8 + 1) * g.pp + 8] = cacc[j][nb][3];
+      }
+    }
+  }
+}
+
+template <int RP, int MBW>
+__global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, const float* __restrict__ X,
+                                                             const float* __restrict__ dU,
+                                                             const float* __restrict__ K0,
+                                                             const float* __restrict__ K1,
+                                                             const float* __restrict__ KH,
+                                                             const float* __restrict__ KW, float* __restrict__ ws) {
+  using K = BCfg<RP>;
+  constexpr int WCOLS = MBW * 16, COLS = kWarps * WCOLS, CPL = (MBW + 1) / 2;
+  constexpr int XP = COLS + 12, ZP = COLS + 4;
+  constexpr int kXR = kFifo * kGC * XP > kWarps * K::CHA * RP ? kFifo * kGC * XP : kWarps * K::CHA * RP;
+  extern __shared__ __align__(16) float smem[];
+  float* Xf = smem;                          // FIFO [kFifo][kGC][XP]; between passes: reduction scratch
+  float* Ps = Xf + kXR;                      // [RP][pp]
+  float* Qs = Ps + (size_t)RP * g.pp;        // [RP][pp]
+  float* Zh = Qs + (size_t)RP * g.pp;        // [RP][ZP]  Z, later Qt; zero outside the tile's interior
+  float* Fh = Zh + RP * ZP;                  // factor planes hi | lo of the current channel chunk
+  float* KHs = Fh + 2 * K::CHA * K::FIN;     // [3][RP]
+  float* KWs = KHs + 3 * RP;                 // [3][RP]
+  float* redk = KWs + 3 * RP;                // [kNT][6]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  int b = blockIdx.x;
+  const int tw = b % g.tilesW;
+  b /= g.tilesW;
+  const int th = b % g.tilesH;
+  const int n = b / g.tilesH;
+  const int h0 = th * g.TH, w0 = tw * g.TW;
+  const size_t HW = (size_t)g.H * g.W;
+  const float* X_n = X + (size_t)n * g.C * HW;
+  const float* dU_n = dU + (size_t)n * g.T * HW;
+  float* part = ws + (size_t)blockIdx.x * g.nparam;
+
+  for (int i = tid; i < 6 * RP; i += kNT) {
+    const int r = i % RP, y = (i / RP) % 3;
+    const float* src = i < 3 * RP ? KH : KW;
+    KHs[i] = r < g.R ? __ldg(src + (size_t)y * g.Rs + g.r0 + r) : 0.f;   // KWs follows KHs
+  }
+  for (int i = tid; i < RP * ZP / 4; i += kNT) reinterpret_cast<float4*>(Zh)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  // the slack columns of P and Q (read by the last strip of a row, never written) must be finite
+  for (int i = tid; i < 2 * RP * (g.pp - COLS); i += kNT) {
+    const int row = i / (g.pp - COLS), col = COLS + i % (g.pp - COLS);
+    Ps[(size_t)row * g.pp + col] = 0.f;   // rows RP..2RP-1 are Q's
+  }
+
+  // this lane's halo pixels: column = halo pixel index, warp w owns [w*WCOLS, (w+1)*WCOLS)
+  const float* gpx[CPL];
+  const float* gpu[CPL];
+  int gsz[CPL];
+#pragma unroll
+  for (int q = 0; q < CPL; ++q) {
+    const int wc = lane + 32 * q;
+    const int hp = warp * WCOLS + wc;
+    const int hy = hp / g.TWh, hx = hp - hy * g.TWh;
+    const int gy = h0 - 1 + hy, gx = w0 - 1 + hx;
+    const bool ok = wc < WCOLS && hp < g.HPX && gy >= 0 && gy < g.H && gx >= 0 && gx < g.W;
+    const int off = ok ? gy * g.W + gx : 0;
+    gpx[q] = X_n + off;
+    gpu[q] = dU_n + off;
+    gsz[q] = ok ? 4 : 0;
+  }
+
+  // ---- pass 1: P ----
+  stream_pass<RP, MBW, true, false>(g, X_n, g.C, K1, Xf, Fh, Ps, nullptr, nullptr, gpx, gsz, tid);
+  __syncthreads();
+
+  // ---- stencil A: Z on the interior pixels ----
+  const int r = tid % RP;   // fixed per thread (kNT is a multiple of RP)
+  float kh[3], kw[3];
+#pragma unroll
+  for (int t = 0; t < 3; ++t) { kh[t] = KHs[t * RP + r]; kw[t] = KWs[t * RP + r]; }
+  constexpr int SW = 8;
+  const int spr = (g.TW + SW - 1) / SW;
+  const int items = g.TH * spr;
+  for (int it = tid / RP; it < items; it += kNT / RP) {
+    const int oy = it / spr, x0 = (it - oy * spr) * SW;
+    float z[SW];
+#pragma unroll
+    for (int j = 0; j < SW; ++j) z[j] = 0.f;
+    const float* p = Ps + (size_t)r * g.pp + oy * g.TWh + x0;
+#pragma unroll
+    for (int dy = 0; dy < 3; ++dy) {
+      float v[SW + 2];
+#pragma unroll
+      for (int j = 0; j < SW + 2; ++j) v[j] = p[j];
+      p += g.TWh;
+#pragma unroll
+      for (int j = 0; j < SW; ++j) {
+        const float t = fmaf(kw[2], v[j + 2], fmaf(kw[1], v[j + 1], kw[0] * v[j]));
+        z[j] = fmaf(kh[dy], t, z[j]);
+      }
+    }
+    float* zd = Zh + r * ZP + (oy + 1) * g.TWh + x0 + 1;
+#pragma unroll
+    for (int j = 0; j < SW; ++j)
+      if (x0 + j < g.TW) zd[j] = z[j];
+  }
+  __syncthreads();
+
+  // ---- pass 2: Q and dK0 ----
+  stream_pass<RP, MBW, true, true>(g, dU_n, g.T, K0, Xf, Fh, Qs, Zh, part, gpu, gsz, tid);
+  __syncthreads();
+
+  // ---- stencil B: Qt on the interior pixels, dKH, dKW ----
+  float dkh[3] = {0.f, 0.f, 0.f}, dkw[3] = {0.f, 0.f, 0.f};
+  for (int it = tid / RP; it < items; it += kNT / RP) {
+    const int oy = it / spr, x0 = (it - oy * spr) * SW;
+    float qt[SW], vc[3][SW];   // vc[x][j] = sum_y KH[y] P[oy+y][x0+j+x]
+#pragma unroll
+    for (int j = 0; j < SW; ++j) qt[j] = vc[0][j] = vc[1][j] = vc[2][j] = 0.f;
+    float qc[SW];
+    const float* p = Ps + (size_t)r * g.pp + oy * g.TWh + x0;
+    const float* q = Qs + (size_t)r * g.pp + oy * g.TWh + x0;
+    float th_[3][SW];          // th_[y][j] = sum_x KW[x] P[oy+y][x0+j+x]
+#pragma unroll
+    for (int dy = 0; dy < 3; ++dy) {
+      float v[SW + 2], u[SW + 2];
+#pragma unroll
+      for (int j = 0; j < SW + 2; ++j) { v[j] = p[j]; u[j] = q[j]; }
+      p += g.TWh;
+      q += g.TWh;
+#pragma unroll
+      for (int j = 0; j < SW; ++j) {
+        th_[dy][j] = fmaf(kw[2], v[j + 2], fmaf(kw[1], v[j + 1], kw[0] * v[j]));
+        vc[0][j] = fmaf(kh[dy], v[j], vc[0][j]);
+        vc[1][j] = fmaf(kh[dy], v[j + 1], vc[1][j]);
+        vc[2][j] = fmaf(kh[dy], v[j + 2], vc[2][j]);
+        // flipped taps: row dy of the neighbourhood carries KH[2-dy], column dx carries KW[2-dx]
+        const float tq_ = fmaf(kw[0], u[j + 2], fmaf(kw[1], u[j + 1], kw[2] * u[j]));
+        qt[j] = fmaf(kh[2 - dy], tq_, qt[j]);
+        if (dy == 1) qc[j] = (x0 + j < g.TW) ? u[j + 1] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < SW; ++j) {
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+        dkh[t] = fmaf(qc[j], th_[t][j], dkh[t]);
+        dkw[t] = fmaf(qc[j], vc[t][j], dkw[t]);
+      }
+    }
+    float* zd = Zh + r * ZP + (oy + 1) * g.TWh + x0 + 1;
+#pragma unroll
+    for (int j = 0; j < SW; ++j)
+      if (x0 + j < g.TW) zd[j] = qt[j];
+  }
+#pragma unroll
+  for (int t = 0; t < 3; ++t) { redk[tid * 6 + t] = dkh[t]; redk[tid * 6 + 3 + t] = dkw[t]; }
+  __syncthreads();
+  for (int i = tid; i < 6 * RP; i += kNT) {
+    // threads rr + RP*k hold the sums of rank rr: add them in k order
+    const int rr = i % RP, t = i / RP;   // t: 0..2 dKH rows, 3..5 dKW rows
+    float s = 0.f;
+    for (int k = 0; k < kNT / RP; ++k) s += redk[(rr + RP * k) * 6 + t];
+    if (rr < g.R) part[(size_t)(g.T + g.C + t) * g.R + rr] = s;
+  }
+
+  // ---- pass 3: dK1 ----
+  stream_pass<RP, MBW, false, true>(g, X_n, g.C, nullptr, Xf, Fh, nullptr, Zh, part + (size_t)g.T * g.R, gpx, gsz, tid);
+}
+
+template <int RP>
+bool plan_bwdf(const Cp4BwdFilterArgs& a, const DeviceInfo& di, BGeom* out, size_t* smem_out) {
+  BGeom best{};
+  double best_cost = 1e300;
+  size_t best_smem = 0;
+  int fTH = 0, fTW = 0;
+  if (const char* e = getenv("B200CP_MMA_TILE")) {  // "TH,TW": experiments
+    if (sscanf(e, "%d,%d", &fTH, &fTW) != 2) fTH = fTW = 0;
+  }
+  for (int TW = 1; TW <= std::min(a.W, 64); ++TW) {
+    if (fTW ? TW != std::min(fTW, a.W) : (TW != a.W && a.W % TW != 0 && TW % 8 != 0)) continue;
+    for (int TH = 1; TH <= std::min(a.H, 64); ++TH) {
+      if (fTH && TH != std::min(fTH, a.H)) continue;
+      BGeom g{};
+      g.TH = TH; g.TW = TW; g.TWh = TW + 2; g.HPX = (TH + 2) * g.TWh;
+      g.MBW = ceil_div(ceil_div(g.HPX, 16), kWarps);
+      if (g.MBW > 4 || g.MBW * (RP / 8) > 8) break;   // contraction accumulators: 4 * MBW * RP/8 registers
+      g.pp = (kWarps * g.MBW * 16 + 11) | 1;
+      const size_t smem = sizeof(float) * bwdf_mma_smem_floats<RP>(g);
+      if ((int)smem > di.smem_optin) break;
+      const int cps = std::max(1, std::min(2, (int)((228 * 1024) / (smem + 1024))));
+      const long ctas = (long)a.N * ceil_div(a.H, TH) * ceil_div(a.W, TW);
+      const long rounds = (ctas + (long)di.sm_count * cps - 1) / ((long)di.sm_count * cps);
+      const double nb = RP / 8.0;
+      const double contract = 2.0 * (g.MBW * (3.0 * nb + 12) + 4.0 * nb) + 40;   // per group of 16 channels
+      const double reduce = 2.0 * g.MBW * (12 + nb * 9.0);
+      const double groups = ceil_div(a.C, 16) * (contract + reduce + 40) + ceil_div(a.T, 16) * (contract + reduce + 40);
+      const double stencil = (double)ceil_div(TH * ceil_div(TW, 8) * RP, kNT) * 450.0;
+      const double tile = groups + stencil + 800.0;
+      const double occupancy = 16.0 / (cps * kWarps);
+      const double cost = (double)ctas * tile / di.sm_count * occupancy + 2500.0 * rounds;
+      if (cost < best_cost) { best_cost = cost; best = g; best_smem = smem; }
+    }
+  }
+  if (best.TH == 0) return false;
+  *out = best;
+  *smem_out = best_smem;
+  return true;
+}
+
+template <int RP, int MBW>
+int launch_bwdf(const BGeom& g, size_t smem, const Cp4BwdFilterArgs& a, cudaStream_t st) {
+  auto kern = cp4_bwdf_mma_kernel<RP, MBW>;
+  B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const long ctas = (long)a.N * g.tilesH * g.tilesW;
+  if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: too many tiles");
+  const size_t need = (size_t)ctas * g.nparam * sizeof(float);
+  if (a.ws_bytes < need)
+    return fail(B200CP_ERR_WORKSPACE, "cp4 bwd-filter: workspace of %zu bytes needed, %zu given", need, a.ws_bytes);
+  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.X, a.dU, a.K0, a.K1, a.KH, a.KW, (float*)a.ws);
+  B200CP_LAUNCH_OK("cp4_bwdf_mma_kernel");
+  return cp4_reduce_partials_launch((const float*)a.ws, (int)ctas, g.nparam, a.R, a.Rs, a.r0, a.dK, st);
+}
+
+template <int RP>
+int run_bwdf(const Cp4BwdFilterArgs& a, const DeviceInfo& di, cudaStream_t st) {
+  BGeom g{};
+  size_t smem = 0;
+  if (!plan_bwdf<RP>(a, di, &g, &smem)) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter (mma path): no tile fits in shared memory");
+  g.N = a.N; g.C = a.C; g.T = a.T; g.H = a.H; g.W = a.W; g.R = a.R; g.Rs = a.Rs; g.r0 = a.r0;
+  g.tilesH = ceil_div(a.H, g.TH); g.tilesW = ceil_div(a.W, g.TW);
+  g.nparam = (a.T + a.C + 6) * a.R;
+  if (getenv("B200CP_DEBUG"))
+    fprintf(stderr, "[b200cp] bwd-filter mma tile TH=%d TW=%d blocks per warp %d smem=%zu RP=%d\n", g.TH, g.TW, g.MBW, smem, RP);
+  switch (g.MBW) {
+    case 1: return launch_bwdf<RP, 1>(g, smem, a, st);
+    case 2: return launch_bwdf<RP, 2>(g, smem, a, st);
+    case 3: if constexpr (RP <= 16) return launch_bwdf<RP, 3>(g, smem, a, st); break;
+    case 4: if constexpr (RP <= 16) return launch_bwdf<RP, 4>(g, smem, a, st); break;
+  }
+  return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: internal: no mma kernel for %d blocks per warp at rank tile %d", g.MBW, RP);
+}
+
+}  // namespace
+
+bool cp4_bwd_filter_mma_supported(const Cp4BwdFilterArgs& a) { return a.F == 3 && a.pad == 1; }
+
+// bytes of workspace the mma path needs for this shape (0: no device or no tile)
+size_t cp4_bwd_filter_mma_workspace(const b200cp_tensor_shape& s) {
+  if (s.Y != 3 || s.X != 3 || s.pad != 1) return 0;
+  DeviceInfo di;
+  int dev_count = 0;
+  if (cudaGetDeviceCount(&dev_count) != cudaSuccess || dev_count <= 0 || device_info(&di) != B200CP_OK) return 0;
+  size_t need = 0;
+  for (unsigned r0 = 0; r0 < s.Rank; r0 += 64) {
+    const int rc = (int)std::min(64u, s.Rank - r0);
+    Cp4BwdFilterArgs a{};
+    a.N = s.N; a.C = s.C; a.T = s.T; a.H = s.H; a.W = s.W; a.F = 3; a.pad = 1; a.R = rc;
+    BGeom g{};
+    size_t smem = 0;
+    const int rp = padded_rank(rc);
+    const bool ok = rp <= 8 ? plan_bwdf<8>(a, di, &g, &smem) : rp == 16 ? plan_bwdf<16>(a, di, &g, &smem)
+                    : rp == 32 ? plan_bwdf<32>(a, di, &g, &smem) : plan_bwdf<64>(a, di, &g, &smem);
+    if (!ok) return 0;
+    need = std::max(need, (size_t)s.N * ceil_div(s.H, g.TH) * ceil_div(s.W, g.TW) * ((size_t)s.T + s.C + 6) * rc * sizeof(float));
+  }
+  return need;
+}
+
+int cp4_bwd_filter_mma_launch(const Cp4BwdFilterArgs& a, cudaStream_t st) {
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  const int rp = padded_rank(a.R);
+  if (rp <= 8) return run_bwdf<8>(a, di, st);
+  if (rp == 16) return run_bwdf<16>(a, di, st);
+  if (rp == 32) return run_bwdf<32>(a, di, st);
+  return run_bwdf<64>(a, di, st);
+}
+
+}  // namespace b200cp

@@ -430,6 +430,13 @@ int dispatch_bwd_filter_rank(const Cp4BwdFilterArgs& a, const DeviceInfo& di, cu
 
 }  // namespace
 
+int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
+                               cudaStream_t st) {
+  cp4_reduce_partials_kernel<<<ceil_div(nparam, 32), dim3(32, 32), 0, st>>>(partial, nparts, nparam, R, Rs, r0, dK);
+  B200CP_LAUNCH_OK("cp4_reduce_partials_kernel");
+  return B200CP_OK;
+}
+
 // One partial gradient set per CTA.  With a device present the tile the launch will pick is
 // known exactly; without one (argument checks on a CPU-only host) an upper bound is returned.
 size_t cp4_bwd_filter_simt_workspace(const b200cp_tensor_shape& s) {

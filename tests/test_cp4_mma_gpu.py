@@ -39,3 +39,24 @@ def test_mma_path_close_to_exact_path():
     a = P.cp4_conv2d_forward(*t, pad, flags=P.PATH_MMA)
     b = P.cp4_conv2d_forward(*t, pad, flags=P.PATH_SIMT)
     assert float((a - b).abs().max()) <= 2e-6 * float(b.abs().max())
+
+
+BWDF_MMA_SHAPES = [c for c in MMA_SHAPES if c[6] == 3 and c[8] == 1] + [
+    (60, 4, 16, 24, 28, 28, 3, 16, 1, 0.1),
+    (58, 3, 40, 72, 19, 23, 3, 24, 1, 0.05),     # ragged tiles, channel counts that are not multiples of 16
+    (59, 2, 24, 24, 8, 8, 3, 80, 1, 0.1),        # rank > 64: two rank chunks
+]
+
+
+@pytest.mark.parametrize("case", BWDF_MMA_SHAPES, ids=lambda c: "s%d" % c[0])
+def test_backward_filter_mma(case):
+    import paralleltnnlayers_b200 as P
+    (X, K0, K1, KH, KW, dU), pad = _inputs(case)
+    dX_, dK0, dK1, dKH, dKW, ddU = dev(X, K0, K1, KH, KW, dU)
+    got = P.cp4_conv2d_backward_filter(ddU, dX_, dK0, dK1, dKH, dKW, pad, flags=P.PATH_MMA)
+    ref = O.cp4_backward_filter(X, dU, K0, K1, KH, KW, pad)
+    for g, r, nm in zip(got, ref, ("dK0", "dK1", "dKH", "dKW")):
+        check(g, r, nm + " (mma)", rtol=1e-4, atol=1e-5 * max(1.0, float(np.abs(r).max())))
+    again = P.cp4_conv2d_backward_filter(ddU, dX_, dK0, dK1, dKH, dKW, pad, flags=P.PATH_MMA)
+    for a, b in zip(got, again):   # bitwise reproducible
+        assert torch.equal(a, b)
