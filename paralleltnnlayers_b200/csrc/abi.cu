@@ -267,7 +267,7 @@ int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, co
   float *dXin, *dUout, *dF, *ddU = nullptr, *ddX = nullptr, *ddK = nullptr, *ws = nullptr;
   const size_t b0 = (size_t)slot * 8;
   size_t wsb = 0;
-  if (bwd) wsb = b200cp_cp4_bwd_filter_workspace_bytes(s, flags);
+  if (bwd) wsb = b200cp_cp4_bwd_filter_workspace_bytes(s, 0);
   // a (re)allocation frees a buffer the other slot's queued work may still use: drain first
   {
     const size_t want[7] = {nX * 4, nU * 4, nK * 4, bwd ? nU * 4 : 0, bwd ? nX * 4 : 0, bwd ? nK * 4 : 0, 0};
@@ -312,7 +312,10 @@ int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, co
     B200CP_CUDA_OK(cudaEventRecord(ev[3], c.s_cmp));
     B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_out, ev[3], 0));
     B200CP_CUDA_OK(cudaMemcpyAsync(dX, ddX, nX * 4, cudaMemcpyDeviceToHost, c.s_out));
-    if (int rc = b200cp_cp4_bwd_filter(s, dXin, ddU, dK0, dK1, dKH, dKW, ddK, ws, wsb, c.s_cmp, flags)) return rc;
+    // the factor gradients have no tcgen05 kernel: a forced tcgen05 path applies to the two convolutions only
+    const int pf = path_of(flags);
+    const int fflags = (pf == B200CP_PATH_TC3X || pf == B200CP_PATH_TC1X) ? (flags & ~B200CP_PATH_MASK) : flags;
+    if (int rc = b200cp_cp4_bwd_filter(s, dXin, ddU, dK0, dK1, dKH, dKW, ddK, ws, wsb, c.s_cmp, fflags)) return rc;
     B200CP_CUDA_OK(cudaEventRecord(ev[4], c.s_cmp));
     B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_out, ev[4], 0));
     B200CP_CUDA_OK(cudaMemcpyAsync(dK_packed, ddK, nK * 4, cudaMemcpyDeviceToHost, c.s_out));
