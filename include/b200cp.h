@@ -84,10 +84,11 @@ int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const fl
 /* The same four factor gradients for callers that must not allocate device memory and have no
  * workspace to hand over: code running inside another framework's stream-ordered section, a
  * real-time loop, or a plugin whose host forbids cudaMalloc after initialisation.  It has no
- * counterpart in the reference.  The per-tile partial sums go to a fixed 8 MiB array inside the
+ * counterpart in the reference.  It runs the CUDA-core kernels (bit-identical to b200cp_cp4_bwd_filter with
+ * B200CP_PATH_SIMT).  The per-tile partial sums go to a fixed 8 MiB array inside the
  * library's device image (every GPU that loads the library holds it until the process exits), so
  *   - shapes whose partial sums need more than 8 MiB are refused with B200CP_ERR_UNSUPPORTED
- *     (b200cp_cp4_bwd_filter_workspace_bytes tells the need; e.g. N=32, C=T=64, 56x56, R=16 needs 5.5 MB);
+ *     (b200cp_cp4_bwd_filter_workspace_bytes with B200CP_PATH_SIMT tells the need; e.g. N=32, C=T=64, 56x56, R=16 needs 5.5 MB);
  *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating library routine;
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress);
  *     make that first call before any stream capture begins on that device;

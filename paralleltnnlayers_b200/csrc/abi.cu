@@ -159,8 +159,8 @@ int b200cp_cp4_bwd_data(const b200cp_tensor_shape* s, const float* dU, const flo
 }
 
 size_t b200cp_cp4_bwd_filter_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
-  (void)flags;
   if (check_shape(s, "b200cp_cp4_bwd_filter_workspace_bytes")) return 0;
+  if (path_of(flags) == B200CP_PATH_SIMT) return cp4_bwd_filter_simt_workspace(*s);
   return std::max(cp4_bwd_filter_simt_workspace(*s), cp4_bwd_filter_mma_workspace(*s));
 }
 
@@ -184,7 +184,10 @@ int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const fl
   for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);
-    const bool mma = (path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma)) && cp4_bwd_filter_mma_supported(a);
+    // measured: with at most 8 ranks and at most 128 channels the CUDA-core kernel is the faster one
+    const bool small = padded_rank(a.R) <= 8 && std::max(a.C, a.T) <= 128;
+    const bool mma = (path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma && !small)) &&
+                     cp4_bwd_filter_mma_supported(a);
     if (int rc = mma ? cp4_bwd_filter_mma_launch(a, static_cast<cudaStream_t>(stream))
                      : cp4_bwd_filter_simt_launch(a, static_cast<cudaStream_t>(stream)))
       return rc;

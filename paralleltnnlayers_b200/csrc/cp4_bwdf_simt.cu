@@ -348,16 +348,18 @@ __global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* 
   const int j = blockIdx.x * 32 + threadIdx.x, sl = threadIdx.y;
   const int per = (nparts + 31) / 32;
   const int i0 = sl * per, i1 = min(nparts, i0 + per);
-  float s0 = 0.f, s1 = 0.f;
+  float s0 = 0.f;
   if (j < nparam) {
-    int i = i0;
-    for (; i + 2 <= i1; i += 2) {
-      s0 += partial[(size_t)i * nparam + j];
-      s1 += partial[(size_t)(i + 1) * nparam + j];
+    // eight loads in flight, then added in index order
+    for (int i = i0; i < i1; i += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = i + u < i1 ? __ldg(partial + (size_t)(i + u) * nparam + j) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s0 += v[u];
     }
-    if (i < i1) s0 += partial[(size_t)i * nparam + j];
   }
-  red[sl][threadIdx.x] = s0 + s1;
+  red[sl][threadIdx.x] = s0;
   __syncthreads();
   if (sl == 0 && j < nparam) {
     float s = 0.f;

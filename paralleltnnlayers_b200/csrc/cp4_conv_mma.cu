@@ -462,10 +462,17 @@ bool plan_tile(const Cp4Args& a, const DeviceInfo& di, MmaGeom* out) {
       g.Y = a.Y; g.X = a.X;
       g.fch = std::min(kFChunk, (std::max(a.Cin, a.Cout) + 7) / 8 * 8);
       g.early_fout = std::max(a.Cin, a.Cout) <= g.fch ? 1 : 0;
-      const size_t smem = sizeof(float) * mma_smem_floats<RP>(g);
-      if ((int)smem > di.smem_optin) break;
-      const int cps_max = (RP <= 16 && g.MBW1 <= 2) ? 3 : 2;
-      const int cps = std::max(1, std::min(cps_max, (int)((228 * 1024) / (smem + 1024))));
+      const int cps_max = (RP <= 16 && g.MBW1 <= 2) ? 3 : 2;   // the kernel's launch bounds
+      size_t smem = sizeof(float) * mma_smem_floats<RP>(g);
+      int cps = (int)smem > di.smem_optin ? 0 : std::max(1, std::min(cps_max, (int)((228 * 1024) / (smem + 1024))));
+      if (g.early_fout) {   // one more CTA per SM is worth more than staging the output-side factors early
+        MmaGeom g2 = g;
+        g2.early_fout = 0;
+        const size_t smem2 = sizeof(float) * mma_smem_floats<RP>(g2);
+        const int cps2 = (int)smem2 > di.smem_optin ? 0 : std::max(1, std::min(cps_max, (int)((228 * 1024) / (smem2 + 1024))));
+        if (cps2 > cps) { g = g2; smem = smem2; cps = cps2; }
+      }
+      if (cps == 0) break;
       const long ctas = (long)a.N * ceil_div(a.H, TH) * ceil_div(a.W, TW);
       const long rounds = (ctas + (long)di.sm_count * cps - 1) / ((long)di.sm_count * cps);
       // issue slots per warp and tile: k-steps * blocks * (3 mma per rank block + fragment work), plus fixed work
@@ -473,9 +480,9 @@ bool plan_tile(const Cp4Args& a, const DeviceInfo& di, MmaGeom* out) {
       const double c3 = (double)ceil_div(a.Cout, 8) * (g.MBW3 * (3.0 * RP / 8 + 10) + 4.0 * RP / 8);
       const double c2 = (double)ceil_div(TH * ceil_div(TW, 8) * RP, kNT) * 90.0;
       const double tile = c1 + c2 + c3;
-      // measured on B200: throughput grows with the warps resident per SM (24 = three CTAs), and every round of
+      // measured on B200: throughput grows with the warps resident per SM, and every round of
       // CTAs pays the latency of one tile's dependent chain (copies, barriers, stores)
-      const double occupancy = 24.0 / (cps * kWarps);
+      const double occupancy = 32.0 / (cps * kWarps);
       const double cost = (double)ctas * tile / di.sm_count * occupancy + 1200.0 * rounds;
       if (cost < best_cost) { best_cost = cost; best = g; }
     }

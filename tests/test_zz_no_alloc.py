@@ -3,8 +3,8 @@
 Some hosts of this library cannot call cudaMalloc where they call us (a plugin slot inside
 another framework's stream-ordered region, a control loop with a fixed memory budget) and have no
 scratch buffer of their own to pass.  b200cp_cp4_bwd_filter_noalloc keeps its partial sums in a
-fixed array inside the library instead.  It must give exactly what b200cp_cp4_bwd_filter gives with
-a caller-provided workspace, call after call, although the array still holds the previous call's
+fixed array inside the library instead.  It runs the CUDA-core kernels and must give exactly what
+b200cp_cp4_bwd_filter gives on that path (B200CP_PATH_SIMT) with a caller-provided workspace, call after call, although the array still holds the previous call's
 partial sums.  This file is collected last on purpose: it has to pass both on its own and after
 every other test has used the library."""
 import ctypes as C
@@ -26,11 +26,11 @@ def _both(P, case):
     lib = P._lib.lib
     p = lambda a: C.c_void_p(a.data_ptr())
     nK = (T + Cc + 2 * F) * R
-    wsb = lib.b200cp_cp4_bwd_filter_workspace_bytes(C.byref(s), 0)
+    wsb = lib.b200cp_cp4_bwd_filter_workspace_bytes(C.byref(s), P.PATH_SIMT)
     ws = torch.empty(max(wsb, 4) // 4, device="cuda")
     ref = torch.full((nK,), float("nan"), device="cuda")
     got = torch.full((nK,), float("nan"), device="cuda")
-    P._lib.check(lib.b200cp_cp4_bwd_filter(C.byref(s), *[p(a) for a in t], p(ref), p(ws), wsb, None, 0))
+    P._lib.check(lib.b200cp_cp4_bwd_filter(C.byref(s), *[p(a) for a in t], p(ref), p(ws), wsb, None, P.PATH_SIMT))
     P._lib.check(lib.b200cp_cp4_bwd_filter_noalloc(C.byref(s), *[p(a) for a in t], p(got), None))
     torch.cuda.synchronize()
     oracle = np.concatenate([g.ravel() for g in O.cp4_backward_filter(X, dU, K0, K1, KH, KW, pad)])
