@@ -107,6 +107,23 @@ int b200cp_cp4_bwd_filter_full(const b200cp_tensor_shape* s, const float* X, con
 int b200cp_cp4_recompose(const b200cp_tensor_shape* s, const float* K0, const float* K1, const float* KH,
                          const float* KW, float* K, void* stream);
 
+/* ---- three-factor CP conv2d ------------------------------------------------ */
+
+/* U[n,t,h,w] = sum_r KT[t,r] sum_{y,x} KC[y,x,r] sum_c KCin[c,r] X[n,c,h+y-pad,w+x-pad]: the layer
+ * `conv2d_cp` defines (test/layers.py:265-283: 1x1 conv C->R, depthwise YxX conv, 1x1 conv R->T) and
+ * Conv2dCpFusedNchwKernelLauncher(U, K0, K1, K2, V) fuses (Kernels/cp_fused_nchw.cc, .cu).  Factors are
+ * [dim, R] like everywhere in this header: KCin[C,R] is the op's kernel0, KC[Y,X,R] its kernel1 and
+ * KT[T,R] its kernel2[R,T] transposed.  Runs on the mma.sync path (flags AUTO or MMA).
+ * The factor gradients come packed as [dKT (T*R) | dKCin (C*R) | dKC (Y*X*R)]; 3x3 filters with pad 1 only. */
+int b200cp_cp3_fwd(const b200cp_tensor_shape* s, const float* X, const float* KT, const float* KCin, const float* KC,
+                   float* U, void* stream, int flags);
+int b200cp_cp3_bwd_data(const b200cp_tensor_shape* s, const float* dU, const float* KT, const float* KCin,
+                        const float* KC, float* dX, void* stream, int flags);
+size_t b200cp_cp3_bwd_filter_workspace_bytes(const b200cp_tensor_shape* s, int flags);
+int b200cp_cp3_bwd_filter(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* KT,
+                          const float* KCin, const float* KC, float* dK_packed, void* workspace,
+                          size_t workspace_bytes, void* stream, int flags);
+
 /* Host-memory variants: copy in, run, copy out, synchronise.  They allocate
  * (and cache per device) their own device buffers.  `dK_packed` may be NULL in
  * the step call to skip nothing -- all three results are always produced. */

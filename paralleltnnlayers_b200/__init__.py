@@ -11,7 +11,8 @@ import importlib
 
 _LIB_NAMES = ("B200CPError", "LIB_PATH", "PATH_AUTO", "PATH_MMA", "PATH_SIMT", "PATH_TC1X", "PATH_TC3X", "TensorShape",
               "launch_count")
-_OPS_NAMES = ("CP4Conv2dFunction", "CPDenseFunction", "RCPConv2dFunction", "conv2d_rcp_fused_nchw",
+_OPS_NAMES = ("CP3Conv2dFunction", "conv2d_cp_fused_nchw", "cp3_conv2d_backward_data", "cp3_conv2d_backward_filter",
+              "cp3_conv2d_forward", "CP4Conv2dFunction", "CPDenseFunction", "RCPConv2dFunction", "conv2d_rcp_fused_nchw",
               "cp4_conv2d_backward_data", "cp4_conv2d_backward_filter", "cp4_conv2d_backward_filter_full",
               "cp4_conv2d_forward", "cp4_conv2d_nchw", "cp4_conv2d_step_host", "cp4_conv2d_step_host_submit",
               "cp4_conv2d_step_host_wait", "cp4recom", "dense_cp",
@@ -26,6 +27,6 @@ def __getattr__(name):
     if name in _OPS_NAMES or name == "ops":
         mod = importlib.import_module(".ops", __name__)
         return mod if name == "ops" else getattr(mod, name)
-    if name in ("build", "dist"):
+    if name in ("build", "dist", "layers", "sweep"):
         return importlib.import_module("." + name, __name__)
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

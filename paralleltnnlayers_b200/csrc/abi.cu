@@ -80,7 +80,7 @@ const bool g_auto_mma = [] {
 }();
 
 int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, const float* K1, const float* KH,
-             const float* KW, float* out, cudaStream_t st, int flags, bool backward) {
+             const float* KW, float* out, cudaStream_t st, int flags, bool backward, const float* KC = nullptr) {
   const int path = path_of(flags);
   Cp4Args a{};
   a.N = s->N; a.H = s->H; a.W = s->W; a.Y = s->Y; a.X = s->X; a.pad = s->pad;
@@ -88,12 +88,14 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
   a.Cout = backward ? s->C : s->T;
   a.Fin = backward ? K0 : K1;
   a.Fout = backward ? K1 : K0;
-  a.KH = KH; a.KW = KW; a.in = in; a.out = out;
+  a.KH = KH; a.KW = KW; a.KC = KC; a.in = in; a.out = out;
   a.flip = backward ? 1 : 0;
   a.Rs = s->Rank;
   a.R = s->Rank;
+  if (KC && path != B200CP_PATH_AUTO && path != B200CP_PATH_MMA)
+    return fail(B200CP_ERR_UNSUPPORTED, "the three-factor CP conv runs on the mma path only (flags AUTO or MMA)");
   if (path == B200CP_PATH_TC3X || path == B200CP_PATH_TC1X) return cp4_tc_launch(a, path == B200CP_PATH_TC3X ? 3 : 1, nullptr, st);
-  if (path == B200CP_PATH_AUTO && g_auto_tc) {
+  if (path == B200CP_PATH_AUTO && g_auto_tc && !KC) {
     DeviceInfo di;
     if (int rc = device_info(&di)) return rc;
     if (cp4_tc_supported(a, di, nullptr)) return cp4_tc_launch(a, 3, nullptr, st);
@@ -102,7 +104,7 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);
     a.accumulate = r0 > 0;
-    const bool mma = path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma);
+    const bool mma = KC || path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma);
     if (int rc = (mma ? cp4_mma_launch(a, st) : cp4_simt_launch(a, st))) return rc;
   }
   return B200CP_OK;
@@ -191,6 +193,52 @@ int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const fl
     if (int rc = mma ? cp4_bwd_filter_mma_launch(a, static_cast<cudaStream_t>(stream))
                      : cp4_bwd_filter_simt_launch(a, static_cast<cudaStream_t>(stream)))
       return rc;
+  }
+  return B200CP_OK;
+}
+
+// ---- three-factor CP conv ---------------------------------------------------------
+int b200cp_cp3_fwd(const b200cp_tensor_shape* s, const float* X, const float* KT, const float* KCin, const float* KC,
+                   float* U, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp3_fwd")) return rc;
+  if (int rc = check_ptrs("b200cp_cp3_fwd", {X, KT, KCin, KC, U})) return rc;
+  return run_conv(s, X, KT, KCin, nullptr, nullptr, U, static_cast<cudaStream_t>(stream), flags, false, KC);
+}
+
+int b200cp_cp3_bwd_data(const b200cp_tensor_shape* s, const float* dU, const float* KT, const float* KCin,
+                        const float* KC, float* dX, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp3_bwd_data")) return rc;
+  if (int rc = check_ptrs("b200cp_cp3_bwd_data", {dU, KT, KCin, KC, dX})) return rc;
+  return run_conv(s, dU, KT, KCin, nullptr, nullptr, dX, static_cast<cudaStream_t>(stream), flags, true, KC);
+}
+
+size_t b200cp_cp3_bwd_filter_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
+  (void)flags;
+  if (check_shape(s, "b200cp_cp3_bwd_filter_workspace_bytes")) return 0;
+  return cp4_bwd_filter_mma_workspace(*s);
+}
+
+int b200cp_cp3_bwd_filter(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* KT,
+                          const float* KCin, const float* KC, float* dK_packed, void* workspace,
+                          size_t workspace_bytes, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp3_bwd_filter")) return rc;
+  if (int rc = check_ptrs("b200cp_cp3_bwd_filter", {X, dU, KT, KCin, KC, dK_packed})) return rc;
+  if (s->Y != 3 || s->X != 3 || s->pad != 1)
+    return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp3_bwd_filter: 3x3 filters with pad 1 only (Y=%u X=%u pad=%u)", s->Y, s->X,
+                s->pad);
+  const int path = path_of(flags);
+  if (path != B200CP_PATH_AUTO && path != B200CP_PATH_MMA)
+    return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp3_bwd_filter: runs on the mma path only (flags AUTO or MMA)");
+  if (!workspace) return fail(B200CP_ERR_WORKSPACE, "b200cp_cp3_bwd_filter: workspace is null");
+  Cp4BwdFilterArgs a{};
+  a.N = s->N; a.C = s->C; a.T = s->T; a.H = s->H; a.W = s->W; a.F = 3; a.pad = 1;
+  a.Rs = s->Rank;
+  a.X = X; a.dU = dU; a.K0 = KT; a.K1 = KCin; a.KC = KC; a.dK = dK_packed;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
+    a.r0 = r0;
+    a.R = std::min(64u, s->Rank - r0);
+    if (int rc = cp4_bwd_filter_mma_launch(a, static_cast<cudaStream_t>(stream))) return rc;
   }
   return B200CP_OK;
 }

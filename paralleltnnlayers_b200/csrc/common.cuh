@@ -59,6 +59,7 @@ struct Cp4Args {
   int accumulate;
   const float *in, *Fin, *Fout, *KH, *KW;
   float* out;
+  const float* KC = nullptr;  // free [Y][X][Rs] spatial core (three-factor CP conv) instead of KH x KW; mma path only
 };
 int cp4_simt_launch(const Cp4Args& a, cudaStream_t st);
 // same arguments; channel contractions on the warp-level tensor path (mma.sync, three tf32 terms)
@@ -68,6 +69,7 @@ struct Cp4BwdFilterArgs {
   int N, C, T, H, W, F, pad;
   int R, Rs, r0;
   const float *X, *dU, *K0, *K1, *KH, *KW;
+  const float* KC = nullptr;  // free [3][3][Rs] core: dK is then packed [T*Rs | C*Rs | 9*Rs]; mma path only
   float* dK;  // packed [T*Rs | C*Rs | F*Rs | F*Rs]
   void* ws;
   size_t ws_bytes;

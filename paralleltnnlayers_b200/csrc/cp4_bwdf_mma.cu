@@ -16,6 +16,9 @@
 // the copies, which is the zero padding of the convolution.  Each CTA writes its partial gradients to
 // workspace[cta][...]; a second kernel sums the partials in CTA order, so results are bitwise reproducible.
 // Formulas: Cuda_kernels/cp4Conv2dBackwardFilter.cu:91-104,142-155,192-205,241-254.
+// CORE = true is the three-factor CP conv (Kernels/cp_fused_nchw.cu, test/layers.py:265-283): the per-rank 3x3
+// filter is a free [3,3,R] core instead of the outer product KH x KW, and its gradient has nine rows,
+// dKC[y, x, r] = sum_px Q[r, px] * P[r, px + (y-1, x-1)].
 #include <algorithm>
 #include <cstdlib>
 
@@ -36,7 +39,7 @@ struct BGeom {
   int N, C, T, H, W, R, Rs, r0;
   int TH, TW, TWh, HPX, tilesH, tilesW;
   int MBW;     // 16-pixel blocks of the halo tile per warp
-  int nparam;  // (T + C + 6) * R floats per partial
+  int nparam;  // (T + C + 6) * R floats per partial (T + C + 9 with a free 3x3 core)
   int pp;      // row pitch of the P and Q planes (odd)
 };
 
@@ -56,7 +59,7 @@ size_t bwdf_mma_smem_floats(const BGeom& g) {
   const size_t red = (size_t)kWarps * K::CHA * RP;
   const size_t planes = 2 * (size_t)RP * g.pp + (size_t)RP * (cols + 4);
   const size_t fac = 2 * (size_t)K::CHA * K::FIN;
-  return std::max(fifo, red) + planes + fac + 6 * RP + kNT * 6;
+  return std::max(fifo, red) + planes + fac + 9 * RP + kNT * 9;
 }
 
 // One pass over the channels of `src_n`.  CONTRACT: Out[r][px] = sum_ch F[ch][r] src[ch][px].
@@ -249,13 +252,14 @@ __device__ __forceinline__ void stream_pass(const BGeom& g, const float* __restr
   }
 }
 
-template <int RP, int MBW>
+template <int RP, int MBW, bool CORE>
 __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, const float* __restrict__ X,
                                                              const float* __restrict__ dU,
                                                              const float* __restrict__ K0,
                                                              const float* __restrict__ K1,
                                                              const float* __restrict__ KH,
-                                                             const float* __restrict__ KW, float* __restrict__ ws) {
+                                                             const float* __restrict__ KW,
+                                                             const float* __restrict__ KC, float* __restrict__ ws) {
   using K = BCfg<RP>;
   constexpr int WCOLS = MBW * 16, COLS = kWarps * WCOLS, CPL = (MBW + 1) / 2;
   constexpr int XP = COLS + 12, ZP = COLS + 4;
@@ -266,9 +270,9 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, con
   float* Qs = Ps + (size_t)RP * g.pp;        // [RP][pp]
   float* Zh = Qs + (size_t)RP * g.pp;        // [RP][ZP]  Z, later Qt; zero outside the tile's interior
   float* Fh = Zh + RP * ZP;                  // factor planes hi | lo of the current channel chunk
-  float* KHs = Fh + 2 * K::CHA * K::FIN;     // [3][RP]
-  float* KWs = KHs + 3 * RP;                 // [3][RP]
-  float* redk = KWs + 3 * RP;                // [kNT][6]
+  constexpr int NG = CORE ? 9 : 6;           // rows of the spatial-factor gradient
+  float* KHs = Fh + 2 * K::CHA * K::FIN;     // [3][RP] KH then [3][RP] KW, or the [9][RP] core
+  float* redk = KHs + 9 * RP;                // [kNT][NG]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   int b = blockIdx.x;
@@ -282,10 +286,10 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, con
   const float* dU_n = dU + (size_t)n * g.T * HW;
   float* part = ws + (size_t)blockIdx.x * g.nparam;
 
-  for (int i = tid; i < 6 * RP; i += kNT) {
-    const int r = i % RP, y = (i / RP) % 3;
-    const float* src = i < 3 * RP ? KH : KW;
-    KHs[i] = r < g.R ? __ldg(src + (size_t)y * g.Rs + g.r0 + r) : 0.f;   // KWs follows KHs
+  for (int i = tid; i < NG * RP; i += kNT) {
+    const int r = i % RP, row = i / RP;
+    const float* src = CORE ? KC + (size_t)row * g.Rs : (row < 3 ? KH + (size_t)row * g.Rs : KW + (size_t)(row - 3) * g.Rs);
+    KHs[i] = r < g.R ? __ldg(src + g.r0 + r) : 0.f;
   }
   for (int i = tid; i < RP * ZP / 4; i += kNT) reinterpret_cast<float4*>(Zh)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   // the slack columns of P and Q (read by the last strip of a row, never written) must be finite
@@ -317,9 +321,11 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, con
 
   // ---- stencil A: Z on the interior pixels ----
   const int r = tid % RP;   // fixed per thread (kNT is a multiple of RP)
-  float kh[3], kw[3];
+  float kh[3], kw[3], w9[9];   // separable factors, and the 3x3 filter of this thread's rank either way
 #pragma unroll
-  for (int t = 0; t < 3; ++t) { kh[t] = KHs[t * RP + r]; kw[t] = KWs[t * RP + r]; }
+  for (int t = 0; t < 3; ++t) { kh[t] = CORE ? 0.f : KHs[t * RP + r]; kw[t] = CORE ? 0.f : KHs[(3 + t) * RP + r]; }
+#pragma unroll
+  for (int t = 0; t < 9; ++t) w9[t] = CORE ? KHs[t * RP + r] : kh[t / 3] * kw[t % 3];
   constexpr int SW = 8;
   const int spr = (g.TW + SW - 1) / SW;
   const int items = g.TH * spr;
@@ -337,8 +343,9 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, con
       p += g.TWh;
 #pragma unroll
       for (int j = 0; j < SW; ++j) {
-        const float t = fmaf(kw[2], v[j + 2], fmaf(kw[1], v[j + 1], kw[0] * v[j]));
-        z[j] = fmaf(kh[dy], t, z[j]);
+        z[j] = fmaf(w9[dy * 3 + 0], v[j], z[j]);
+        z[j] = fmaf(w9[dy * 3 + 1], v[j + 1], z[j]);
+        z[j] = fmaf(w9[dy * 3 + 2], v[j + 2], z[j]);
       }
     }
     float* zd = Zh + r * ZP + (oy + 1) * g.TWh + x0 + 1;
@@ -353,16 +360,24 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, con
   __syncthreads();
 
   // ---- stencil B: Qt on the interior pixels, dKH, dKW ----
-  float dkh[3] = {0.f, 0.f, 0.f}, dkw[3] = {0.f, 0.f, 0.f};
+  float dk[NG];   // separable: dKH[0..2], dKW[0..2];  free core: dKC[y*3 + x]
+#pragma unroll
+  for (int t = 0; t < NG; ++t) dk[t] = 0.f;
   for (int it = tid / RP; it < items; it += kNT / RP) {
     const int oy = it / spr, x0 = (it - oy * spr) * SW;
-    float qt[SW], vc[3][SW];   // vc[x][j] = sum_y KH[y] P[oy+y][x0+j+x]
+    float qt[SW], qc[SW];
 #pragma unroll
-    for (int j = 0; j < SW; ++j) qt[j] = vc[0][j] = vc[1][j] = vc[2][j] = 0.f;
-    float qc[SW];
+    for (int j = 0; j < SW; ++j) qt[j] = 0.f;
     const float* p = Ps + (size_t)r * g.pp + oy * g.TWh + x0;
     const float* q = Qs + (size_t)r * g.pp + oy * g.TWh + x0;
-    float th_[3][SW];          // th_[y][j] = sum_x KW[x] P[oy+y][x0+j+x]
+    // the centre of the neighbourhood is the interior pixel; strips may run past the tile's last column
+#pragma unroll
+    for (int j = 0; j < SW; ++j) qc[j] = (x0 + j < g.TW) ? q[g.TWh + j + 1] : 0.f;
+    float vc[3][SW];           // separable: vc[x][j] = sum_y KH[y] P[oy+y][x0+j+x]
+    if (!CORE) {
+#pragma unroll
+      for (int j = 0; j < SW; ++j) vc[0][j] = vc[1][j] = vc[2][j] = 0.f;
+    }
 #pragma unroll
     for (int dy = 0; dy < 3; ++dy) {
       float v[SW + 2], u[SW + 2];
@@ -372,23 +387,28 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, con
       q += g.TWh;
 #pragma unroll
       for (int j = 0; j < SW; ++j) {
-        th_[dy][j] = fmaf(kw[2], v[j + 2], fmaf(kw[1], v[j + 1], kw[0] * v[j]));
-        vc[0][j] = fmaf(kh[dy], v[j], vc[0][j]);
-        vc[1][j] = fmaf(kh[dy], v[j + 1], vc[1][j]);
-        vc[2][j] = fmaf(kh[dy], v[j + 2], vc[2][j]);
-        // flipped taps: row dy of the neighbourhood carries KH[2-dy], column dx carries KW[2-dx]
-        const float tq_ = fmaf(kw[0], u[j + 2], fmaf(kw[1], u[j + 1], kw[2] * u[j]));
-        qt[j] = fmaf(kh[2 - dy], tq_, qt[j]);
-        if (dy == 1) qc[j] = (x0 + j < g.TW) ? u[j + 1] : 0.f;
+        // flipped taps: row dy of the neighbourhood carries filter row 2-dy, column dx carries filter column 2-dx
+        qt[j] = fmaf(w9[(2 - dy) * 3 + 2], u[j], qt[j]);
+        qt[j] = fmaf(w9[(2 - dy) * 3 + 1], u[j + 1], qt[j]);
+        qt[j] = fmaf(w9[(2 - dy) * 3 + 0], u[j + 2], qt[j]);
+        if (CORE) {
+          dk[dy * 3 + 0] = fmaf(qc[j], v[j], dk[dy * 3 + 0]);
+          dk[dy * 3 + 1] = fmaf(qc[j], v[j + 1], dk[dy * 3 + 1]);
+          dk[dy * 3 + 2] = fmaf(qc[j], v[j + 2], dk[dy * 3 + 2]);
+        } else {
+          const float th_ = fmaf(kw[2], v[j + 2], fmaf(kw[1], v[j + 1], kw[0] * v[j]));   // sum_x KW[x] P[oy+dy][..+x]
+          dk[dy] = fmaf(qc[j], th_, dk[dy]);
+          vc[0][j] = fmaf(kh[dy], v[j], vc[0][j]);
+          vc[1][j] = fmaf(kh[dy], v[j + 1], vc[1][j]);
+          vc[2][j] = fmaf(kh[dy], v[j + 2], vc[2][j]);
+        }
       }
     }
+    if (!CORE) {
 #pragma unroll
-    for (int j = 0; j < SW; ++j) {
+      for (int j = 0; j < SW; ++j)
 #pragma unroll
-      for (int t = 0; t < 3; ++t) {
-        dkh[t] = fmaf(qc[j], th_[t][j], dkh[t]);
-        dkw[t] = fmaf(qc[j], vc[t][j], dkw[t]);
-      }
+        for (int t = 0; t < 3; ++t) dk[3 + t] = fmaf(qc[j], vc[t][j], dk[3 + t]);
     }
     float* zd = Zh + r * ZP + (oy + 1) * g.TWh + x0 + 1;
 #pragma unroll
@@ -396,13 +416,13 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_mma_kernel(const BGeom g, con
       if (x0 + j < g.TW) zd[j] = qt[j];
   }
 #pragma unroll
-  for (int t = 0; t < 3; ++t) { redk[tid * 6 + t] = dkh[t]; redk[tid * 6 + 3 + t] = dkw[t]; }
+  for (int t = 0; t < NG; ++t) redk[tid * NG + t] = dk[t];
   __syncthreads();
-  for (int i = tid; i < 6 * RP; i += kNT) {
+  for (int i = tid; i < NG * RP; i += kNT) {
     // threads rr + RP*k hold the sums of rank rr: add them in k order
-    const int rr = i % RP, t = i / RP;   // t: 0..2 dKH rows, 3..5 dKW rows
+    const int rr = i % RP, t = i / RP;
     float s = 0.f;
-    for (int k = 0; k < kNT / RP; ++k) s += redk[(rr + RP * k) * 6 + t];
+    for (int k = 0; k < kNT / RP; ++k) s += redk[(rr + RP * k) * NG + t];
     if (rr < g.R) part[(size_t)(g.T + g.C + t) * g.R + rr] = s;
   }
 
@@ -450,18 +470,23 @@ bool plan_bwdf(const Cp4BwdFilterArgs& a, const DeviceInfo& di, BGeom* out, size
   return true;
 }
 
-template <int RP, int MBW>
-int launch_bwdf(const BGeom& g, size_t smem, const Cp4BwdFilterArgs& a, cudaStream_t st) {
-  auto kern = cp4_bwdf_mma_kernel<RP, MBW>;
+template <int RP, int MBW, bool CORE>
+int launch_bwdf_core(const BGeom& g, size_t smem, const Cp4BwdFilterArgs& a, cudaStream_t st) {
+  auto kern = cp4_bwdf_mma_kernel<RP, MBW, CORE>;
   B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const long ctas = (long)a.N * g.tilesH * g.tilesW;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: too many tiles");
   const size_t need = (size_t)ctas * g.nparam * sizeof(float);
   if (a.ws_bytes < need)
     return fail(B200CP_ERR_WORKSPACE, "cp4 bwd-filter: workspace of %zu bytes needed, %zu given", need, a.ws_bytes);
-  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.X, a.dU, a.K0, a.K1, a.KH, a.KW, (float*)a.ws);
+  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.X, a.dU, a.K0, a.K1, a.KH, a.KW, a.KC, (float*)a.ws);
   B200CP_LAUNCH_OK("cp4_bwdf_mma_kernel");
   return cp4_reduce_partials_launch((const float*)a.ws, (int)ctas, g.nparam, a.R, a.Rs, a.r0, a.dK, st);
+}
+
+template <int RP, int MBW>
+int launch_bwdf(const BGeom& g, size_t smem, const Cp4BwdFilterArgs& a, cudaStream_t st) {
+  return a.KC ? launch_bwdf_core<RP, MBW, true>(g, smem, a, st) : launch_bwdf_core<RP, MBW, false>(g, smem, a, st);
 }
 
 template <int RP>
@@ -471,7 +496,7 @@ int run_bwdf(const Cp4BwdFilterArgs& a, const DeviceInfo& di, cudaStream_t st) {
   if (!plan_bwdf<RP>(a, di, &g, &smem)) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter (mma path): no tile fits in shared memory");
   g.N = a.N; g.C = a.C; g.T = a.T; g.H = a.H; g.W = a.W; g.R = a.R; g.Rs = a.Rs; g.r0 = a.r0;
   g.tilesH = ceil_div(a.H, g.TH); g.tilesW = ceil_div(a.W, g.TW);
-  g.nparam = (a.T + a.C + 6) * a.R;
+  g.nparam = (a.T + a.C + (a.KC ? 9 : 6)) * a.R;
   if (getenv("B200CP_DEBUG"))
     fprintf(stderr, "[b200cp] bwd-filter mma tile TH=%d TW=%d blocks per warp %d smem=%zu RP=%d\n", g.TH, g.TW, g.MBW, smem, RP);
   switch (g.MBW) {
@@ -504,7 +529,8 @@ size_t cp4_bwd_filter_mma_workspace(const b200cp_tensor_shape& s) {
     const bool ok = rp <= 8 ? plan_bwdf<8>(a, di, &g, &smem) : rp == 16 ? plan_bwdf<16>(a, di, &g, &smem)
                     : rp == 32 ? plan_bwdf<32>(a, di, &g, &smem) : plan_bwdf<64>(a, di, &g, &smem);
     if (!ok) return 0;
-    need = std::max(need, (size_t)s.N * ceil_div(s.H, g.TH) * ceil_div(s.W, g.TW) * ((size_t)s.T + s.C + 6) * rc * sizeof(float));
+    // nine spatial rows cover both the separable factors (six) and the free core of the three-factor layer
+    need = std::max(need, (size_t)s.N * ceil_div(s.H, g.TH) * ceil_div(s.W, g.TW) * ((size_t)s.T + s.C + 9) * rc * sizeof(float));
   }
   return need;
 }

@@ -73,7 +73,8 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
                                                              const float* __restrict__ Fin,
                                                              const float* __restrict__ Fout,
                                                              const float* __restrict__ KH,
-                                                             const float* __restrict__ KW, float* __restrict__ out) {
+                                                             const float* __restrict__ KW,
+                                                             const float* __restrict__ KC, float* __restrict__ out) {
   constexpr int NB = RP / 8;                    // rank blocks (n of phase 1, k of phase 3)
   constexpr int XP = kWarps * MBW1 * 16 + 8;    // FIFO row pitch:  8 mod 32
   constexpr int ZP = kWarps * MBW3 * 16 + 8;    // Z row pitch:     8 mod 32
@@ -105,7 +106,10 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
   for (int i = tid; i < g.Y * g.X * RP; i += kNT) {
     const int r = i % RP, yx = i / RP, y = yx / g.X, x = yx - y * g.X;
     const int yy = g.flip ? g.Y - 1 - y : y, xx = g.flip ? g.X - 1 - x : x;
-    Ws[i] = r < g.R ? __ldg(KH + (size_t)yy * g.Rs + g.r0 + r) * __ldg(KW + (size_t)xx * g.Rs + g.r0 + r) : 0.f;
+    // a free core [Y][X][Rs] (three-factor CP conv) takes the place of the outer product KH x KW
+    Ws[i] = r >= g.R ? 0.f
+            : KC   ? __ldg(KC + (size_t)(yy * g.X + xx) * g.Rs + g.r0 + r)
+                   : __ldg(KH + (size_t)yy * g.Rs + g.r0 + r) * __ldg(KW + (size_t)xx * g.Rs + g.r0 + r);
   }
 
   auto stage_fout = [&](int t0) {
@@ -417,7 +421,7 @@ int launch_mma(const MmaGeom& g, const Cp4Args& a, cudaStream_t st) {
   B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const long ctas = (long)a.N * g.tilesH * g.tilesW;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4: too many tiles");
-  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.in, a.Fin, a.Fout, a.KH, a.KW, a.out);
+  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.in, a.Fin, a.Fout, a.KH, a.KW, a.KC, a.out);
   B200CP_LAUNCH_OK("cp4_conv_mma_kernel");
   return B200CP_OK;
 }

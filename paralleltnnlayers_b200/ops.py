@@ -174,6 +174,80 @@ def debug_cp4_tc(Input, FT, FC, FY, FX, pad=1, terms=3, p_floats=0):
     return out, P
 
 
+# ---- three-factor CP conv -----------------------------------------------------
+def _shape3(inp, KT, KCin, KC, pad, in_is_upstream=False):
+    if inp.dim() != 4 or KT.dim() != 2 or KCin.dim() != 2 or KC.dim() != 3:
+        raise ValueError("expected input [N,ch,H,W], KT [T,R], KCin [C,R], KC [Y,X,R]")
+    R = KT.shape[1]
+    if KCin.shape[1] != R or KC.shape[2] != R:
+        raise ValueError("all factors must have the same rank")
+    if inp.shape[1] != (KT.shape[0] if in_is_upstream else KCin.shape[0]):
+        raise ValueError("channel count of the input does not match the factor")
+    return tensor_shape(inp.shape[0], KCin.shape[0], inp.shape[2], inp.shape[3], KT.shape[0], KC.shape[0], KC.shape[1],
+                        R, pad)
+
+
+def cp3_conv2d_forward(Input, KT, KCin, KC, pad=1, flags=0):
+    """Three-factor CP conv (``b200cp_cp3_fwd``): ``KT [T,R]``, ``KCin [C,R]``, free core ``KC [Y,X,R]``."""
+    Input, KT, KCin, KC = (_dev(t, n) for t, n in ((Input, "Input"), (KT, "KT"), (KCin, "KCin"), (KC, "KC")))
+    s = _shape3(Input, KT, KCin, KC, pad)
+    out = torch.empty((s.N, s.T, s.H, s.W), device=Input.device, dtype=torch.float32)
+    with torch.cuda.device(Input.device):
+        check(lib.b200cp_cp3_fwd(C.byref(s), _p(Input), _p(KT), _p(KCin), _p(KC), _p(out), _stream(), flags))
+    return out
+
+
+def cp3_conv2d_backward_data(Upstream, KT, KCin, KC, pad=1, flags=0):
+    Upstream, KT, KCin, KC = (_dev(t, n) for t, n in ((Upstream, "Upstream"), (KT, "KT"), (KCin, "KCin"), (KC, "KC")))
+    s = _shape3(Upstream, KT, KCin, KC, pad, in_is_upstream=True)
+    out = torch.empty((s.N, s.C, s.H, s.W), device=Upstream.device, dtype=torch.float32)
+    with torch.cuda.device(Upstream.device):
+        check(lib.b200cp_cp3_bwd_data(C.byref(s), _p(Upstream), _p(KT), _p(KCin), _p(KC), _p(out), _stream(), flags))
+    return out
+
+
+def cp3_conv2d_backward_filter(dLdO, In, KT, KCin, KC, pad=1, flags=0):
+    """Factor gradients (dKT, dKCin, dKC) of the three-factor CP conv; 3x3 cores with pad 1."""
+    dLdO, In, KT, KCin, KC = (_dev(t, n) for t, n in
+                              ((dLdO, "dLdO"), (In, "In"), (KT, "KT"), (KCin, "KCin"), (KC, "KC")))
+    s = _shape3(In, KT, KCin, KC, pad)
+    R = s.Rank
+    nT, nC, nS = s.T * R, s.C * R, s.Y * s.X * R
+    dK = torch.empty(nT + nC + nS, device=In.device, dtype=torch.float32)
+    with torch.cuda.device(In.device):
+        wsb = lib.b200cp_cp3_bwd_filter_workspace_bytes(C.byref(s), flags)
+        ws = torch.empty(max(wsb, 4) // 4, device=In.device, dtype=torch.float32)
+        check(lib.b200cp_cp3_bwd_filter(C.byref(s), _p(In), _p(dLdO), _p(KT), _p(KCin), _p(KC), _p(dK), _p(ws),
+                                        ws.numel() * 4, _stream(), flags))
+    return dK[:nT].view(s.T, R), dK[nT:nT + nC].view(s.C, R), dK[nT + nC:].view(s.Y, s.X, R)
+
+
+def conv2d_cp_fused_nchw(U, K0, K1, K2, flags=0):
+    """``Conv2dCpFusedNchw`` (Kernels/cp_fused_nchw.cc): K0 [C,R], K1 [FH,FW,R], K2 [R,T], SAME padding
+    (test/test_conv2d_cp.py:33-38)."""
+    return cp3_conv2d_forward(U, K2.t().contiguous(), K0, K1, pad=(K1.shape[0] - 1) // 2, flags=flags)
+
+
+class CP3Conv2dFunction(torch.autograd.Function):
+    """y = three-factor CP conv2d(x; KT, KCin, KC) with the fused backward kernels."""
+
+    @staticmethod
+    def forward(ctx, x, KT, KCin, KC, pad=1):
+        ctx.save_for_backward(x, KT, KCin, KC)
+        ctx.pad = pad
+        return cp3_conv2d_forward(x, KT, KCin, KC, pad)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, KT, KCin, KC = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = cp3_conv2d_backward_data(dy, KT, KCin, KC, ctx.pad) if ctx.needs_input_grad[0] else None
+        g = (None,) * 3
+        if any(ctx.needs_input_grad[1:4]):
+            g = cp3_conv2d_backward_filter(dy, x, KT, KCin, KC, ctx.pad)
+        return (dx, *g, None)
+
+
 # ---- TF custom-op order -----------------------------------------------------
 def cp4_conv2d_nchw(U, K0, K1, K2, K3, flags=0):
     """``Cp4Conv2dNchw`` (Kernels/cp4_conv_nchw.cc:6-13): K0 [C,R], K1 [FH,R], K2 [FW,R], K3 [T,R],

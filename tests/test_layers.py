@@ -1,0 +1,89 @@
+"""The nn.Module layer: rank rules (CPU) and forward / backward through the fused kernels (GPU)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cp_oracle as O
+
+
+def test_rank_rules_follow_the_reference():
+    from paralleltnnlayers_b200 import layers as L
+    # generate_shape (test/layers.py:22-48)
+    assert L.generate_shape(4096, base=16) == [16, 16, 16]
+    assert L.generate_shape(64, base=16) == [16, 4]
+    assert L.generate_shape(32, base=16) == [32]              # remainder folded into the first mode
+    assert L.generate_shape(256, order=2) == [16, 16]
+    assert L.generate_shape(128, order=2) == [16, 8]
+    assert L.generate_shape(128, order=2, reverse=True) == [8, 16]
+    with pytest.raises(ValueError):
+        L.generate_shape(48, order=2)
+    # generate_params_dense_cp (test/layers.py:491-507): 4096 x 4096 at rate 0.1
+    p = L.params_dense_cp(4096, 4096, 0.1)
+    assert p == {"input_shape": [16, 16, 16], "output_shape": [16, 16, 16], "rank": 2185}
+    # generate_params_conv2d_rcp (test/layers.py:816-851): 256 -> 256, 3x3, rate 0.1
+    p = L.params_conv2d_rcp(256, 256, 3, 0.1)
+    assert p == {"input_shape": [16, 16], "output_shape": [16, 16], "rank": 843}
+    assert L.params_conv2d_rcp(64, 64, 1, 0.5)["rank"] == int(np.ceil(0.5 * 4096 / 32))
+    assert L.params_conv2d_cp4(64, 64, 3, 0.1)["rank"] == int(np.ceil(0.1 * 9 * 4096 / 134))
+    assert L.params_conv2d_cp(64, 64, 3, 0.1)["rank"] == int(np.ceil(0.1 * 9 * 4096 / 137))   # test/layers.py:296-304
+
+
+@pytest.mark.gpu
+def test_modules_forward_backward():
+    from paralleltnnlayers_b200 import layers as L
+    from tests.gpu_util import check
+    torch.manual_seed(0)
+    # CP4
+    m = L.CP4Conv2d(8, 6, 3, rank=4, bias=True).cuda()
+    x = torch.randn(2, 8, 9, 10, device="cuda", requires_grad=True)
+    y = m(x)
+    f = [p.detach().cpu().numpy() for p in (m.FT, m.FC, m.FY, m.FX)]
+    ref = O.cp4_forward(x.detach().cpu().numpy(), *f, 1) + m.bias.detach().cpu().numpy().reshape(1, -1, 1, 1)
+    check(y, ref, "CP4Conv2d forward")
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    check(x.grad, O.cp4_backward_data(dy.cpu().numpy(), *f, 1), "CP4Conv2d dX")
+    for p_, r in zip((m.FT, m.FC, m.FY, m.FX), O.cp4_backward_filter(x.detach().cpu().numpy(), dy.cpu().numpy(), *f, 1)):
+        check(p_.grad, r, "CP4Conv2d dK", atol=1e-4)
+    check(m.bias.grad, dy.sum(dim=(0, 2, 3)).cpu().numpy(), "CP4Conv2d dbias", atol=1e-4)
+    # three-factor CP
+    m = L.CPConv2d(8, 6, 3, rank=5).cuda()
+    x = torch.randn(2, 8, 9, 10, device="cuda", requires_grad=True)
+    y = m(x)
+    f = [p.detach().cpu().numpy() for p in (m.KT, m.KCin, m.KC)]
+    check(y, O.cp3_forward(x.detach().cpu().numpy(), *f, 1), "CPConv2d forward")
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    rX, *rK = O.cp3_backward(x.detach().cpu().numpy(), dy.cpu().numpy(), *f, 1)
+    check(x.grad, rX, "CPConv2d dX")
+    for p_, r in zip((m.KT, m.KCin, m.KC), rK):
+        check(p_.grad, r, "CPConv2d dK", atol=1e-4)
+    # rCP with the mode sizes of the rank rule
+    m = L.RCPConv2d(16, 16, 3, rank=5).cuda()
+    assert m.input_shape == [4, 4] and m.output_shape == [4, 4]
+    x = torch.randn(2, 16, 7, 6, device="cuda", requires_grad=True)
+    y = m(x)
+    A = [p.detach().cpu().numpy() for p in m.factors]
+    S = m.core.detach().cpu().numpy()
+    check(y, O.rcp_forward(x.detach().cpu().numpy(), A, S), "RCPConv2d forward", atol=1e-4)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    rX, rA, rS = O.rcp_backward(x.detach().cpu().numpy(), dy.cpu().numpy(), A, S)
+    check(x.grad, rX, "RCPConv2d dX", atol=1e-4)
+    for p_, r in zip(m.factors, rA):
+        check(p_.grad, r, "RCPConv2d dA", atol=1e-4)
+    check(m.core.grad, rS, "RCPConv2d dS", atol=1e-4)
+    # dense
+    m = L.CPDense(64, 64, rate=0.05, bias=True).cuda()
+    assert m.input_shape == [16, 4] and m.output_shape == [8, 8]
+    x = torch.randn(3, 5, 64, device="cuda", requires_grad=True)
+    y = m(x)
+    F = [p.detach().cpu().numpy() for p in m.factors]
+    ref = O.dense_cp_forward(x.detach().cpu().numpy().reshape(15, 64), F).reshape(3, 5, 64) + m.bias.detach().cpu().numpy()
+    check(y, ref, "CPDense forward", atol=1e-4)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    rX, rF = O.dense_cp_backward(x.detach().cpu().numpy().reshape(15, 64), dy.cpu().numpy().reshape(15, 64), F)
+    check(x.grad.reshape(15, 64), rX, "CPDense dX", atol=1e-4)
+    for p_, r in zip(m.factors, rF):
+        check(p_.grad, r, "CPDense dF", atol=1e-4)

@@ -138,3 +138,22 @@ def test_oracle_matches_reference_golden():
         g = O.cp4_backward_filter(X, dU, K0, K1, KH, KW, pad)
         for nm, a in zip(("dK0", "dK1", "dKH", "dKW"), g):
             np.testing.assert_allclose(gold[f"{name}_{nm}"], a, rtol=1e-3, atol=1e-4, err_msg=f"{name}_{nm}")
+
+
+def test_cp3_oracle_matches_the_reference_formula_and_autograd():
+    """The three-factor filter of test/test_conv2d_cp.py:19, evaluated with the reference's own einsum string,
+    and float64 autograd of the dense conv for the gradients."""
+    import torch
+    rng = np.random.default_rng(11)
+    K0 = rng.uniform(size=(1, 1, 16, 6)); K1 = rng.uniform(size=(3, 3, 6, 1)); K2 = rng.uniform(size=(1, 1, 6, 16))
+    Kcp = np.einsum('llar,ijrl,llrx->ijax', K0, K1, K2)                       # HWIO, as the reference builds it
+    mine = O.cp3_recompose(K2.reshape(6, 16).T, K0.reshape(16, 6), K1.reshape(3, 3, 6))   # [T,C,Y,X]
+    np.testing.assert_allclose(mine, Kcp.transpose(3, 2, 0, 1), rtol=1e-12, atol=1e-12)
+    X = rng.normal(size=(2, 5, 7, 6)); KT = rng.normal(size=(4, 3)); KCin = rng.normal(size=(5, 3))
+    KC = rng.normal(size=(3, 3, 3)); dU = rng.normal(size=(2, 4, 7, 6))
+    t = [torch.tensor(a, dtype=torch.float64, requires_grad=True) for a in (X, KT, KCin, KC)]
+    y = torch.nn.functional.conv2d(t[0], torch.einsum('tr,cr,yxr->tcyx', t[1], t[2], t[3]), padding=1)
+    np.testing.assert_allclose(y.detach().numpy(), O.cp3_forward(X, KT, KCin, KC, 1), rtol=1e-10, atol=1e-10)
+    y.backward(torch.tensor(dU))
+    for a, b in zip([x.grad.numpy() for x in t], O.cp3_backward(X, dU, KT, KCin, KC, 1)):
+        np.testing.assert_allclose(a, b, rtol=1e-10, atol=1e-10)
