@@ -1,6 +1,11 @@
 """Kernel timings of every layer family at the sizes of the benchmark configurations.
 
     python -m paralleltnnlayers_b200.sweep [cp4] [rcp] [dense] [--reps 12] [--json]
+    python -m paralleltnnlayers_b200.sweep --shapes FILE [--ranks 1,2,4,8,16] [--reps 47] [--out results.csv]
+
+The second form reads a shape list in the reference's format (``N C H W pad T Y X`` per line, ``#`` comments;
+Cuda_kernels/bench/tensors*.txt) and writes the CSV its ``BenchBothTime`` writes (bench/BenchBothTime.cu:84-104):
+the shape, then the mean forward time in microseconds for each CP rank (the cuDNN column is left out).
 
 Inputs live on the device; every call of a timed kernel uses the next of several distinct buffer sets (more
 than the L2 holds), the calls of one measurement are captured in one CUDA graph so that there are no host gaps,
@@ -115,12 +120,63 @@ def sweep_dense(P, reps, rows):
                  "hbm_floor_us": 2 * X.numel() * 4 / 6.45e12 * 1e6})
 
 
+def read_shapes(path):
+    """Unique shapes of a reference-format list, in the order ``tensor_shape::operator<`` gives them
+    (Cuda_kernels/Tensor.cuh:10-25: lexicographic over N, C, H, W, pad, T, Y, X)."""
+    shapes = set()
+    with open(path) as f:
+        for line in f:
+            line = line.split("#", 1)[0].strip()
+            if not line:
+                continue
+            v = [int(x) for x in line.replace("|", " ").split()]
+            if len(v) < 8:
+                raise ValueError(f"shape line needs N C H W pad T Y X: {line!r}")
+            shapes.add(tuple(v[:8]))
+    return sorted(shapes)
+
+
+def bench_shapes(P, path, ranks, reps, out):
+    lines = []
+    for (N, C, H, W, pad, T, Y, X) in read_shapes(path):
+        rng = np.random.default_rng(1234)     # the reference seeds its generator with 1234 (test_cp4Conv.cpp.cu)
+        x = _dev(rng.uniform(0, 1, size=(N, C, H, W)))
+        xs = _sets(x)
+        n = len(xs)
+        cols = []
+        for R in ranks:
+            K = [_dev(rng.uniform(0, 1, size=(d, R))) for d in (T, C, Y, X)]
+            try:
+                cols.append("%.3f" % timeit(lambda i: P.cp4_conv2d_forward(xs[i % n], *K, pad), reps))
+            except P.B200CPError as e:
+                cols.append("nan")
+                sys.stderr.write(f"[sweep] {N} {C} {H} {W} {pad} {T} {Y} {X} rank {R}: {e}\n")
+        lines.append(f"{N} {C} {H} {W} {pad} {T} {Y} {X}, " + ", ".join(cols))
+        del xs
+        torch.cuda.empty_cache()
+    text = "\n".join(lines) + "\n"
+    if out:
+        with open(out, "w") as f:
+            f.write(text)
+    else:
+        sys.stdout.write(text)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("which", nargs="*", help="any of cp4, rcp, dense (default: all)")
     ap.add_argument("--reps", type=int, default=12)
     ap.add_argument("--json", action="store_true", help="one JSON object per line instead of text")
+    ap.add_argument("--shapes", help="shape list in the reference's format: time the CP4 forward per shape and rank")
+    ap.add_argument("--ranks", default="1,2,4,8,16", help="CP ranks of the --shapes run (the reference's 1..16)")
+    ap.add_argument("--out", help="CSV file of the --shapes run (default: stdout)")
     args = ap.parse_args(argv)
+    if args.shapes:
+        import paralleltnnlayers_b200 as P
+        assert torch.cuda.is_available(), "the sweep needs a CUDA device"
+        bench_shapes(P, args.shapes, [int(r) for r in args.ranks.split(",")], 47 if args.reps == 12 else args.reps,
+                     args.out)
+        return 0
     args.which = args.which or ["cp4", "rcp", "dense"]
     for w in args.which:
         if w not in ("cp4", "rcp", "dense"):

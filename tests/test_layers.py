@@ -87,3 +87,23 @@ def test_modules_forward_backward():
     check(x.grad.reshape(15, 64), rX, "CPDense dX", atol=1e-4)
     for p_, r in zip(m.factors, rF):
         check(p_.grad, r, "CPDense dF", atol=1e-4)
+
+
+def test_shape_list_reader(tmp_path):
+    from paralleltnnlayers_b200.sweep import read_shapes
+    f = tmp_path / "shapes.txt"
+    f.write_text("# N C H W pad | T Y X\n1 256 27 27 1   384 3 3\n\n1  48 55 55 2 | 256 5 5  # comment\n1 256 27 27 1 384 3 3\n")
+    assert read_shapes(str(f)) == [(1, 48, 55, 55, 2, 256, 5, 5), (1, 256, 27, 27, 1, 384, 3, 3)]
+
+
+@pytest.mark.gpu
+def test_shape_list_bench_writes_the_reference_csv(tmp_path):
+    import paralleltnnlayers_b200 as P
+    from paralleltnnlayers_b200.sweep import bench_shapes
+    f = tmp_path / "shapes.txt"
+    f.write_text("1 48 27 27 2 64 5 5\n1 16 13 13 1 32 3 3\n")
+    out = tmp_path / "r.csv"
+    bench_shapes(P, str(f), [1, 4, 16], 3, str(out))
+    rows = out.read_text().strip().split("\n")
+    assert rows[0].startswith("1 16 13 13 1 32 3 3, ") and rows[1].startswith("1 48 27 27 2 64 5 5, ")
+    assert all(len(r.split(", ")) == 4 and all(float(v) > 0 for v in r.split(", ")[1:]) for r in rows)
