@@ -162,6 +162,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc3x", "mma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--separate", action="store_true",
+                    help="step = the three entry points one after the other instead of b200cp_cp4_step")
     ap.add_argument("--watchdog", type=int, default=420, help="seconds after which a stuck run dumps its stacks and exits")
     args = ap.parse_args()
     import faulthandler
@@ -224,10 +226,38 @@ def main():
         x, du, u, dx = sets[i % NSETS]
         P._lib.check(lib.b200cp_cp4_bwd_filter(C.byref(s), ptr(x), ptr(du), *fp, ptr(dK), ptr(ws), wsb, st, flags_f))
 
+    # b200cp_cp4_step: the same three results from one call; the two convolutions leave their rank planes in the
+    # workspace and the factor gradients start from those (3x3 filters on the default path)
+    shared = not args.separate and args.path in ("auto", "mma")
+    wsb_step = lib.b200cp_cp4_step_workspace_bytes(C.byref(s), flags)
+    ws_step = torch.empty(max(wsb_step, 4) // 4, device="cuda")
+    plane_floats = n * c["R"] * HW
+    Pp, Qp = ws_step[:plane_floats], ws_step[plane_floats + 64:2 * plane_floats + 64]   # scratch for the per-kernel runs
+    wsb_sv = lib.b200cp_cp4_bwd_filter_saved_workspace_bytes(C.byref(s), flags) if shared else 0
+    ws_sv = torch.empty(max(wsb_sv, 4) // 4, device="cuda")
+
+    def k_fwd_save(i, st):
+        x, du, u, dx = sets[i % NSETS]
+        P._lib.check(lib.b200cp_cp4_fwd_save(C.byref(s), ptr(x), *fp, ptr(u), ptr(Pp), st, flags))
+
+    def k_bwdd_save(i, st):
+        x, du, u, dx = sets[i % NSETS]
+        P._lib.check(lib.b200cp_cp4_bwd_data_save(C.byref(s), ptr(du), *fp, ptr(dx), ptr(Qp), st, flags))
+
+    def k_bwdf_saved(i, st):
+        x, du, u, dx = sets[i % NSETS]
+        P._lib.check(lib.b200cp_cp4_bwd_filter_saved(C.byref(s), ptr(x), ptr(du), ptr(Pp), ptr(Qp), fp[2], fp[3], ptr(dK),
+                                                     ptr(ws_sv), wsb_sv, st, flags))
+
     def step(i, st):
-        k_fwd(i, st)
-        k_bwdd(i, st)
-        k_bwdf(i, st)
+        if shared:
+            x, du, u, dx = sets[i % NSETS]
+            P._lib.check(lib.b200cp_cp4_step(C.byref(s), ptr(x), ptr(du), *fp, ptr(u), ptr(dx), ptr(dK), ptr(ws_step),
+                                             wsb_step, st, flags))
+        else:
+            k_fwd(i, st)
+            k_bwdd(i, st)
+            k_bwdf(i, st)
         if dist is not None:
             dist.all_reduce(dK)
 
@@ -276,7 +306,13 @@ def main():
     ms = e0.elapsed_time(e1)
     # the three kernels on their own, K back-to-back launches each, same rotating buffers, same run
     kt = []
-    for fn in (k_fwd, k_bwdd, k_bwdf):
+    kernels = [("cp4_fwd", k_fwd, 0), ("cp4_bwd_data", k_bwdd, 0), ("cp4_bwd_filter", k_bwdf, 0)]
+    if shared:   # the kernels of the step: extra bytes = the rank planes written / read
+        kernels += [("cp4_fwd_save", k_fwd_save, 4 * plane_floats), ("cp4_bwd_data_save", k_bwdd_save, 4 * plane_floats),
+                    ("cp4_bwd_filter_saved", k_bwdf_saved, 8 * plane_floats)]
+        k_fwd_save(0, cur_stream())      # the planes the saved-plane kernel reads
+        k_bwdd_save(0, cur_stream())
+    for _, fn, _ in kernels:
         run_k, _ = many(fn, K)
         run_k()
         torch.cuda.synchronize()
@@ -348,9 +384,12 @@ def main():
         return
 
     # ---- roofline of the dominant kernel ---------------------------------------------------------
-    names = ["cp4_fwd", "cp4_bwd_data", "cp4_bwd_filter"]
-    dom = int(np.argmax(mean_ms))
-    alg_bytes = 4 * n * HW * (c["C"] + c["T"]) + 4 * c["R"] * (c["T"] + c["C"] + 2 * c["F"])
+    names = [k[0] for k in kernels]
+    base_bytes = 4 * n * HW * (c["C"] + c["T"]) + 4 * c["R"] * (c["T"] + c["C"] + 2 * c["F"])
+    kbytes = [base_bytes + k[2] for k in kernels]
+    in_step = range(3, 6) if shared else range(0, 3)      # the kernels the timed step launches
+    dom = max(in_step, key=lambda i: mean_ms[i])
+    alg_bytes = kbytes[dom]
     peak, peak_kind = hbm_peak()
     achieved = alg_bytes / (mean_ms[dom] * 1e-3) / 1e9
     traffic = None
@@ -362,7 +401,8 @@ def main():
                 "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                 "algorithmic_bytes_per_launch": alg_bytes,
                 "per_kernel_us": {nm: float(v * 1e3) for nm, v in zip(names, mean_ms)},
-                "per_kernel_frac": {nm: float(alg_bytes / (v * 1e-3) / 1e9 / peak) for nm, v in zip(names, mean_ms)}}
+                "per_kernel_frac": {nm: float(b / (v * 1e-3) / 1e9 / peak) for nm, v, b in zip(names, mean_ms, kbytes)},
+                "kernels_in_step": [names[i] for i in in_step]}
 
     cpu = None
     if not args.no_cpu_baseline:
@@ -377,6 +417,8 @@ def main():
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic (seeded; X~U[-1,1], factors~N(0,1/sqrt(9C)), dU~N(0,1))",
         "config": {"workload": WORKLOAD, "images_per_step_per_gpu": n, "path": args.path,
+                   "step": "b200cp_cp4_step: forward, backward-data and backward-filter in one call, rank planes shared"
+                           if shared else "b200cp_cp4_fwd + b200cp_cp4_bwd_data + b200cp_cp4_bwd_filter",
                    "timing": "K steps replayed as one CUDA graph between two events" if graphed else "K eager steps between two events",
                    "l2": f"{NSETS} rotating buffer sets ({NSETS * 4 * n * HW * 64 * 4 / 1e6:.0f} MB) > 126 MB L2",
                    "collective": "allreduce of %d packed factor-gradient floats" % nK if world > 1 else "none"},

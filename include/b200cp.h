@@ -107,6 +107,30 @@ int b200cp_cp4_bwd_filter_full(const b200cp_tensor_shape* s, const float* X, con
 int b200cp_cp4_recompose(const b200cp_tensor_shape* s, const float* K0, const float* K1, const float* KH,
                          const float* KW, float* K, void* stream);
 
+/* One training step on device buffers: U = forward(X), dX = backward-data(dU) and the packed factor gradients,
+ * the three results of b200cp_cp4_fwd, _bwd_data and _bwd_filter on the same inputs.  Inside one call the work
+ * the three have in common is done once: with 3x3 filters (pad 1) on the default path the two convolutions leave
+ * their rank-R planes K1^T X and K0^T dU ([N,R,H,W] each) in the workspace and the factor gradients start from
+ * those instead of contracting the channels again.  No counterpart in the reference, whose three entry points
+ * (Cuda_kernels/cp4Conv2d.cuh:8-28) are called one after the other by its callers. */
+size_t b200cp_cp4_step_workspace_bytes(const b200cp_tensor_shape* s, int flags);
+int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0, const float* K1,
+                    const float* KH, const float* KW, float* U, float* dX, float* dK_packed, void* workspace,
+                    size_t workspace_bytes, void* stream, int flags);
+
+/* The pieces of b200cp_cp4_step for callers that run the forward and the backward pass at different times
+ * (an autograd function): the two convolutions that also write their rank plane (P = K1^T X from the forward,
+ * Q = K0^T dU from backward-data; [N,R,H,W] fp32 each, caller-owned), and the factor gradients from the two
+ * planes.  3x3 filters with pad 1, flags AUTO or MMA.  No counterpart in the reference. */
+int b200cp_cp4_fwd_save(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1, const float* KH,
+                        const float* KW, float* U, float* P, void* stream, int flags);
+int b200cp_cp4_bwd_data_save(const b200cp_tensor_shape* s, const float* dU, const float* K0, const float* K1,
+                             const float* KH, const float* KW, float* dX, float* Q, void* stream, int flags);
+size_t b200cp_cp4_bwd_filter_saved_workspace_bytes(const b200cp_tensor_shape* s, int flags);
+int b200cp_cp4_bwd_filter_saved(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* P,
+                                const float* Q, const float* KH, const float* KW, float* dK_packed, void* workspace,
+                                size_t workspace_bytes, void* stream, int flags);
+
 /* ---- three-factor CP conv2d ------------------------------------------------ */
 
 /* U[n,t,h,w] = sum_r KT[t,r] sum_{y,x} KC[y,x,r] sum_c KCin[c,r] X[n,c,h+y-pad,w+x-pad]: the layer

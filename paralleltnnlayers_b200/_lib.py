@@ -45,6 +45,12 @@ def _load():
         "b200cp_cp4_bwd_filter_noalloc": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp]),
         "b200cp_cp4_bwd_filter_full": (i, [sp, fp, fp, fp, vp]),
         "b200cp_cp4_recompose": (i, [sp, fp, fp, fp, fp, fp, vp]),
+        "b200cp_cp4_step_workspace_bytes": (sz, [sp, i]),
+        "b200cp_cp4_step": (i, [sp, fp, fp, fp, fp, fp, fp, fp, fp, fp, vp, sz, vp, i]),
+        "b200cp_cp4_fwd_save": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp, i]),
+        "b200cp_cp4_bwd_data_save": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp, i]),
+        "b200cp_cp4_bwd_filter_saved_workspace_bytes": (sz, [sp, i]),
+        "b200cp_cp4_bwd_filter_saved": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp, sz, vp, i]),
         "b200cp_cp3_fwd": (i, [sp, fp, fp, fp, fp, fp, vp, i]),
         "b200cp_cp3_bwd_data": (i, [sp, fp, fp, fp, fp, fp, vp, i]),
         "b200cp_cp3_bwd_filter_workspace_bytes": (sz, [sp, i]),

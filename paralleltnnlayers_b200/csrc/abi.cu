@@ -80,7 +80,8 @@ const bool g_auto_mma = [] {
 }();
 
 int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, const float* K1, const float* KH,
-             const float* KW, float* out, cudaStream_t st, int flags, bool backward, const float* KC = nullptr) {
+             const float* KW, float* out, cudaStream_t st, int flags, bool backward, const float* KC = nullptr,
+             float* save = nullptr) {
   const int path = path_of(flags);
   Cp4Args a{};
   a.N = s->N; a.H = s->H; a.W = s->W; a.Y = s->Y; a.X = s->X; a.pad = s->pad;
@@ -88,14 +89,14 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
   a.Cout = backward ? s->C : s->T;
   a.Fin = backward ? K0 : K1;
   a.Fout = backward ? K1 : K0;
-  a.KH = KH; a.KW = KW; a.KC = KC; a.in = in; a.out = out;
+  a.KH = KH; a.KW = KW; a.KC = KC; a.in = in; a.out = out; a.save = save;
   a.flip = backward ? 1 : 0;
   a.Rs = s->Rank;
   a.R = s->Rank;
   if (KC && path != B200CP_PATH_AUTO && path != B200CP_PATH_MMA)
     return fail(B200CP_ERR_UNSUPPORTED, "the three-factor CP conv runs on the mma path only (flags AUTO or MMA)");
   if (path == B200CP_PATH_TC3X || path == B200CP_PATH_TC1X) return cp4_tc_launch(a, path == B200CP_PATH_TC3X ? 3 : 1, nullptr, st);
-  if (path == B200CP_PATH_AUTO && g_auto_tc && !KC) {
+  if (path == B200CP_PATH_AUTO && g_auto_tc && !KC && !save) {
     DeviceInfo di;
     if (int rc = device_info(&di)) return rc;
     if (cp4_tc_supported(a, di, nullptr)) return cp4_tc_launch(a, 3, nullptr, st);
@@ -104,7 +105,7 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);
     a.accumulate = r0 > 0;
-    const bool mma = KC || path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma);
+    const bool mma = KC || save || path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma);
     if (int rc = (mma ? cp4_mma_launch(a, st) : cp4_simt_launch(a, st))) return rc;
   }
   return B200CP_OK;
@@ -280,6 +281,105 @@ int b200cp_cp4_recompose(const b200cp_tensor_shape* s, const float* K0, const fl
   if (int rc = check_shape(s, "b200cp_cp4_recompose")) return rc;
   if (int rc = check_ptrs("b200cp_cp4_recompose", {K0, K1, KH, KW, K})) return rc;
   return cp4_recompose_launch(*s, K0, K1, KH, KW, K, static_cast<cudaStream_t>(stream));
+}
+
+// One training step on device buffers: forward, backward-data and backward-filter.  With 3x3 filters (pad 1) on the
+// default path the two convolutions also write their rank planes P = K1^T X and Q = K0^T dU into the workspace and
+// the factor gradients are computed from those, without contracting the channels a second time.
+static bool step_shares_planes(const b200cp_tensor_shape* s, int flags) {
+  const int path = path_of(flags);
+  return s->Y == 3 && s->X == 3 && s->pad == 1 && (path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma)) &&
+         !getenv("B200CP_STEP_NO_SHARE");
+}
+
+size_t b200cp_cp4_step_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
+  if (check_shape(s, "b200cp_cp4_step_workspace_bytes")) return 0;
+  const size_t plain = b200cp_cp4_bwd_filter_workspace_bytes(s, flags);
+  if (!step_shares_planes(s, flags)) return plain;
+  const size_t plane = align_up((size_t)s->N * s->Rank * s->H * s->W * sizeof(float), 256);
+  return 2 * plane + std::max(plain, cp4_bwd_filter_saved_workspace(*s));
+}
+
+int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0, const float* K1,
+                    const float* KH, const float* KW, float* U, float* dX, float* dK_packed, void* workspace,
+                    size_t workspace_bytes, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_step")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_step", {X, dU, K0, K1, KH, KW, U, dX, dK_packed})) return rc;
+  const size_t need = b200cp_cp4_step_workspace_bytes(s, flags);
+  if (!workspace || workspace_bytes < need)
+    return fail(B200CP_ERR_WORKSPACE, "b200cp_cp4_step: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!step_shares_planes(s, flags)) {
+    const int pf = path_of(flags);
+    const int fflags = (pf == B200CP_PATH_TC3X || pf == B200CP_PATH_TC1X) ? (flags & ~B200CP_PATH_MASK) : flags;
+    if (int rc = b200cp_cp4_fwd(s, X, K0, K1, KH, KW, U, stream, flags)) return rc;
+    if (int rc = b200cp_cp4_bwd_data(s, dU, K0, K1, KH, KW, dX, stream, flags)) return rc;
+    return b200cp_cp4_bwd_filter(s, X, dU, K0, K1, KH, KW, dK_packed, workspace, workspace_bytes, stream, fflags);
+  }
+  const size_t plane = align_up((size_t)s->N * s->Rank * s->H * s->W * sizeof(float), 256);
+  float* P = static_cast<float*>(workspace);
+  float* Q = reinterpret_cast<float*>(static_cast<char*>(workspace) + plane);
+  void* part = static_cast<char*>(workspace) + 2 * plane;
+  if (int rc = run_conv(s, X, K0, K1, KH, KW, U, st, flags, false, nullptr, P)) return rc;
+  if (int rc = run_conv(s, dU, K0, K1, KH, KW, dX, st, flags, true, nullptr, Q)) return rc;
+  Cp4BwdFilterArgs a{};
+  a.N = s->N; a.C = s->C; a.T = s->T; a.H = s->H; a.W = s->W; a.F = 3; a.pad = 1;
+  a.Rs = s->Rank;
+  a.X = X; a.dU = dU; a.K0 = K0; a.K1 = K1; a.KH = KH; a.KW = KW; a.dK = dK_packed;
+  a.ws = part; a.ws_bytes = workspace_bytes - 2 * plane;
+  for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
+    a.r0 = r0;
+    a.R = std::min(64u, s->Rank - r0);
+    if (int rc = cp4_bwd_filter_saved_launch(a, P, Q, st)) return rc;
+  }
+  return B200CP_OK;
+}
+
+// The pieces of the step, for callers that run forward and backward at different times (autograd): the convolutions
+// with their rank plane written out, and the factor gradients from the two planes.
+int b200cp_cp4_fwd_save(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1, const float* KH,
+                        const float* KW, float* U, float* P, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_fwd_save")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_fwd_save", {X, K0, K1, KH, KW, U, P})) return rc;
+  if (!step_shares_planes(s, flags))
+    return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp4_fwd_save: 3x3 filters with pad 1 on the default (mma) path only");
+  return run_conv(s, X, K0, K1, KH, KW, U, static_cast<cudaStream_t>(stream), flags, false, nullptr, P);
+}
+
+int b200cp_cp4_bwd_data_save(const b200cp_tensor_shape* s, const float* dU, const float* K0, const float* K1,
+                             const float* KH, const float* KW, float* dX, float* Q, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_bwd_data_save")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_bwd_data_save", {dU, K0, K1, KH, KW, dX, Q})) return rc;
+  if (!step_shares_planes(s, flags))
+    return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp4_bwd_data_save: 3x3 filters with pad 1 on the default (mma) path only");
+  return run_conv(s, dU, K0, K1, KH, KW, dX, static_cast<cudaStream_t>(stream), flags, true, nullptr, Q);
+}
+
+size_t b200cp_cp4_bwd_filter_saved_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
+  (void)flags;
+  if (check_shape(s, "b200cp_cp4_bwd_filter_saved_workspace_bytes")) return 0;
+  return cp4_bwd_filter_saved_workspace(*s);
+}
+
+int b200cp_cp4_bwd_filter_saved(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* P,
+                                const float* Q, const float* KH, const float* KW, float* dK_packed, void* workspace,
+                                size_t workspace_bytes, void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_bwd_filter_saved")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_bwd_filter_saved", {X, dU, P, Q, KH, KW, dK_packed})) return rc;
+  if (!step_shares_planes(s, flags))
+    return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp4_bwd_filter_saved: 3x3 filters with pad 1 on the default (mma) path only");
+  if (!workspace) return fail(B200CP_ERR_WORKSPACE, "b200cp_cp4_bwd_filter_saved: workspace is null");
+  Cp4BwdFilterArgs a{};
+  a.N = s->N; a.C = s->C; a.T = s->T; a.H = s->H; a.W = s->W; a.F = 3; a.pad = 1;
+  a.Rs = s->Rank;
+  a.X = X; a.dU = dU; a.KH = KH; a.KW = KW; a.dK = dK_packed;
+  a.ws = workspace; a.ws_bytes = workspace_bytes;
+  for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
+    a.r0 = r0;
+    a.R = std::min(64u, s->Rank - r0);
+    if (int rc = cp4_bwd_filter_saved_launch(a, P, Q, static_cast<cudaStream_t>(stream))) return rc;
+  }
+  return B200CP_OK;
 }
 
 static int host_ctx_ready(HostCtx& c) {

@@ -60,6 +60,7 @@ struct Cp4Args {
   const float *in, *Fin, *Fout, *KH, *KW;
   float* out;
   const float* KC = nullptr;  // free [Y][X][Rs] spatial core (three-factor CP conv) instead of KH x KW; mma path only
+  float* save = nullptr;      // [N][Rs][H][W]: the rank plane sum_ch Fin[ch][r] in[ch][px] is also written here (mma, 3x3)
 };
 int cp4_simt_launch(const Cp4Args& a, cudaStream_t st);
 // same arguments; channel contractions on the warp-level tensor path (mma.sync, three tf32 terms)
@@ -80,6 +81,9 @@ int cp4_bwd_filter_simt_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
 bool cp4_bwd_filter_mma_supported(const Cp4BwdFilterArgs& a);
 size_t cp4_bwd_filter_mma_workspace(const b200cp_tensor_shape& s);
 int cp4_bwd_filter_mma_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
+// the same gradients from the rank planes P = K1^T X, Q = K0^T dU ([N][Rs][H][W]) saved by the convolutions
+size_t cp4_bwd_filter_saved_workspace(const b200cp_tensor_shape& s);
+int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st);
 // dK[row*Rs + r0 + r] = sum over parts of partial[part][row*R + r], in a fixed order
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
                                cudaStream_t st);

@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
                                                              const float* __restrict__ Fout,
                                                              const float* __restrict__ KH,
                                                              const float* __restrict__ KW,
-                                                             const float* __restrict__ KC, float* __restrict__ out) {
+                                                             const float* __restrict__ KC, float* __restrict__ out,
+                                                             float* __restrict__ save) {
   constexpr int NB = RP / 8;                    // rank blocks (n of phase 1, k of phase 3)
   constexpr int XP = kWarps * MBW1 * 16 + 8;    // FIFO row pitch:  8 mod 32
   constexpr int ZP = kWarps * MBW3 * 16 + 8;    // Z row pitch:     8 mod 32
@@ -256,6 +257,29 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
       p[(nb * 8 + 1) * PP + 8] = acc[j][nb][3];
     }
   }
+  if (save != nullptr) {
+    // The rank plane at the tile's own pixels also goes to global memory (3x3, pad 1): the backward-filter kernel
+    // of the same step reads it instead of contracting the channels again.  Straight from the fragments: a quarter
+    // warp writes eight consecutive pixels of one plane.
+    float* sv = save + ((size_t)n * g.Rs + g.r0) * HW;
+#pragma unroll
+    for (int j = 0; j < MBW1; ++j)
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int hp = (j * kWarps + warp) * 16 + gq + 8 * hlf;
+        const int hy = hp / g.TWh, hx = hp - hy * g.TWh;
+        const int gy = h0 - 1 + hy, gx = w0 - 1 + hx;
+        if (hy >= 1 && hy <= g.TH && hx >= 1 && hx <= g.TW && gy < g.H && gx < g.W) {
+          float* d = sv + (size_t)gy * g.W + gx;
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            const int r = nb * 8 + 2 * tq;
+            if (r < g.R) d[(size_t)r * HW] = acc[j][nb][2 * hlf];
+            if (r + 1 < g.R) d[(size_t)(r + 1) * HW] = acc[j][nb][2 * hlf + 1];
+          }
+        }
+      }
+  }
   __syncthreads();
 
   if (!g.early_fout) stage_fout(0);
@@ -421,7 +445,9 @@ int launch_mma(const MmaGeom& g, const Cp4Args& a, cudaStream_t st) {
   B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const long ctas = (long)a.N * g.tilesH * g.tilesW;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4: too many tiles");
-  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.in, a.Fin, a.Fout, a.KH, a.KW, a.KC, a.out);
+  float* save = (FS == 3 && a.pad == 1) ? a.save : nullptr;
+  if (a.save && !save) return fail(B200CP_ERR_UNSUPPORTED, "cp4: rank planes are saved for 3x3 filters with pad 1 only");
+  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.in, a.Fin, a.Fout, a.KH, a.KW, a.KC, a.out, save);
   B200CP_LAUNCH_OK("cp4_conv_mma_kernel");
   return B200CP_OK;
 }

@@ -31,6 +31,20 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// Four 8 x 4 tiles of 32-bit values (ldmatrix on 8 x 8 b16 tiles): lane l gives the address of row l%8 of tile l/8
+// (16-byte aligned); every thread receives element (row lane/4, column lane%4) of each tile -- the layout of the
+// tf32 A fragment rows and of a "col" B fragment whose K index is contiguous in shared memory.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const float* row_ptr) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(row_ptr);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ void split_tf32_bits(uint32_t x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(__uint_as_float(x)));
+  lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(hi));
+}
+
 __device__ __forceinline__ void cp_async4(float* smem_dst, const float* gsrc, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
   const int sz = valid ? 4 : 0;  // src-size 0: the destination is zero-filled, nothing is read
@@ -40,10 +54,23 @@ __device__ __forceinline__ void cp_async4(float* smem_dst, const float* gsrc, bo
 __device__ __forceinline__ void cp_async4_s(unsigned smem_dst, const float* gsrc, int src_size) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_size) : "memory");
 }
+__device__ __forceinline__ void cp_async16_s(unsigned smem_dst, const float* gsrc, int src_size) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_size) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// the same with a count that is known after unrolling (at most 3 groups may stay pending)
+__device__ __forceinline__ void cp_async_wait_upto(int pending) {
+  switch (pending) {
+    case 3: cp_async_wait<3>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 1: cp_async_wait<1>(); break;
+    default: cp_async_wait<0>(); break;
+  }
 }
 
 }  // namespace mma

@@ -115,6 +115,25 @@ def cp4recom(FT, FC, FY, FX):
     return K
 
 
+def cp4_conv2d_step(X, dU, FT, FC, FY, FX, pad=1, flags=0):
+    """One training step on device tensors (``b200cp_cp4_step``): returns (U, dX, dK_packed); the work forward,
+    backward-data and backward-filter share is done once."""
+    X, dU, FT, FC, FY, FX = (_dev(t, n) for t, n in
+                             ((X, "X"), (dU, "dU"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(X, FT, FC, FY, FX, pad)
+    if tuple(dU.shape) != (s.N, s.T, s.H, s.W):
+        raise ValueError("dU must be [N,T,H,W]")
+    U = torch.empty((s.N, s.T, s.H, s.W), device=X.device, dtype=torch.float32)
+    dX = torch.empty_like(X)
+    dK = torch.empty((s.T + s.C + s.Y + s.X) * s.Rank, device=X.device, dtype=torch.float32)
+    with torch.cuda.device(X.device):
+        wsb = lib.b200cp_cp4_step_workspace_bytes(C.byref(s), flags)
+        ws = torch.empty(max(wsb, 4) // 4, device=X.device, dtype=torch.float32)
+        check(lib.b200cp_cp4_step(C.byref(s), _p(X), _p(dU), _p(FT), _p(FC), _p(FY), _p(FX), _p(U), _p(dX), _p(dK),
+                                  _p(ws), ws.numel() * 4, _stream(), flags))
+    return U, dX, dK
+
+
 def cp4_conv2d_step_host(X, dU, FT, FC, FY, FX, pad=1, flags=0, out=None):
     """Forward + both backward passes through the host-buffer entry point
     (``b200cp_cp4_step_host``): CPU tensors in, CPU tensors out, transfers included.

@@ -60,3 +60,30 @@ def test_backward_filter_mma(case):
     again = P.cp4_conv2d_backward_filter(ddU, dX_, dK0, dK1, dKH, dKW, pad, flags=P.PATH_MMA)
     for a, b in zip(got, again):   # bitwise reproducible
         assert torch.equal(a, b)
+
+
+STEP_SHAPES = [
+    (53, 2, 64, 64, 56, 56, 3, 16, 1, 1.0 / 24),   # BASELINE config 2 at N = 2
+    (58, 3, 40, 72, 19, 23, 3, 24, 1, 0.05),       # ragged tiles, odd channel counts
+    (59, 2, 24, 24, 8, 8, 3, 80, 1, 0.1),          # rank > 64
+    (56, 2, 512, 512, 7, 7, 3, 8, 1, 0.015),
+    (43, 2, 48, 64, 27, 27, 5, 4, 2, 0.1),         # 5x5: the step runs the three kernels as they are
+]
+
+
+@pytest.mark.parametrize("case", STEP_SHAPES, ids=lambda c: "s%d" % c[0])
+def test_step_shares_the_rank_planes(case):
+    """b200cp_cp4_step gives what the three entry points give on the same inputs."""
+    import paralleltnnlayers_b200 as P
+    (X, K0, K1, KH, KW, dU), pad = _inputs(case)
+    dX_, dK0, dK1, dKH, dKW, ddU = dev(X, K0, K1, KH, KW, dU)
+    U, gX, dK = P.cp4_conv2d_step(dX_, ddU, dK0, dK1, dKH, dKW, pad)
+    check(U, O.cp4_forward(X, K0, K1, KH, KW, pad), "step forward")
+    check(gX, O.cp4_backward_data(dU, K0, K1, KH, KW, pad), "step backward-data")
+    ref = O.cp4_backward_filter(X, dU, K0, K1, KH, KW, pad)
+    off = 0
+    for r, nm in zip(ref, ("dK0", "dK1", "dKH", "dKW")):
+        check(dK[off:off + r.size].view(*r.shape), r, "step " + nm, rtol=1e-4, atol=1e-5 * max(1.0, float(np.abs(r).max())))
+        off += r.size
+    U2, gX2, dK2 = P.cp4_conv2d_step(dX_, ddU, dK0, dK1, dKH, dKW, pad)
+    assert torch.equal(dK, dK2) and torch.equal(U, U2)     # bitwise reproducible
