@@ -134,6 +134,52 @@ def cp4_conv2d_step(X, dU, FT, FC, FY, FX, pad=1, flags=0):
     return U, dX, dK
 
 
+def _shares_planes(s, flags):
+    return s.Y == 3 and s.X == 3 and s.pad == 1 and (flags & 7) in (0, 4)
+
+
+def cp4_conv2d_forward_save(Input, FT, FC, FY, FX, pad=1, flags=0):
+    """Forward that also returns its rank plane ``P = FC^T Input`` [N,R,H,W] (``b200cp_cp4_fwd_save``)."""
+    Input, FT, FC, FY, FX = (_dev(t, n) for t, n in ((Input, "Input"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(Input, FT, FC, FY, FX, pad)
+    out = torch.empty((s.N, s.T, s.H, s.W), device=Input.device, dtype=torch.float32)
+    P = torch.empty((s.N, s.Rank, s.H, s.W), device=Input.device, dtype=torch.float32)
+    with torch.cuda.device(Input.device):
+        check(lib.b200cp_cp4_fwd_save(C.byref(s), _p(Input), _p(FT), _p(FC), _p(FY), _p(FX), _p(out), _p(P), _stream(),
+                                      flags))
+    return out, P
+
+
+def cp4_conv2d_backward_data_save(Upstream, FT, FC, FY, FX, pad=1, flags=0):
+    """Backward-data that also returns its rank plane ``Q = FT^T Upstream`` (``b200cp_cp4_bwd_data_save``)."""
+    Upstream, FT, FC, FY, FX = (_dev(t, n) for t, n in
+                                ((Upstream, "Upstream"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(Upstream, FT, FC, FY, FX, pad, in_is_upstream=True)
+    out = torch.empty((s.N, s.C, s.H, s.W), device=Upstream.device, dtype=torch.float32)
+    Q = torch.empty((s.N, s.Rank, s.H, s.W), device=Upstream.device, dtype=torch.float32)
+    with torch.cuda.device(Upstream.device):
+        check(lib.b200cp_cp4_bwd_data_save(C.byref(s), _p(Upstream), _p(FT), _p(FC), _p(FY), _p(FX), _p(out), _p(Q),
+                                           _stream(), flags))
+    return out, Q
+
+
+def cp4_conv2d_backward_filter_saved(dLdO, In, P, Q, FT, FC, FY, FX, pad=1, flags=0):
+    """The four factor gradients from the saved rank planes (``b200cp_cp4_bwd_filter_saved``)."""
+    dLdO, In, P, Q, FY, FX = (_dev(t, n) for t, n in
+                              ((dLdO, "dLdO"), (In, "In"), (P, "P"), (Q, "Q"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(In, FT, FC, FY, FX, pad)
+    R = s.Rank
+    nT, nC, nY, nX = s.T * R, s.C * R, s.Y * R, s.X * R
+    dK = torch.empty(nT + nC + nY + nX, device=In.device, dtype=torch.float32)
+    with torch.cuda.device(In.device):
+        wsb = lib.b200cp_cp4_bwd_filter_saved_workspace_bytes(C.byref(s), flags)
+        ws = torch.empty(max(wsb, 4) // 4, device=In.device, dtype=torch.float32)
+        check(lib.b200cp_cp4_bwd_filter_saved(C.byref(s), _p(In), _p(dLdO), _p(P), _p(Q), _p(FY), _p(FX), _p(dK), _p(ws),
+                                              ws.numel() * 4, _stream(), flags))
+    return (dK[:nT].view(s.T, R), dK[nT:nT + nC].view(s.C, R), dK[nT + nC:nT + nC + nY].view(s.Y, R),
+            dK[nT + nC + nY:].view(s.X, R))
+
+
 def cp4_conv2d_step_host(X, dU, FT, FC, FY, FX, pad=1, flags=0, out=None):
     """Forward + both backward passes through the host-buffer entry point
     (``b200cp_cp4_step_host``): CPU tensors in, CPU tensors out, transfers included.
@@ -384,14 +430,26 @@ class CP4Conv2dFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, FT, FC, FY, FX, pad=1, flags=0):
-        ctx.save_for_backward(x, FT, FC, FY, FX)
         ctx.pad, ctx.flags = pad, flags
+        # with 3x3 filters the forward keeps its rank plane for the factor gradients (a quarter of x at C = 4R)
+        ctx.shared = (FY.shape[0] == 3 and FX.shape[0] == 3 and pad == 1 and (flags & 7) in (0, 4) and
+                      any(t.requires_grad for t in (FT, FC, FY, FX)))
+        if ctx.shared:
+            y, P = cp4_conv2d_forward_save(x, FT, FC, FY, FX, pad, flags)
+            ctx.save_for_backward(x, FT, FC, FY, FX, P)
+            return y
+        ctx.save_for_backward(x, FT, FC, FY, FX)
         return cp4_conv2d_forward(x, FT, FC, FY, FX, pad, flags)
 
     @staticmethod
     def backward(ctx, dy):
-        x, FT, FC, FY, FX = ctx.saved_tensors
         dy = dy.contiguous()
+        if ctx.shared:
+            x, FT, FC, FY, FX, P = ctx.saved_tensors
+            dx, Q = cp4_conv2d_backward_data_save(dy, FT, FC, FY, FX, ctx.pad, ctx.flags)
+            g = cp4_conv2d_backward_filter_saved(dy, x, P, Q, FT, FC, FY, FX, ctx.pad, ctx.flags)
+            return (dx if ctx.needs_input_grad[0] else None, *g, None, None)
+        x, FT, FC, FY, FX = ctx.saved_tensors
         dx = cp4_conv2d_backward_data(dy, FT, FC, FY, FX, ctx.pad, ctx.flags) if ctx.needs_input_grad[0] else None
         g = (None,) * 4
         if any(ctx.needs_input_grad[1:5]):

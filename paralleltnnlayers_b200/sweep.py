@@ -80,6 +80,8 @@ def sweep_cp4(P, reps, rows):
         for name, fl in (("simt", P.PATH_SIMT), ("mma", P.PATH_MMA)):
             row["bwd_filter_" + name] = timeit(
                 lambda i: P.cp4_conv2d_backward_filter(dUs[i % n], Xs[i % n], *K, 1, flags=fl, packed=True), reps)
+        # the whole training step in one call (rank planes shared between the three kernels)
+        row["step"] = timeit(lambda i: P.cp4_conv2d_step(Xs[i % n], dUs[i % n], *K, 1), reps)
         rows.append(row)
         del Xs, dUs
         torch.cuda.empty_cache()
