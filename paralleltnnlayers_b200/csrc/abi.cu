@@ -292,6 +292,25 @@ static bool step_shares_planes(const b200cp_tensor_shape* s, int flags) {
          !getenv("B200CP_STEP_NO_SHARE");
 }
 
+// a second stream and two events per device: forward and backward-data of a step are independent and run side by
+// side (the tail of one kernel's last wave overlaps the other kernel), joined again before the factor gradients
+struct StepFork {
+  cudaStream_t side = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+static StepFork g_step_fork[64];
+static std::mutex g_step_mu;
+static int step_fork(int dev, StepFork** out) {   // caller holds g_step_mu
+  StepFork& f = g_step_fork[dev];
+  if (!f.side) {
+    B200CP_CUDA_OK(cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking));
+    B200CP_CUDA_OK(cudaEventCreateWithFlags(&f.fork, cudaEventDisableTiming));
+    B200CP_CUDA_OK(cudaEventCreateWithFlags(&f.join, cudaEventDisableTiming));
+  }
+  *out = &f;
+  return B200CP_OK;
+}
+
 size_t b200cp_cp4_step_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
   if (check_shape(s, "b200cp_cp4_step_workspace_bytes")) return 0;
   const size_t plain = b200cp_cp4_bwd_filter_workspace_bytes(s, flags);
@@ -320,8 +339,24 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
   float* P = static_cast<float*>(workspace);
   float* Q = reinterpret_cast<float*>(static_cast<char*>(workspace) + plane);
   void* part = static_cast<char*>(workspace) + 2 * plane;
+  int dev = 0;
+  B200CP_CUDA_OK(cudaGetDevice(&dev));
+  StepFork* fk = nullptr;
+  const bool fork = dev >= 0 && dev < 64 && !getenv("B200CP_STEP_NO_FORK");
+  // the fork / join pairs of two host threads must not interleave on the shared side stream
+  std::unique_lock<std::mutex> lk(g_step_mu, std::defer_lock);
+  if (fork) {
+    lk.lock();
+    if (int rc = step_fork(dev, &fk)) return rc;
+    B200CP_CUDA_OK(cudaEventRecord(fk->fork, st));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(fk->side, fk->fork, 0));
+  }
   if (int rc = run_conv(s, X, K0, K1, KH, KW, U, st, flags, false, nullptr, P)) return rc;
-  if (int rc = run_conv(s, dU, K0, K1, KH, KW, dX, st, flags, true, nullptr, Q)) return rc;
+  if (int rc = run_conv(s, dU, K0, K1, KH, KW, dX, fork ? fk->side : st, flags, true, nullptr, Q)) return rc;
+  if (fork) {
+    B200CP_CUDA_OK(cudaEventRecord(fk->join, fk->side));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(st, fk->join, 0));
+  }
   Cp4BwdFilterArgs a{};
   a.N = s->N; a.C = s->C; a.T = s->T; a.H = s->H; a.W = s->W; a.F = 3; a.pad = 1;
   a.Rs = s->Rank;
