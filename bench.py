@@ -249,24 +249,48 @@ def main():
         P._lib.check(lib.b200cp_cp4_bwd_filter_saved(C.byref(s), ptr(x), ptr(du), ptr(Pp), ptr(Qp), fp[2], fp[3], ptr(dK),
                                                      ptr(ws_sv), wsb_sv, st, flags))
 
+    # Data parallel: the allreduce of step i's packed gradients runs on a communication stream while step i+1
+    # computes (two gradient buffers; a buffer is reused only after its allreduce has finished); every allreduce is
+    # joined back before the timed region ends.
+    dKs = [dK, torch.empty_like(dK)] if dist is not None else [dK]
+    comm = torch.cuda.Stream() if dist is not None else None
+    ar_done = [None, None]
+
     def step(i, st):
+        dk = dKs[i % len(dKs)]
+        if dist is not None and ar_done[i % 2] is not None:
+            torch.cuda.current_stream().wait_event(ar_done[i % 2])
         if shared:
             x, du, u, dx = sets[i % NSETS]
-            P._lib.check(lib.b200cp_cp4_step(C.byref(s), ptr(x), ptr(du), *fp, ptr(u), ptr(dx), ptr(dK), ptr(ws_step),
+            P._lib.check(lib.b200cp_cp4_step(C.byref(s), ptr(x), ptr(du), *fp, ptr(u), ptr(dx), ptr(dk), ptr(ws_step),
                                              wsb_step, st, flags))
         else:
+            x, du, u, dx = sets[i % NSETS]
             k_fwd(i, st)
             k_bwdd(i, st)
-            k_bwdf(i, st)
+            P._lib.check(lib.b200cp_cp4_bwd_filter(C.byref(s), ptr(x), ptr(du), *fp, ptr(dk), ptr(ws), wsb, st, flags_f))
         if dist is not None:
-            dist.all_reduce(dK)
+            ready = torch.cuda.Event()
+            ready.record()
+            comm.wait_event(ready)
+            with torch.cuda.stream(comm):
+                dist.all_reduce(dk)
+                done = torch.cuda.Event()
+                done.record()
+            ar_done[i % 2] = done
+
+    def join_comm(*_):
+        for k in range(2):
+            if ar_done[k] is not None:
+                torch.cuda.current_stream().wait_event(ar_done[k])
+                ar_done[k] = None
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def many(fn, k):
+    def many(fn, k, tail=None):
         """k consecutive calls of fn as one CUDA graph (no host launch gaps); falls back to an eager loop."""
         g = torch.cuda.CUDAGraph()
         try:
@@ -274,18 +298,27 @@ def main():
                 st = cur_stream()
                 for i in range(k):
                     fn(i, st)
+                if tail:
+                    tail()
             return g.replay, True
         except Exception as e:  # capture not possible: time the eager loop instead
             sys.stderr.write(f"[bench] graph capture failed ({e}); timing eager launches\n")
             torch.cuda.synchronize()
-            return (lambda: [fn(i, cur_stream()) for i in range(k)]), False
+
+            def eager():
+                for i in range(k):
+                    fn(i, cur_stream())
+                if tail:
+                    tail()
+            return eager, False
 
     for i in range(args.warmup):
         step(i, cur_stream())
+    join_comm()
     barrier()
     K = args.steps
     l0 = P.launch_count()
-    run_steps, graphed = many(step, K)
+    run_steps, graphed = many(step, K, join_comm)
     launches = P.launch_count() - l0 if graphed else None
     run_steps()                      # one untimed replay (graph upload, caches)
     barrier()
@@ -421,7 +454,8 @@ def main():
                            if shared else "b200cp_cp4_fwd + b200cp_cp4_bwd_data + b200cp_cp4_bwd_filter",
                    "timing": "K steps replayed as one CUDA graph between two events" if graphed else "K eager steps between two events",
                    "l2": f"{NSETS} rotating buffer sets ({NSETS * 4 * n * HW * 64 * 4 / 1e6:.0f} MB) > 126 MB L2",
-                   "collective": "allreduce of %d packed factor-gradient floats" % nK if world > 1 else "none"},
+                   "collective": ("allreduce of %d packed factor-gradient floats per step, on a communication stream, "
+                                  "overlapped with the next step" % nK) if world > 1 else "none"},
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ks},
         "gpu_launches": launches, "clocks": clocks,
