@@ -296,7 +296,7 @@ static bool step_shares_planes(const b200cp_tensor_shape* s, int flags) {
 // side (the tail of one kernel's last wave overlaps the other kernel), joined again before the factor gradients
 struct StepFork {
   cudaStream_t side = nullptr;
-  cudaEvent_t fork = nullptr, join = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr, fwd_done = nullptr;
 };
 static StepFork g_step_fork[64];
 static std::mutex g_step_mu;
@@ -306,6 +306,7 @@ static int step_fork(int dev, StepFork** out) {   // caller holds g_step_mu
     B200CP_CUDA_OK(cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking));
     B200CP_CUDA_OK(cudaEventCreateWithFlags(&f.fork, cudaEventDisableTiming));
     B200CP_CUDA_OK(cudaEventCreateWithFlags(&f.join, cudaEventDisableTiming));
+    B200CP_CUDA_OK(cudaEventCreateWithFlags(&f.fwd_done, cudaEventDisableTiming));
   }
   *out = &f;
   return B200CP_OK;
@@ -353,15 +354,28 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
   }
   if (int rc = run_conv(s, X, K0, K1, KH, KW, U, st, flags, false, nullptr, P)) return rc;
   if (int rc = run_conv(s, dU, K0, K1, KH, KW, dX, fork ? fk->side : st, flags, true, nullptr, Q)) return rc;
-  if (fork) {
-    B200CP_CUDA_OK(cudaEventRecord(fk->join, fk->side));
-    B200CP_CUDA_OK(cudaStreamWaitEvent(st, fk->join, 0));
-  }
   Cp4BwdFilterArgs a{};
   a.N = s->N; a.C = s->C; a.T = s->T; a.H = s->H; a.W = s->W; a.F = 3; a.pad = 1;
   a.Rs = s->Rank;
   a.X = X; a.dU = dU; a.K0 = K0; a.K1 = K1; a.KH = KH; a.KW = KW; a.dK = dK_packed;
   a.ws = part; a.ws_bytes = workspace_bytes - 2 * plane;
+  if (fork && s->Rank <= 64) {
+    // the gradient kernel in two halves, also side by side: the dK0 half follows the forward on the caller's
+    // stream, the dK1 / spatial half follows backward-data on the side stream once the forward's plane is there
+    a.r0 = 0;
+    a.R = (int)s->Rank;
+    B200CP_CUDA_OK(cudaEventRecord(fk->fwd_done, st));
+    if (int rc = cp4_bwd_filter_saved_launch(a, P, Q, st, 1)) return rc;
+    B200CP_CUDA_OK(cudaStreamWaitEvent(fk->side, fk->fwd_done, 0));
+    if (int rc = cp4_bwd_filter_saved_launch(a, P, Q, fk->side, 2)) return rc;
+    B200CP_CUDA_OK(cudaEventRecord(fk->join, fk->side));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(st, fk->join, 0));
+    return cp4_bwd_filter_saved_launch(a, P, Q, st, 3);
+  }
+  if (fork) {
+    B200CP_CUDA_OK(cudaEventRecord(fk->join, fk->side));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(st, fk->join, 0));
+  }
   for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);

@@ -83,7 +83,9 @@ size_t cp4_bwd_filter_mma_workspace(const b200cp_tensor_shape& s);
 int cp4_bwd_filter_mma_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
 // the same gradients from the rank planes P = K1^T X, Q = K0^T dU ([N][Rs][H][W]) saved by the convolutions
 size_t cp4_bwd_filter_saved_workspace(const b200cp_tensor_shape& s);
-int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st);
+// part 0: everything and the sum of the per-CTA partials; 1: the dK0 half (needs P only); 2: the dK1 / spatial half;
+// 3: the sum of the partials only (after halves 1 and 2, which may run on different streams)
+int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, int part = 0);
 // dK[row*Rs + r0 + r] = sum over parts of partial[part][row*R + r], in a fixed order
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
                                cudaStream_t st);

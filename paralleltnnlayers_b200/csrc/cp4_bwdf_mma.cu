@@ -631,7 +631,10 @@ __device__ __forceinline__ void reduce_pass(const SGeom& g, const float* __restr
   }
 }
 
-template <int RP, int MBW, bool CORE>
+// PART 0: everything.  PART 1: Z and dK0 only (needs the forward's plane P only).  PART 2: Qt, dK1 and the
+// spatial-factor gradients.  The two halves write disjoint rows of the CTA's partial vector, so a step can run
+// them side by side on two streams.
+template <int RP, int MBW, bool CORE, int PART>
 __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in, const float* __restrict__ X,
                                                                const float* __restrict__ dU,
                                                                const float* __restrict__ Pg,
@@ -645,6 +648,7 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
   constexpr int XP = COLS + 12, ZP = COLS + 4;
   constexpr int kXR = kFifo * kGC * XP > kWarps * K::CHA * RPZ ? kFifo * kGC * XP : kWarps * K::CHA * RPZ;
   constexpr int NG = CORE ? 9 : 6;
+  constexpr bool DOZ = PART != 2, DOQ = PART != 1;
   SGeom g = g_in;
   extern __shared__ __align__(16) float smem[];
   float* Xf = smem;                          // FIFO stages 0, 1; at the end of a chunk: reduction scratch
@@ -682,7 +686,7 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
         const int sz = ok && r < g.R ? 4 : 0;
         const size_t o = sz ? (size_t)r * HW + off : 0;
         cp_async4_s(dp + (unsigned)(r * g.pp * 4), Pn + o, sz);
-        cp_async4_s(dq + (unsigned)(r * g.pp * 4), Qn + o, sz);
+        if (DOQ) cp_async4_s(dq + (unsigned)(r * g.pp * 4), Qn + o, sz);
       }
     }
     cp_async_commit();
@@ -735,7 +739,7 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
       const float* p = Ps + (size_t)r * g.pp + oy * g.TWh + x0;
       const float* q = Qs + (size_t)r * g.pp + oy * g.TWh + x0;
 #pragma unroll
-      for (int j = 0; j < SW; ++j) qc[j] = (x0 + j < g.TW) ? q[g.TWh + j + 1] : 0.f;
+      for (int j = 0; j < SW; ++j) qc[j] = (DOQ && x0 + j < g.TW) ? q[g.TWh + j + 1] : 0.f;
       float vc[3][SW];
       if (!CORE) {
 #pragma unroll
@@ -745,31 +749,35 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
       for (int dy = 0; dy < 3; ++dy) {
         float v[SW + 2], u[SW + 2];
 #pragma unroll
-        for (int j = 0; j < SW + 2; ++j) { v[j] = p[j]; u[j] = q[j]; }
+        for (int j = 0; j < SW + 2; ++j) { v[j] = p[j]; u[j] = DOQ ? q[j] : 0.f; }
         p += g.TWh;
         q += g.TWh;
 #pragma unroll
         for (int j = 0; j < SW; ++j) {
-          z[j] = fmaf(w9[dy * 3 + 0], v[j], z[j]);
-          z[j] = fmaf(w9[dy * 3 + 1], v[j + 1], z[j]);
-          z[j] = fmaf(w9[dy * 3 + 2], v[j + 2], z[j]);
-          qt[j] = fmaf(w9[(2 - dy) * 3 + 2], u[j], qt[j]);
-          qt[j] = fmaf(w9[(2 - dy) * 3 + 1], u[j + 1], qt[j]);
-          qt[j] = fmaf(w9[(2 - dy) * 3 + 0], u[j + 2], qt[j]);
-          if (CORE) {
-            dk[dy * 3 + 0] = fmaf(qc[j], v[j], dk[dy * 3 + 0]);
-            dk[dy * 3 + 1] = fmaf(qc[j], v[j + 1], dk[dy * 3 + 1]);
-            dk[dy * 3 + 2] = fmaf(qc[j], v[j + 2], dk[dy * 3 + 2]);
-          } else {
-            const float th_ = fmaf(kw[2], v[j + 2], fmaf(kw[1], v[j + 1], kw[0] * v[j]));
-            dk[dy] = fmaf(qc[j], th_, dk[dy]);
-            vc[0][j] = fmaf(kh[dy], v[j], vc[0][j]);
-            vc[1][j] = fmaf(kh[dy], v[j + 1], vc[1][j]);
-            vc[2][j] = fmaf(kh[dy], v[j + 2], vc[2][j]);
+          if (DOZ) {
+            z[j] = fmaf(w9[dy * 3 + 0], v[j], z[j]);
+            z[j] = fmaf(w9[dy * 3 + 1], v[j + 1], z[j]);
+            z[j] = fmaf(w9[dy * 3 + 2], v[j + 2], z[j]);
+          }
+          if (DOQ) {
+            qt[j] = fmaf(w9[(2 - dy) * 3 + 2], u[j], qt[j]);
+            qt[j] = fmaf(w9[(2 - dy) * 3 + 1], u[j + 1], qt[j]);
+            qt[j] = fmaf(w9[(2 - dy) * 3 + 0], u[j + 2], qt[j]);
+            if (CORE) {
+              dk[dy * 3 + 0] = fmaf(qc[j], v[j], dk[dy * 3 + 0]);
+              dk[dy * 3 + 1] = fmaf(qc[j], v[j + 1], dk[dy * 3 + 1]);
+              dk[dy * 3 + 2] = fmaf(qc[j], v[j + 2], dk[dy * 3 + 2]);
+            } else {
+              const float th_ = fmaf(kw[2], v[j + 2], fmaf(kw[1], v[j + 1], kw[0] * v[j]));
+              dk[dy] = fmaf(qc[j], th_, dk[dy]);
+              vc[0][j] = fmaf(kh[dy], v[j], vc[0][j]);
+              vc[1][j] = fmaf(kh[dy], v[j + 1], vc[1][j]);
+              vc[2][j] = fmaf(kh[dy], v[j + 2], vc[2][j]);
+            }
           }
         }
       }
-      if (!CORE) {
+      if (!CORE && DOQ) {
 #pragma unroll
         for (int j = 0; j < SW; ++j)
 #pragma unroll
@@ -779,17 +787,24 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
       float* qd = Qts + r * ZP + oy * g.TW + x0;
 #pragma unroll
       for (int j = 0; j < SW; ++j)
-        if (x0 + j < g.TW) { zd[j] = z[j]; qd[j] = qt[j]; }
+        if (x0 + j < g.TW) {
+          if (DOZ) zd[j] = z[j];
+          if (DOQ) qd[j] = qt[j];
+        }
     }
+    if (DOQ) {
 #pragma unroll
-    for (int t = 0; t < NG; ++t) redk[tid * NG + t] = dk[t];
+      for (int t = 0; t < NG; ++t) redk[tid * NG + t] = dk[t];
+    }
   }
   __syncthreads();
-  for (int i = tid; i < NG * RP; i += kNT) {
-    const int rr = i % RP, t = i / RP;
-    float s = 0.f;
-    for (int k = 0; k < kNT / RP; ++k) s += redk[(rr + RP * k) * NG + t];
-    if (rr < g.R) part[(size_t)(g.T + g.C + t) * g.R + rr] = s;
+  if (DOQ) {
+    for (int i = tid; i < NG * RP; i += kNT) {
+      const int rr = i % RP, t = i / RP;
+      float s = 0.f;
+      for (int k = 0; k < kNT / RP; ++k) s += redk[(rr + RP * k) * NG + t];
+      if (rr < g.R) part[(size_t)(g.T + g.C + t) * g.R + rr] = s;
+    }
   }
 
   // every group of a 16*MB2-channel chunk gets its own FIFO stage when the dead P / Q tiles give the room
@@ -798,11 +813,11 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
   const bool allin = kAllIn && (size_t)kFifo * kGC * XP + 2 * (size_t)RP * g.pp >= (size_t)K::MB2 * kGC * XP;
   __syncthreads();   // the stencil phase is over: P and Q may be overwritten
   if (allin) {
-    reduce_pass<RP, MBW, true>(g, dU + (size_t)n * g.T * HW, g.T, Xf, Zs, part, gpu, gsz, tid);
-    reduce_pass<RP, MBW, true>(g, X + (size_t)n * g.C * HW, g.C, Xf, Qts, part + (size_t)g.T * g.R, gpx, gsz, tid);
+    if (DOZ) reduce_pass<RP, MBW, true>(g, dU + (size_t)n * g.T * HW, g.T, Xf, Zs, part, gpu, gsz, tid);
+    if (DOQ) reduce_pass<RP, MBW, true>(g, X + (size_t)n * g.C * HW, g.C, Xf, Qts, part + (size_t)g.T * g.R, gpx, gsz, tid);
   } else {
-    reduce_pass<RP, MBW, false>(g, dU + (size_t)n * g.T * HW, g.T, Xf, Zs, part, gpu, gsz, tid);
-    reduce_pass<RP, MBW, false>(g, X + (size_t)n * g.C * HW, g.C, Xf, Qts, part + (size_t)g.T * g.R, gpx, gsz, tid);
+    if (DOZ) reduce_pass<RP, MBW, false>(g, dU + (size_t)n * g.T * HW, g.T, Xf, Zs, part, gpu, gsz, tid);
+    if (DOQ) reduce_pass<RP, MBW, false>(g, X + (size_t)n * g.C * HW, g.C, Xf, Qts, part + (size_t)g.T * g.R, gpx, gsz, tid);
   }
 }
 
@@ -851,28 +866,45 @@ bool plan_saved(const Cp4BwdFilterArgs& a, const DeviceInfo& di, SGeom* out, siz
   return true;
 }
 
+template <int RP, int MBW, bool CORE, int PART>
+int launch_saved_part(const SGeom& g, size_t smem, long ctas, const Cp4BwdFilterArgs& a, const float* P, const float* Q,
+                      cudaStream_t st) {
+  auto kern = cp4_bwdf_saved_kernel<RP, MBW, CORE, PART>;
+  B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.X, a.dU, P, Q, a.KH, a.KW, a.KC, (float*)a.ws);
+  B200CP_LAUNCH_OK("cp4_bwdf_saved_kernel");
+  return B200CP_OK;
+}
+
+// part 0: the whole kernel, then the sum of the partials.  part 1 / 2: one half, no sum.  part 3: the sum only.
 template <int RP, int MBW>
-int launch_saved(const SGeom& g, size_t smem, const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st) {
+int launch_saved(const SGeom& g, size_t smem, const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st,
+                 int part) {
   const long ctas = (long)a.N * g.tilesH * g.tilesW;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: too many tiles");
   const size_t need = (size_t)ctas * g.nparam * sizeof(float);
   if (a.ws_bytes < need)
     return fail(B200CP_ERR_WORKSPACE, "cp4 bwd-filter: workspace of %zu bytes needed, %zu given", need, a.ws_bytes);
-  if (a.KC) {
-    auto kern = cp4_bwdf_saved_kernel<RP, MBW, true>;
-    B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.X, a.dU, P, Q, a.KH, a.KW, a.KC, (float*)a.ws);
+  int rc = B200CP_OK;
+  if (part == 3) {
+  } else if (a.KC) {
+    if (part != 0) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: internal: the free-core kernel is not split");
+    rc = launch_saved_part<RP, MBW, true, 0>(g, smem, ctas, a, P, Q, st);
+  } else if (part == 0) {
+    rc = launch_saved_part<RP, MBW, false, 0>(g, smem, ctas, a, P, Q, st);
+  } else if (part == 1) {
+    rc = launch_saved_part<RP, MBW, false, 1>(g, smem, ctas, a, P, Q, st);
   } else {
-    auto kern = cp4_bwdf_saved_kernel<RP, MBW, false>;
-    B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.X, a.dU, P, Q, a.KH, a.KW, a.KC, (float*)a.ws);
+    rc = launch_saved_part<RP, MBW, false, 2>(g, smem, ctas, a, P, Q, st);
   }
-  B200CP_LAUNCH_OK("cp4_bwdf_saved_kernel");
-  return cp4_reduce_partials_launch((const float*)a.ws, (int)ctas, g.nparam, a.R, a.Rs, a.r0, a.dK, st);
+  if (rc) return rc;
+  if (part == 0 || part == 3)
+    return cp4_reduce_partials_launch((const float*)a.ws, (int)ctas, g.nparam, a.R, a.Rs, a.r0, a.dK, st);
+  return B200CP_OK;
 }
 
 template <int RP>
-int run_saved(const Cp4BwdFilterArgs& a, const float* P, const float* Q, const DeviceInfo& di, cudaStream_t st) {
+int run_saved(const Cp4BwdFilterArgs& a, const float* P, const float* Q, const DeviceInfo& di, cudaStream_t st, int part) {
   SGeom g{};
   size_t smem = 0;
   if (!plan_saved<RP>(a, di, &g, &smem)) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter (saved planes): no tile fits in shared memory");
@@ -881,14 +913,14 @@ int run_saved(const Cp4BwdFilterArgs& a, const float* P, const float* Q, const D
   g.nparam = (a.T + a.C + (a.KC ? 9 : 6)) * a.R;
   g.vec = (g.TW % 4 == 0 && a.W % 4 == 0 && (g.MBW == 1 || g.MBW == 2 || g.MBW == 4) &&
            ((uintptr_t)a.X % 16 == 0) && ((uintptr_t)a.dU % 16 == 0) && !getenv("B200CP_NO_VEC")) ? 1 : 0;
-  if (getenv("B200CP_DEBUG"))
+  if (getenv("B200CP_DEBUG") && part != 3)
     fprintf(stderr, "[b200cp] bwd-filter (saved planes) tile TH=%d TW=%d blocks per warp %d smem=%zu RP=%d vec=%d\n", g.TH, g.TW, g.MBW,
             smem, RP, g.vec);
   switch (g.MBW) {
-    case 1: return launch_saved<RP, 1>(g, smem, a, P, Q, st);
-    case 2: return launch_saved<RP, 2>(g, smem, a, P, Q, st);
-    case 3: return launch_saved<RP, 3>(g, smem, a, P, Q, st);
-    case 4: return launch_saved<RP, 4>(g, smem, a, P, Q, st);
+    case 1: return launch_saved<RP, 1>(g, smem, a, P, Q, st, part);
+    case 2: return launch_saved<RP, 2>(g, smem, a, P, Q, st, part);
+    case 3: return launch_saved<RP, 3>(g, smem, a, P, Q, st, part);
+    case 4: return launch_saved<RP, 4>(g, smem, a, P, Q, st, part);
   }
   return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: internal: no kernel for %d blocks per warp", g.MBW);
 }
@@ -1000,14 +1032,14 @@ size_t cp4_bwd_filter_mma_workspace(const b200cp_tensor_shape& s) {
 
 // factor gradients from the rank planes P = K1^T X and Q = K0^T dU ([N][Rs][H][W]) the convolutions of the same
 // step saved; 3x3 filters with pad 1
-int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st) {
+int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, int part) {
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
   const int rp = padded_rank(a.R);
-  if (rp <= 8) return run_saved<8>(a, P, Q, di, st);
-  if (rp == 16) return run_saved<16>(a, P, Q, di, st);
-  if (rp == 32) return run_saved<32>(a, P, Q, di, st);
-  return run_saved<64>(a, P, Q, di, st);
+  if (rp <= 8) return run_saved<8>(a, P, Q, di, st, part);
+  if (rp == 16) return run_saved<16>(a, P, Q, di, st, part);
+  if (rp == 32) return run_saved<32>(a, P, Q, di, st, part);
+  return run_saved<64>(a, P, Q, di, st, part);
 }
 
 size_t cp4_bwd_filter_saved_workspace(const b200cp_tensor_shape& s) {
