@@ -278,6 +278,35 @@ inline Tensor Conv2dBackwardFilter(Tensor const& dLdO, Tensor const& In, Tensor 
   FactorGrads g = Conv2dBackwardFilterFactors(dLdO, In, FT, FC, FY, FX, pad);
   return cp4recom(g.dFT, g.dFC, g.dFY, g.dFX);
 }
+// One training step: what Conv2dForward, Conv2dBackwardData and Conv2dBackwardFilterFactors return for the same inputs,
+// from one library call that does their common work once (b200cp_cp4_step; no counterpart in the reference).
+struct StepResult {
+  Tensor Out, dIn;
+  FactorGrads grads;
+};
+inline StepResult Conv2dStep(Tensor const& Input, Tensor const& Upstream, Tensor const& FT, Tensor const& FC,
+                             Tensor const& FY, Tensor const& FX, unsigned pad = 1) {
+  const tensor_shape p = shape_of(Input, false, FT, FC, FY, FX, pad);
+  const b200cp_tensor_shape s = b200cp_detail::abi(p);
+  StepResult r{Tensor{p.N, p.T, p.H, p.W}, Tensor{p.N, p.C, p.H, p.W},
+               FactorGrads{Tensor{p.T, p.Rank}, Tensor{p.C, p.Rank}, Tensor{p.Y, p.Rank}, Tensor{p.X, p.Rank}}};
+  Tensor packed{(p.T + p.C + p.Y + p.X) * p.Rank};
+  const size_t wsb = b200cp_cp4_step_workspace_bytes(&s, 0);
+  void* ws = nullptr;
+  b200cp_detail::cuda(cudaMalloc(&ws, wsb ? wsb : 4), "cudaMalloc");
+  const int rc = b200cp_cp4_step(&s, Input.m_data, Upstream.m_data, FT.m_data, FC.m_data, FY.m_data, FX.m_data, r.Out.m_data,
+                                 r.dIn.m_data, packed.m_data, ws, wsb, nullptr, 0);
+  const cudaError_t e = cudaDeviceSynchronize();
+  cudaFree(ws);
+  b200cp_detail::check(rc, "b200cp_cp4_step");
+  b200cp_detail::cuda(e, "cudaDeviceSynchronize");
+  size_t off = 0;
+  for (Tensor* t : {&r.grads.dFT, &r.grads.dFC, &r.grads.dFY, &r.grads.dFX}) {
+    for (size_t i = 0; i < t->size(); ++i) t->m_data[i] = packed.m_data[off + i];
+    off += t->size();
+  }
+  return r;
+}
 // Cuda_kernels/cp4Conv2d.cu:158-190: forward on uninitialised device buffers -> (mean microseconds, bytes)
 inline std::pair<float, unsigned> run_convolution(tensor_shape p, unsigned PROFCOUNT = 1) {
   float *In, *Out, *FT, *FC, *FX, *FY;

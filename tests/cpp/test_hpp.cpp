@@ -60,6 +60,12 @@ int main() {
   cp4_conv2d_backward_filter_c_gpu(p, dFC.m_data, In.m_data, dO.m_data, FT.m_data, FY.m_data, FX.m_data);
   if (!AllClose(dFC, g.dFC, 1e-4f)) { std::printf("per-factor entry point mismatch\n"); return 5; }
 
+  // the one-call step gives the three results
+  CP::StepResult st = CP::Conv2dStep(In, dO, FT, FC, FY, FX, pad);
+  if (!AllClose(st.Out, CP::Conv2dForward(In, FT, FC, FY, FX, pad), 1e-4f)) { std::printf("step forward mismatch\n"); return 7; }
+  if (!AllClose(st.dIn, CP::Conv2dBackwardData(dO, FT, FC, FY, FX, pad), 1e-4f)) { std::printf("step backward-data mismatch\n"); return 8; }
+  if (!AllClose(st.grads.dFC, g.dFC, 2e-3f) || !AllClose(st.grads.dFY, g.dFY, 2e-3f)) { std::printf("step gradient mismatch\n"); return 9; }
+
   auto r = CP::run_convolution(p, 3);
   if (!(r.first > 0.f) || r.second == 0) return 6;
   Tensor copy = U;
