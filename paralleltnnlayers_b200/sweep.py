@@ -1,11 +1,14 @@
 """Kernel timings of every layer family at the sizes of the benchmark configurations.
 
     python -m paralleltnnlayers_b200.sweep [cp4] [rcp] [dense] [--reps 12] [--json]
-    python -m paralleltnnlayers_b200.sweep --shapes FILE [--ranks 1,2,4,8,16] [--reps 47] [--out results.csv]
+    python -m paralleltnnlayers_b200.sweep --shapes FILE [--ranks 1,2,4,8,16] [--reps 47] [--out results.csv] [--mem]
 
 The second form reads a shape list in the reference's format (``N C H W pad T Y X`` per line, ``#`` comments;
 Cuda_kernels/bench/tensors*.txt) and writes the CSV its ``BenchBothTime`` writes (bench/BenchBothTime.cu:84-104):
-the shape, then the mean forward time in microseconds for each CP rank (the cuDNN column is left out).
+the shape, then the mean forward time in microseconds for each CP rank (the cuDNN column is left out).  With
+``--mem`` it writes the table of ``BenchBothMem`` instead (bench/BenchBothMem.cu:84-106): the KiB of device memory
+the forward call touches per rank, input + output + factors (``CP::run_convolution``, cp4Conv2d.cu:176-178); that
+mode needs no device.
 
 Inputs live on the device; every call of a timed kernel uses the next of several distinct buffer sets (more
 than the L2 holds), the calls of one measurement are captured in one CUDA graph so that there are no host gaps,
@@ -138,6 +141,23 @@ def read_shapes(path):
     return sorted(shapes)
 
 
+def footprint_bytes(N, C, H, W, T, Y, X, R):
+    """Bytes the forward call touches: input, output and the four factors (cp4Conv2d.cu:176-178)."""
+    return 4 * (N * T * H * W + N * C * H * W + R * (T + C + X + Y))
+
+
+def mem_shapes(path, ranks, out):
+    lines = [f"{N} {C} {H} {W} {pad} {T} {Y} {X}, "
+             + ", ".join(str(footprint_bytes(N, C, H, W, T, Y, X, R) // 1024) for R in ranks)
+             for (N, C, H, W, pad, T, Y, X) in read_shapes(path)]
+    text = "\n".join(lines) + "\n"
+    if out:
+        with open(out, "w") as f:
+            f.write(text)
+    else:
+        sys.stdout.write(text)
+
+
 def bench_shapes(P, path, ranks, reps, out):
     lines = []
     for (N, C, H, W, pad, T, Y, X) in read_shapes(path):
@@ -172,7 +192,11 @@ def main(argv=None):
     ap.add_argument("--shapes", help="shape list in the reference's format: time the CP4 forward per shape and rank")
     ap.add_argument("--ranks", default="1,2,4,8,16", help="CP ranks of the --shapes run (the reference's 1..16)")
     ap.add_argument("--out", help="CSV file of the --shapes run (default: stdout)")
+    ap.add_argument("--mem", action="store_true", help="with --shapes: KiB touched per rank instead of timings")
     args = ap.parse_args(argv)
+    if args.shapes and args.mem:
+        mem_shapes(args.shapes, [int(r) for r in args.ranks.split(",")], args.out)
+        return 0
     if args.shapes:
         import paralleltnnlayers_b200 as P
         assert torch.cuda.is_available(), "the sweep needs a CUDA device"

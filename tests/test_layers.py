@@ -96,6 +96,17 @@ def test_shape_list_reader(tmp_path):
     assert read_shapes(str(f)) == [(1, 48, 55, 55, 2, 256, 5, 5), (1, 256, 27, 27, 1, 384, 3, 3)]
 
 
+def test_shape_list_memory_table(tmp_path):
+    """The KiB column of the reference's memory table: 4 * (N*T*H*W + N*C*H*W + R*(T+C+X+Y)) / 1024, floored."""
+    from paralleltnnlayers_b200.sweep import main
+    f = tmp_path / "shapes.txt"
+    f.write_text("1 16 13 13 1 32 3 3\n")
+    out = tmp_path / "m.csv"
+    assert main(["--shapes", str(f), "--mem", "--ranks", "1,16", "--out", str(out)]) == 0
+    kib = lambda R: 4 * (32 * 169 + 16 * 169 + R * (32 + 16 + 3 + 3)) // 1024
+    assert out.read_text() == f"1 16 13 13 1 32 3 3, {kib(1)}, {kib(16)}\n"
+
+
 @pytest.mark.gpu
 def test_shape_list_bench_writes_the_reference_csv(tmp_path):
     import paralleltnnlayers_b200 as P
