@@ -658,6 +658,8 @@ int b200cp_device_status(void) {
   int v = 0;
   if (int rc = tc_device_status(&v)) return rc;
   if (v) return fail(B200CP_ERR_TIMEOUT, "a bounded wait ran out in block %d (code %d)", v & 0xffff, v >> 16);
+  if (int rc = gemm_tc_status(&v)) return rc;
+  if (v) return fail(B200CP_ERR_TIMEOUT, "gradient GEMM: a bounded wait ran out in block %d", v & 0xffff);
   return B200CP_OK;
 }
 

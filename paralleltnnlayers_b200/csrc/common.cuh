@@ -121,6 +121,11 @@ int dense_chain_launch(int B, int order, const int* idims, const int* odims, int
 size_t dense_grad_scratch_floats(int N, int T, int C, int H, int W, int FH, int FW);
 int dense_grad_launch(int N, int T, int C, int H, int W, int FH, int FW, const float* dV, const float* X, float* G,
                       float* scratch, cudaStream_t st);
+// tcgen05 form of the flat gradient GEMM (G[M][N] = A^T B, A [K][M], B [K][N]); three-term tf32 split, fp32-grade
+bool gemm_tc_supported(int K, int M, int N);
+size_t gemm_tc_scratch_floats(int K, int M, int N);
+int gemm_tc_launch(int K, int M, int N, const float* A, const float* B, float* G, float* scratch, cudaStream_t st);
+int gemm_tc_status(int* out);
 size_t contract_scratch_floats(int order, const int* cdims, const int* tdims, int R, int taps, bool has_s);
 int contract_factors_launch(int order, const int* cdims, const int* tdims, int R, int taps, const float* const* A,
                             const float* S, const float* G, float* const* dA, float* dS, float* scratch,

@@ -406,8 +406,9 @@ size_t dense_grad_scratch_floats(int N, int T, int C, int H, int W, int FH, int 
   if (device_info(&di)) di.sm_count = 148;
   const long tiles = (long)ceil_div(C, BN) * ceil_div(T, BM) * FH * FW;
   const int splits = pick_splits(tiles, N, di.sm_count);
-  (void)H; (void)W;
-  return splits > 1 ? (size_t)splits * T * C * FH * FW : 0;
+  const size_t simt = splits > 1 ? (size_t)splits * T * C * FH * FW : 0;
+  if (H * W == 1 && FH * FW == 1 && gemm_tc_supported(N, T, C)) return std::max(simt, gemm_tc_scratch_floats(N, T, C));
+  return simt;
 }
 
 // G is written as [tap][T][C]
@@ -416,6 +417,11 @@ int dense_grad_launch(int N, int T, int C, int H, int W, int FH, int FW, const f
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
   const int taps = FH * FW;
+  // large flat GEMMs go to the tensor cores (16-byte aligned operands; the scratch then holds the hi / lo planes)
+  if (H * W == 1 && taps == 1 && gemm_tc_supported(N, T, C) && scratch &&
+      ((reinterpret_cast<uintptr_t>(dV) | reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(G) |
+        reinterpret_cast<uintptr_t>(scratch)) & 15) == 0)
+    return gemm_tc_launch(N, T, C, dV, X, G, scratch, st);
   const long tiles = (long)ceil_div(C, BN) * ceil_div(T, BM) * taps;
   const int splits = pick_splits(tiles, N, di.sm_count);
   GemmArgs g{};

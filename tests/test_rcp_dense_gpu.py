@@ -74,6 +74,9 @@ DENSE_CASES = [
     (82, 7, (12,), (9,), 3),
     (83, 64, (8, 8, 8, 8), (8, 8, 8, 8), 4),       # BASELINE config 5 modes at reduced batch and rank
     (84, 5, (8, 8, 8, 8), (8, 8, 8, 8), 3),        # same modes, odd batch (half-empty last CTA)
+    (86, 300, (4, 8, 8), (4, 8, 8), 8),            # gradient GEMM on the tensor cores: one 128x256 tile column, ragged K
+    (87, 333, (4, 8, 10), (4, 6, 8), 5),           # ... tiles ragged in M (192) and N (320)
+    (88, 1024, (8, 8, 8), (8, 8, 8), 4),           # ... several tiles, 64 K stages (the ring wraps 16 times)
 ]
 
 
@@ -106,6 +109,20 @@ def test_dense_register_tiled_kernel_matches_chain_kernel(monkeypatch):
     g0, _ = P.dense_cp_backward(dX_, ddY, *dF_, need_dw=False)
     scale = float(Y0.abs().max())
     assert float((Y - Y0).abs().max()) < 1e-5 * scale and float((gX - g0).abs().max()) < 1e-5 * float(g0.abs().max())
+
+
+def test_dense_gradient_gemm_tensor_path_matches_cuda_core_path(monkeypatch):
+    """The tcgen05 three-term GEMM and the fp32 CUDA-core GEMM give the same factor gradients to fp32 accuracy."""
+    import paralleltnnlayers_b200 as P
+    X, F, dY = O.make_dense_inputs(89, 512, (4, 8, 8), (8, 8, 8), 6)
+    dX_, ddY = dev(X, dY)
+    dF_ = dev(*F)
+    _, g1 = P.dense_cp_backward(dX_, ddY, *dF_, need_dx=False)
+    monkeypatch.setenv("B200CP_GEMM_TC", "0")
+    _, g0 = P.dense_cp_backward(dX_, ddY, *dF_, need_dx=False)
+    P.device_status()
+    for a, b in zip(g1, g0):
+        assert float((a - b).abs().max()) < 2e-5 * float(b.abs().max())
 
 
 def test_dense_reference_op_layout():
