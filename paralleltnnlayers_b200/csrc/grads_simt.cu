@@ -225,172 +225,6 @@ __global__ void __launch_bounds__(256) sum_splits_kernel(const float* __restrict
   G[i] = s;
 }
 
-// ---- contraction of G with all factors but one ---------------------------------------
-// Index modes: the m factor modes, pair index p_j = (c_j, t_j), and (for the conv) the tap mode with
-// vector S[tap, r].  For the mode q being differentiated
-//   out_q[p_q][r] = sum_{rest} G[p_q, rest] * W_q[rest][r],   W_q[rest][r] = prod_{j != q} vec_j[p_j(rest)][r],
-// a GEMM whose right operand is generated on the fly.  A CTA owns one q, one chunk of `rest` and 32 ranks; it
-// stages 32 rest items at a time (their G offsets, W rows and G columns) in shared memory.  Partial sums per
-// chunk are added in chunk order by a second kernel.
-constexpr int kCNT = 256, kRB = 32, kSub = 32, kMaxNq = 256;
-
-struct ContractGeom {
-  int m, R, T, C, taps, has_s;
-  int cd[4], td[4], cstride[4], tstride[4];
-  int chunk[5];        // rest items per CTA for each mode
-  int part_off[5];     // first partial block of each mode (in units of [n_q][R] blocks, scaled below)
-};
-struct ContractPtrs {
-  const float* A[4];
-  const float* S;   // null for the dense layer
-  float* dA[4];
-  float* dS;        // may be null
-  float* part;      // partial sums
-};
-
-struct Digit { int size, gstride, mode, fstride; };
-
-__device__ __forceinline__ int mode_size(const ContractGeom& g, int q) { return q < g.m ? g.cd[q] * g.td[q] : g.taps; }
-__device__ __forceinline__ long rest_size(const ContractGeom& g, int q) {
-  long n = 1;
-  for (int j = 0; j < g.m; ++j)
-    if (j != q) n *= (long)g.cd[j] * g.td[j];
-  if (q != g.m) n *= g.taps;
-  return n;
-}
-
-// grid = (chunks of mode q, 1, rank blocks); NP * 8 >= entries of mode q
-template <int NP>
-__global__ void __launch_bounds__(kCNT) contract_factors_kernel(const ContractGeom g, const ContractPtrs p,
-                                                                 const float* __restrict__ G, const int q) {
-  const long rest_total = rest_size(g, q);
-  const long first = (long)blockIdx.x * g.chunk[q];
-  if (first >= rest_total) return;
-  const int nq = mode_size(g, q);
-  const int tid = threadIdx.x, lane = tid % kRB, pg = tid / kRB;
-  const int r = blockIdx.z * kRB + lane;
-
-  __shared__ Digit digits[9];
-  __shared__ int ndig;
-  __shared__ long goff[kSub];
-  __shared__ int foff[kSub][5];
-  __shared__ long poff[kMaxNq];
-  __shared__ float Ws[kSub * kRB];
-  __shared__ float Gs[kMaxNq * (kSub + 1)];
-
-  const long TC = (long)g.T * g.C;
-  if (tid == 0) {
-    int n = 0;
-    if (q != g.m && g.taps > 1) digits[n++] = Digit{g.taps, 0, g.m, g.R};  // gstride of the tap handled as TC below
-    for (int j = 0; j < g.m; ++j)
-      if (j != q) digits[n++] = Digit{g.td[j], g.tstride[j] * g.C, j, g.R};
-    for (int j = 0; j < g.m; ++j)
-      if (j != q) digits[n++] = Digit{g.cd[j], g.cstride[j], j, g.td[j] * g.R};
-    ndig = n;
-  }
-  for (int pp = tid; pp < nq; pp += kCNT) {
-    if (q < g.m) {
-      const int ck = pp / g.td[q], tk = pp - ck * g.td[q];
-      poff[pp] = (long)tk * g.tstride[q] * g.C + (long)ck * g.cstride[q];
-    } else {
-      poff[pp] = (long)pp * TC;
-    }
-  }
-  float acc[NP];
-#pragma unroll
-  for (int i = 0; i < NP; ++i) acc[i] = 0.f;
-  __syncthreads();
-
-  const long last = min(rest_total, first + g.chunk[q]);
-  for (long base = first; base < last; base += kSub) {
-    if (tid < kSub) {
-      long idx = base + tid;
-      long go = -1;
-#pragma unroll
-      for (int j = 0; j < 5; ++j) foff[tid][j] = 0;
-      if (idx < last) {
-        go = 0;
-        for (int d = ndig - 1; d >= 0; --d) {
-          const int size = digits[d].size, mode = digits[d].mode;
-          const int v = (int)(idx % size);
-          idx /= size;
-          go += mode == g.m ? (long)v * TC : (long)v * digits[d].gstride;
-          foff[tid][mode] += v * digits[d].fstride;
-        }
-      }
-      goff[tid] = go;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < kSub * kRB; idx += kCNT) {
-      const int ri = idx / kRB;  // lane == idx % kRB
-      float w = 0.f;
-      if (goff[ri] >= 0 && r < g.R) {
-        w = 1.f;
-        for (int j = 0; j < g.m; ++j)
-          if (j != q) w *= __ldg(p.A[j] + foff[ri][j] + r);
-        if (q != g.m && g.has_s) w *= __ldg(p.S + foff[ri][g.m] + r);
-      }
-      Ws[idx] = w;
-    }
-    for (int idx = tid; idx < nq * kSub; idx += kCNT) {
-      const int pp = idx / kSub, ri = idx - pp * kSub;
-      Gs[pp * (kSub + 1) + ri] = goff[ri] >= 0 ? __ldg(G + goff[ri] + poff[pp]) : 0.f;
-    }
-    __syncthreads();
-#pragma unroll 4
-    for (int ri = 0; ri < kSub; ++ri) {
-      const float w = Ws[ri * kRB + lane];
-#pragma unroll
-      for (int i = 0; i < NP; ++i)
-        if (i * 8 + pg < nq) acc[i] = fmaf(Gs[(i * 8 + pg) * (kSub + 1) + ri], w, acc[i]);
-    }
-    __syncthreads();
-  }
-  if (r < g.R) {
-    float* out = p.part + ((size_t)g.part_off[q] + (size_t)blockIdx.x * nq) * g.R;
-#pragma unroll
-    for (int i = 0; i < NP; ++i)
-      if (i * 8 + pg < nq) out[(size_t)(i * 8 + pg) * g.R + r] = acc[i];
-  }
-}
-
-// out_q[e] = sum over chunks of part[q][chunk][e], in chunk order; grid.y = mode
-__global__ void __launch_bounds__(256) contract_sum_kernel(const ContractGeom g, const ContractPtrs p) {
-  const int q = blockIdx.y;
-  const int n = mode_size(g, q) * g.R;
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= n) return;
-  const long rest_total = rest_size(g, q);
-  const int chunks = (int)((rest_total + g.chunk[q] - 1) / g.chunk[q]);
-  const float* src = p.part + (size_t)g.part_off[q] * g.R + e;
-  float s = 0.f;
-  for (int c = 0; c < chunks; ++c) s += src[(size_t)c * n];
-  float* dst = q < g.m ? p.dA[q] : p.dS;
-  dst[e] = s;
-}
-
-// host mirror of the chunking; returns the number of partial floats
-size_t contract_plan(ContractGeom& g, int order, const int* cdims, const int* tdims, int R, int taps, bool has_s) {
-  g.m = order; g.R = R; g.taps = taps; g.has_s = has_s ? 1 : 0; g.T = 1; g.C = 1;
-  for (int k = 0; k < order; ++k) { g.cd[k] = cdims[k]; g.td[k] = tdims[k]; g.T *= tdims[k]; g.C *= cdims[k]; }
-  int cs = 1, ts = 1;
-  for (int k = order - 1; k >= 0; --k) { g.cstride[k] = cs; g.tstride[k] = ts; cs *= cdims[k]; ts *= tdims[k]; }
-  const int modes = order + (has_s ? 1 : 0);
-  size_t blocks = 0;  // in units of R floats
-  for (int q = 0; q < modes; ++q) {
-    long rest = 1;
-    for (int j = 0; j < order; ++j)
-      if (j != q) rest *= (long)cdims[j] * tdims[j];
-    if (q != order) rest *= taps;
-    const int nq = q < order ? cdims[q] * tdims[q] : taps;
-    g.chunk[q] = rest > 65536 ? 1024 : rest > 4096 ? 256 : 64;
-    const long chunks = (rest + g.chunk[q] - 1) / g.chunk[q];
-    g.part_off[q] = (int)blocks;
-    blocks += (size_t)chunks * nq;
-  }
-  return blocks * R;
-}
-
 int pick_splits(long tiles, int kunits, int sm_count) {
   // aim at two waves of CTAs; never more splits than K units, at most 16
   int s = (int)std::min<long>(16, std::max<long>(1, (2L * sm_count + tiles - 1) / tiles));
@@ -449,45 +283,6 @@ int dense_grad_launch(int N, int T, int C, int H, int W, int FH, int FW, const f
     sum_splits_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(scratch, G, n, splits);
     B200CP_LAUNCH_OK("sum_splits_kernel");
   }
-  return B200CP_OK;
-}
-
-size_t contract_scratch_floats(int order, const int* cdims, const int* tdims, int R, int taps, bool has_s) {
-  ContractGeom g{};
-  return contract_plan(g, order, cdims, tdims, R, taps, has_s);
-}
-
-int contract_factors_launch(int order, const int* cdims, const int* tdims, int R, int taps, const float* const* A,
-                            const float* S, const float* G, float* const* dA, float* dS, float* scratch,
-                            cudaStream_t st) {
-  ContractGeom g{};
-  ContractPtrs p{};
-  contract_plan(g, order, cdims, tdims, R, taps, S != nullptr);
-  if (S && !dS) return fail(B200CP_ERR_INVALID_ARG, "factor contraction: dS missing");
-  if (!scratch) return fail(B200CP_ERR_WORKSPACE, "factor contraction: scratch missing");
-  const int modes = order + (S ? 1 : 0);
-  for (int k = 0; k < order; ++k) { p.A[k] = A[k]; p.dA[k] = dA[k]; }
-  p.S = S; p.dS = dS; p.part = scratch;
-  int max_n = 1;
-  for (int q = 0; q < modes; ++q) {
-    long rest = 1;
-    for (int j = 0; j < order; ++j)
-      if (j != q) rest *= (long)cdims[j] * tdims[j];
-    if (q != order) rest *= taps;
-    const int nq = q < order ? cdims[q] * tdims[q] : taps;
-    if (nq > kMaxNq) return fail(B200CP_ERR_UNSUPPORTED, "factor contraction: mode %d has %d > %d entries", q, nq, kMaxNq);
-    const long chunks = (rest + g.chunk[q] - 1) / g.chunk[q];
-    if (chunks > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "factor contraction: too many chunks");
-    max_n = std::max(max_n, nq);
-    dim3 grid((unsigned)chunks, 1, ceil_div(R, kRB));
-    if (nq <= 16) contract_factors_kernel<2><<<grid, kCNT, 0, st>>>(g, p, G, q);
-    else if (nq <= 64) contract_factors_kernel<8><<<grid, kCNT, 0, st>>>(g, p, G, q);
-    else contract_factors_kernel<32><<<grid, kCNT, 0, st>>>(g, p, G, q);
-    B200CP_LAUNCH_OK("contract_factors_kernel");
-  }
-  dim3 grid2(ceil_div(max_n * R, 256), modes);
-  contract_sum_kernel<<<grid2, 256, 0, st>>>(g, p);
-  B200CP_LAUNCH_OK("contract_sum_kernel");
   return B200CP_OK;
 }
 
