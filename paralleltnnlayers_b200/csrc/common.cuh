@@ -126,6 +126,13 @@ bool gemm_tc_supported(int K, int M, int N);
 size_t gemm_tc_scratch_floats(int K, int M, int N);
 int gemm_tc_launch(int K, int M, int N, const float* A, const float* B, float* G, float* scratch, cudaStream_t st);
 int gemm_tc_status(int* out);
+// conv form of the same kernel: G[tap][T][C] from NCHW operands (padded, transposed hi / lo planes in the scratch)
+bool conv_gemm_tc_supported(int N, int T, int C, int H, int W, int FH, int FW);
+size_t conv_gemm_tc_scratch_floats(int N, int T, int C, int H, int W, int FH, int FW);
+int conv_gemm_tc_launch(int N, int T, int C, int H, int W, int FH, int FW, const float* dV, const float* X, float* G,
+                        float* scratch, cudaStream_t st);
+// G[e] = sum over splits of P[split][e], in split order
+void sum_splits_launch(const float* P, float* G, size_t n, int splits, cudaStream_t st);
 size_t contract_scratch_floats(int order, const int* cdims, const int* tdims, int R, int taps, bool has_s);
 int contract_factors_launch(int order, const int* cdims, const int* tdims, int R, int taps, const float* const* A,
                             const float* S, const float* G, float* const* dA, float* dS, float* scratch,

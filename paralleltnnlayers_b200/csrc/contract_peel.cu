@@ -25,7 +25,7 @@ constexpr int kPT = 256;      // threads per CTA: lane = rank within a block of 
 constexpr int kRB = 32;       // ranks per CTA
 constexpr int kRows0 = 64;    // rows of G per batch in the first peel
 constexpr int kMaxNb = 256;   // entries of one mode (c_dim * t_dim)
-constexpr int kGridCap = 296; // CTAs per level (fixed: the order of the partial sums must not depend on the device)
+constexpr int kGridCap = 592; // CTAs per level (fixed: the order of the partial sums must not depend on the device)
 
 struct PeelMode {
   int nc, nt;      // p = c * nt + t
@@ -53,10 +53,10 @@ __global__ void __launch_bounds__(kPT) peel_first_kernel(const PeelGeom g) {
   float* Gs = smem_f;                       // [kRows0][nbp]
   float* Vs = Gs + kRows0 * nbp;            // [nbp][kRB]
   float* Ls = Vs + nbp * kRB;               // [kRows0][kRB]
-  long* goff = reinterpret_cast<long*>(Ls + kRows0 * kRB);  // [kRows0] G offset of the row, -1 past the end
-  long* orow = goff + kRows0;               // [kRows0] row index in the layout of `next`
-  int* poff = reinterpret_cast<int*>(orow + kRows0);        // [nbp] G offset of the entry (fits: one mode of one image)
-  int* pmap = poff + nbp;                   // [nbp] entry index p for the load order (t slow, c fast)
+  int* goff = reinterpret_cast<int*>(Ls + kRows0 * kRB);  // [kRows0] G offset of the row, -1 past the end
+  int* orow = goff + kRows0;                // [kRows0] row index in the layout of `next`
+  int* pjs = orow + kRows0;                 // [kRows0][4] entry index of each outer mode
+  int* slab = pjs + kRows0 * 4;             // [kRows0 * nc] (row << 16) | c for the load order of one t slab
 
   const int tid = threadIdx.x, lane = tid & 31, wg = tid >> 5;
   const int r = blockIdx.y * kRB + lane;
@@ -66,40 +66,56 @@ __global__ void __launch_bounds__(kPT) peel_first_kernel(const PeelGeom g) {
     const int p = i / kRB, rr = blockIdx.y * kRB + (i - p * kRB);
     Vs[i] = (p < g.nb && rr < g.R) ? __ldg(g.b.vec + (size_t)p * g.R + rr) : 0.f;
   }
-  for (int i = tid; i < nbp; i += kPT) {
-    // load order: t slow, c fast (c is the contiguous index of G)
-    const int t = i / g.b.nc, c = i - t * g.b.nc;
-    poff[i] = i < g.nb ? (int)(t * g.b.gt + c * g.b.gc) : 0;
-    pmap[i] = i < g.nb ? c * g.b.nt + t : i;
+  // load order within one t slab of the peeled mode: row slow, c fast (c is the contiguous index of G)
+  for (int i = tid; i < kRows0 * g.b.nc; i += kPT) {
+    const int row = i / g.b.nc;
+    slab[i] = (row << 16) | (i - row * g.b.nc);
   }
   float acc2[NPW];
 #pragma unroll
   for (int i = 0; i < NPW; ++i) acc2[i] = 0.f;
 
-  const long batches = (g.rows + kRows0 - 1) / kRows0;
-  for (long bt = blockIdx.x; bt < batches; bt += gridDim.x) {
-    __syncthreads();  // the previous batch has been consumed (and, the first time, Vs / poff are written)
+  // entries past nb stay zero for the whole kernel
+  if (g.nb < nbp)
+    for (int i = tid; i < kRows0 * (nbp - g.nb); i += kPT) {
+      const int row = i / (nbp - g.nb), e = g.nb + i - row * (nbp - g.nb);
+      Gs[row * nbp + e] = 0.f;
+    }
+  const int rows = (int)g.rows;  // the host checks that rows and the G offsets fit 31 bits
+  const int batches = (rows + kRows0 - 1) / kRows0;
+  for (int bt = blockIdx.x; bt < batches; bt += gridDim.x) {
+    __syncthreads();  // the previous batch has been consumed (and, the first time, Vs / slab are written)
     if (tid < kRows0) {
-      long idx = bt * kRows0 + tid, go = -1, orw = 0;
-      if (idx < g.rows) {
+      int idx = bt * kRows0 + tid, go = -1, orw = 0;
+      int pj[4] = {0, 0, 0, 0};
+      if (idx < rows) {
         go = 0;
-        int pj[4] = {0, 0, 0, 0};
-        for (int j = g.nouter - 1; j >= 0; --j) {  // c digits, fastest first
-          const int v = (int)(idx % g.outer[j].nc);
-          idx /= g.outer[j].nc;
-          go += v * g.outer[j].gc;
-          pj[j] = v * g.outer[j].nt;
+#pragma unroll
+        for (int j = 3; j >= 0; --j) {  // c digits, fastest first
+          if (j < g.nouter) {
+            const int v = idx % g.outer[j].nc;
+            idx /= g.outer[j].nc;
+            go += v * (int)g.outer[j].gc;
+            pj[j] = v * g.outer[j].nt;
+          }
         }
-        for (int j = g.nouter - 1; j >= 0; --j) {  // t digits
-          const int v = (int)(idx % g.outer[j].nt);
-          idx /= g.outer[j].nt;
-          go += v * g.outer[j].gt;
-          pj[j] += v;
+#pragma unroll
+        for (int j = 3; j >= 0; --j) {  // t digits
+          if (j < g.nouter) {
+            const int v = idx % g.outer[j].nt;
+            idx /= g.outer[j].nt;
+            go += v * (int)g.outer[j].gt;
+            pj[j] += v;
+          }
         }
-        for (int j = 0; j < g.nouter; ++j) orw = orw * (g.outer[j].nc * g.outer[j].nt) + pj[j];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j < g.nouter) orw = orw * (g.outer[j].nc * g.outer[j].nt) + pj[j];
       }
       goff[tid] = go;
       orow[tid] = orw;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pjs[tid * 4 + j] = pj[j];
     }
     __syncthreads();
     // product of the outer vectors per row
@@ -108,29 +124,21 @@ __global__ void __launch_bounds__(kPT) peel_first_kernel(const PeelGeom g) {
       float w = 0.f;
       if (goff[row] >= 0 && rok) {
         w = 1.f;
-        long o = orow[row];
-        for (int j = g.nouter - 1; j >= 0; --j) {
-          const int n = g.outer[j].nc * g.outer[j].nt;
-          const int pj = (int)(o % n);
-          o /= n;
-          w *= __ldg(g.outer[j].vec + (size_t)pj * g.R + r);
-        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j < g.nouter) w *= __ldg(g.outer[j].vec + (size_t)pjs[row * 4 + j] * g.R + r);
       }
       Ls[i] = w;
     }
-    // the batch of G: [t of the peeled mode][row][c of the peeled mode], c fastest
+    // the batch of G, one t slab of the peeled mode at a time: [row][c], c fastest
     {
-      const int nc = g.b.nc, per_t = kRows0 * nc, total = g.b.nt * per_t;
-      for (int i = tid; i < total; i += kPT) {
-        const int t = i / per_t, rem = i - t * per_t, row = rem / nc, c = rem - row * nc;
-        const int e = t * nc + c;
-        const long go = goff[row];
-        Gs[row * nbp + pmap[e]] = go >= 0 ? __ldg(g.src + go + poff[e]) : 0.f;
-      }
-      if (g.nb < nbp)
-        for (int i = tid; i < kRows0 * (nbp - g.nb); i += kPT) {
-          const int row = i / (nbp - g.nb), e = g.nb + i - row * (nbp - g.nb);
-          Gs[row * nbp + e] = 0.f;
+      const int nc = g.b.nc, nt = g.b.nt, per_t = kRows0 * nc;
+      const int gc = (int)g.b.gc, gt = (int)g.b.gt;
+      for (int t = 0; t < nt; ++t)
+        for (int i = tid; i < per_t; i += kPT) {
+          const int rc = slab[i], row = rc >> 16, c = rc & 0xffff;
+          const int go = goff[row];
+          Gs[row * nbp + c * nt + t] = go >= 0 ? __ldg(g.src + go + t * gt + c * gc) : 0.f;
         }
     }
     __syncthreads();
@@ -240,14 +248,24 @@ __global__ void __launch_bounds__(kPT) peel_rank_kernel(const PeelGeom g) {
   }
 }
 
-// dst[e] = sum over CTAs of part[cta][e], in CTA order
+// dst[e] = sum over CTAs of part[cta][e]: 32 elements per block, eight interleaved slices of the CTA range summed
+// side by side and then added in slice order (a fixed association, whatever the schedule)
 __global__ void __launch_bounds__(256) peel_sum_kernel(const float* __restrict__ part, float* __restrict__ dst, int n,
                                                        int ctas) {
-  const int e = blockIdx.x * 256 + threadIdx.x;
-  if (e >= n) return;
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  const int e = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int c = 0; c < ctas; ++c) s += part[(size_t)c * n + e];
-  dst[e] = s;
+  if (e < n)
+    for (int c = sl; c < ctas; c += 8) s += __ldg(part + (size_t)c * n + e);
+  red[sl][lane] = s;
+  __syncthreads();
+  if (sl == 0 && e < n) {
+    float t = red[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t += red[w][lane];
+    dst[e] = t;
+  }
 }
 
 struct PeelPlan {
@@ -341,7 +359,9 @@ int contract_factors_launch(int order, const int* cdims, const int* tdims, int R
     // partial blocks are per (CTA, rank block): the rank blocks write disjoint columns of the same [nb][R] block
     if (first) {
       const size_t smem = sizeof(float) * ((size_t)kRows0 * g.nbp + (size_t)g.nbp * kRB + kRows0 * kRB) +
-                          sizeof(long) * 2 * kRows0 + sizeof(int) * 2 * g.nbp;
+                          sizeof(int) * (6 * kRows0 + kRows0 * g.b.nc);
+      if (g.rows > 0x7fffffffL / 2 || (long)taps * T * C > 0x7fffffffL)
+        return fail(B200CP_ERR_UNSUPPORTED, "factor contraction: the dense gradient has too many entries");
 #define LAUNCH_FIRST(N)                                                                                       \
   do {                                                                                                        \
     B200CP_CUDA_OK(cudaFuncSetAttribute(peel_first_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
@@ -362,12 +382,12 @@ int contract_factors_launch(int order, const int* cdims, const int* tdims, int R
     }
     if (k >= 1) {
       const int n = g.nb * R;
-      peel_sum_kernel<<<ceil_div(n, 256), 256, 0, st>>>(part, grads[k], n, pl.grid[k]);
+      peel_sum_kernel<<<ceil_div(n, 32), 256, 0, st>>>(part, grads[k], n, pl.grid[k]);
       B200CP_LAUNCH_OK("peel_sum_kernel");
     } else if (L == 1) {
       // a single mode: its gradient is the sum of the partial blocks as well
       const int n = g.nb * R;
-      peel_sum_kernel<<<ceil_div(n, 256), 256, 0, st>>>(part, grads[0], n, pl.grid[0]);
+      peel_sum_kernel<<<ceil_div(n, 32), 256, 0, st>>>(part, grads[0], n, pl.grid[0]);
       B200CP_LAUNCH_OK("peel_sum_kernel");
     }
     src = g.next;

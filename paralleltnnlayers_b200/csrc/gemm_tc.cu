@@ -86,8 +86,45 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float4* __restric
 }
 
 struct GemmTcGeom {
-  int M, N, K, NS;  // NS = stages of kKS rows
+  int M, N, K;
+  int NS;            // stages of kKS rows per CTA (per K split)
+  int splits;        // blockIdx.z = tap * splits + split; the tile goes to G + (split * taps + tap) * M * N
+  int taps, FW, padH, padW, Wp;  // conv form: the B rows of tap (y, x) are shifted by (y - padH) * Wp + (x - padW)
 };
+
+// NCHW -> [n][padded pixel][channel] hi / lo planes with a zero ring of (padH, padW) pixels: the layout in which a
+// filter tap is a shift of the row index, which TMA takes at any value (only the contiguous coordinate has an
+// alignment rule).  grid = (pixel tiles, channel tiles, N), block = (32, 8).
+__global__ void __launch_bounds__(256) pad_transpose_split_kernel(const float* __restrict__ src, float* __restrict__ hi,
+                                                                  float* __restrict__ lo, int CH, int H, int W,
+                                                                  int padH, int padW) {
+  __shared__ float tile[32][33];
+  const int Hp = H + 2 * padH, Wp = W + 2 * padW, PP = Hp * Wp;
+  const int n = blockIdx.z, p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  {
+    const int p = p0 + tx, ph = p / Wp, pw = p - ph * Wp;
+    const int h = ph - padH, w = pw - padW;
+    const bool in = p < PP && h >= 0 && h < H && w >= 0 && w < W;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = c0 + ty + 8 * j;
+      tile[ty + 8 * j][tx] = (in && c < CH) ? __ldg(src + (((size_t)n * CH + c) * H + h) * W + w) : 0.f;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int p = p0 + ty + 8 * j, c = c0 + tx;
+    if (p < PP && c < CH) {
+      const float v = tile[tx][ty + 8 * j];
+      const float h = tf32_hi(v);
+      const size_t o = ((size_t)n * PP + p) * CH + c;
+      hi[o] = h;
+      lo[o] = v - h;
+    }
+  }
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const GemmTcGeom g, const __grid_constant__ CUtensorMap mAhi, const __grid_constant__ CUtensorMap mAlo,
@@ -104,6 +141,10 @@ gemm_tc_kernel(const GemmTcGeom g, const __grid_constant__ CUtensorMap mAhi, con
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+  const int tap = blockIdx.z / g.splits, split = blockIdx.z - tap * g.splits;
+  const int k0 = split * g.NS * kKS;
+  const int bshift = (tap / g.FW - g.padH) * g.Wp + (tap % g.FW - g.padW);
+  G += ((size_t)split * g.taps + tap) * g.M * g.N;
 
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) {
@@ -132,7 +173,7 @@ gemm_tc_kernel(const GemmTcGeom g, const __grid_constant__ CUtensorMap mAhi, con
         if (s >= kStages && !wait_or_abort(&empty[slot], ((s / kStages) - 1) & 1, abort_flag)) break;
         uint8_t* dst = sm + slot * kStageBytes;
         mbar_expect_tx(&full[slot], kStageBytes);
-        const int k = s * kKS;
+        const int k = k0 + s * kKS;  // rows past K (and shifted rows outside the tensor) read as zero
 #pragma unroll
         for (int grp = 0; grp < kBM / 32; ++grp) {
           tma_load_2d(dst + grp * kGroupBytes, &mAhi, &full[slot], m0 + grp * 32, k);
@@ -140,8 +181,8 @@ gemm_tc_kernel(const GemmTcGeom g, const __grid_constant__ CUtensorMap mAhi, con
         }
 #pragma unroll
         for (int grp = 0; grp < kBN / 32; ++grp) {
-          tma_load_2d(dst + 2 * kAPlane + grp * kGroupBytes, &mBhi, &full[slot], n0 + grp * 32, k);
-          tma_load_2d(dst + 2 * kAPlane + kBPlane + grp * kGroupBytes, &mBlo, &full[slot], n0 + grp * 32, k);
+          tma_load_2d(dst + 2 * kAPlane + grp * kGroupBytes, &mBhi, &full[slot], n0 + grp * 32, k + bshift);
+          tma_load_2d(dst + 2 * kAPlane + kBPlane + grp * kGroupBytes, &mBlo, &full[slot], n0 + grp * 32, k + bshift);
         }
       }
     }
@@ -207,7 +248,8 @@ gemm_tc_kernel(const GemmTcGeom g, const __grid_constant__ CUtensorMap mAhi, con
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0 && *abort_flag)
-    atomicCAS(&g_gemm_tc_status, 0, (1 << 16) | ((blockIdx.y * gridDim.x + blockIdx.x) & 0xffff));
+    atomicCAS(&g_gemm_tc_status, 0,
+              (1 << 16) | (((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) & 0xffff));
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -263,12 +305,88 @@ int gemm_tc_launch(int K, int M, int N, const float* A, const float* B, float* G
   if (int rc = encode_plane(enc, &mAlo, Alo, M, K)) return rc;
   if (int rc = encode_plane(enc, &mBhi, Bhi, N, K)) return rc;
   if (int rc = encode_plane(enc, &mBlo, Blo, N, K)) return rc;
-  GemmTcGeom g{M, N, K, ceil_div(K, kKS)};
+  GemmTcGeom g{M, N, K, ceil_div(K, kKS), 1, 1, 1, 0, 0, 0};
   dim3 grid(ceil_div(N, kBN), ceil_div(M, kBM));
   if (grid.y > 65535) return fail(B200CP_ERR_UNSUPPORTED, "tensor-core gradient GEMM: too many tiles");
   B200CP_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem));
   gemm_tc_kernel<<<grid, kThreads, kSmem, st>>>(g, mAhi, mAlo, mBhi, mBlo, G);
   B200CP_LAUNCH_OK("gemm_tc_kernel");
+  return B200CP_OK;
+}
+
+// ---- conv form: G[tap][t][c] = sum_{n,h,w} dV[n,t,h,w] * Xpad[n,c,h+y,w+x] ------------------------------------------------
+// Both operands are rewritten once as [n][padded pixel][channel] hi / lo planes (K = padded pixel index, rows);
+// the nine taps are then nine GEMMs over the same planes with the X rows shifted, each split over K so that the
+// (tile, tap, split) grid fills the GPU; a last kernel adds the splits in order.
+namespace {
+struct ConvGemmPlan {
+  int Hp, Wp, taps, splits, NS;
+  long K;
+  size_t plane_a, plane_b, partial;
+};
+bool conv_plan(ConvGemmPlan& p, int N, int T, int C, int H, int W, int FH, int FW) {
+  if (!(enabled() && T % 4 == 0 && C % 4 == 0 && T >= 128 && C >= 128 && FH % 2 == 1 && FW % 2 == 1)) return false;
+  p.Hp = H + FH - 1; p.Wp = W + FW - 1; p.taps = FH * FW;
+  p.K = (long)N * p.Hp * p.Wp;
+  if (p.K < 1024 || p.K > 0x7fffff00L) return false;
+  const long tiles = (long)ceil_div(C, kBN) * ceil_div(T, kBM) * p.taps;
+  const int stages = (int)((p.K + kKS - 1) / kKS);
+  // one wave of CTAs (one CTA per SM by its shared memory); at least 32 stages per split
+  int splits = (int)std::max<long>(1, std::min<long>(148 / std::max<long>(1, tiles), stages / 32));
+  p.NS = ceil_div(stages, splits);
+  p.splits = ceil_div(stages, p.NS);
+  p.plane_a = (size_t)p.K * T;
+  p.plane_b = (size_t)p.K * C;
+  p.partial = p.splits > 1 ? (size_t)p.splits * p.taps * T * C : 0;
+  return get_encode_tiled() != nullptr;
+}
+}  // namespace
+
+bool conv_gemm_tc_supported(int N, int T, int C, int H, int W, int FH, int FW) {
+  ConvGemmPlan p;
+  return conv_plan(p, N, T, C, H, W, FH, FW);
+}
+
+size_t conv_gemm_tc_scratch_floats(int N, int T, int C, int H, int W, int FH, int FW) {
+  ConvGemmPlan p;
+  if (!conv_plan(p, N, T, C, H, W, FH, FW)) return 0;
+  return 2 * (p.plane_a + p.plane_b) + p.partial;
+}
+
+// G is written as [tap][T][C]; dV [N][T][H][W], X [N][C][H][W]
+int conv_gemm_tc_launch(int N, int T, int C, int H, int W, int FH, int FW, const float* dV, const float* X, float* G,
+                        float* scratch, cudaStream_t st) {
+  ConvGemmPlan p;
+  if (!conv_plan(p, N, T, C, H, W, FH, FW)) return fail(B200CP_ERR_UNSUPPORTED, "tensor-core conv gradient: shape not taken");
+  PFN_encodeTiled enc = get_encode_tiled();
+  if ((reinterpret_cast<uintptr_t>(G) | reinterpret_cast<uintptr_t>(scratch)) & 15)
+    return fail(B200CP_ERR_INVALID_ARG, "tensor-core conv gradient: buffers must be 16-byte aligned");
+  float *Ahi = scratch, *Alo = Ahi + p.plane_a, *Bhi = Alo + p.plane_a, *Blo = Bhi + p.plane_b;
+  float* part = Blo + p.plane_b;
+  const int padH = (FH - 1) / 2, padW = (FW - 1) / 2, PP = p.Hp * p.Wp;
+  if (N > 65535) return fail(B200CP_ERR_UNSUPPORTED, "tensor-core conv gradient: batch too large");
+  pad_transpose_split_kernel<<<dim3(ceil_div(PP, 32), ceil_div(T, 32), N), dim3(32, 8), 0, st>>>(dV, Ahi, Alo, T, H, W,
+                                                                                                 padH, padW);
+  B200CP_LAUNCH_OK("pad_transpose_split_kernel");
+  pad_transpose_split_kernel<<<dim3(ceil_div(PP, 32), ceil_div(C, 32), N), dim3(32, 8), 0, st>>>(X, Bhi, Blo, C, H, W,
+                                                                                                 padH, padW);
+  B200CP_LAUNCH_OK("pad_transpose_split_kernel");
+  CUtensorMap mAhi, mAlo, mBhi, mBlo;
+  if (int rc = encode_plane(enc, &mAhi, Ahi, T, (int)p.K)) return rc;
+  if (int rc = encode_plane(enc, &mAlo, Alo, T, (int)p.K)) return rc;
+  if (int rc = encode_plane(enc, &mBhi, Bhi, C, (int)p.K)) return rc;
+  if (int rc = encode_plane(enc, &mBlo, Blo, C, (int)p.K)) return rc;
+  GemmTcGeom g{T, C, (int)p.K, p.NS, p.splits, p.taps, FW, padH, padW, p.Wp};
+  dim3 grid(ceil_div(C, kBN), ceil_div(T, kBM), p.taps * p.splits);
+  if (grid.y > 65535 || grid.z > 65535) return fail(B200CP_ERR_UNSUPPORTED, "tensor-core conv gradient: too many tiles");
+  B200CP_CUDA_OK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem));
+  gemm_tc_kernel<<<grid, kThreads, kSmem, st>>>(g, mAhi, mAlo, mBhi, mBlo, p.splits > 1 ? part : G);
+  B200CP_LAUNCH_OK("gemm_tc_kernel");
+  if (p.splits > 1) {
+    const size_t n = (size_t)p.taps * T * C;
+    sum_splits_launch(part, G, n, p.splits, st);
+    B200CP_LAUNCH_OK("sum_splits_kernel");
+  }
   return B200CP_OK;
 }
 

@@ -225,6 +225,14 @@ __global__ void __launch_bounds__(256) sum_splits_kernel(const float* __restrict
   G[i] = s;
 }
 
+}  // namespace
+
+void sum_splits_launch(const float* P, float* G, size_t n, int splits, cudaStream_t st) {
+  sum_splits_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(P, G, n, splits);
+}
+
+namespace {
+
 int pick_splits(long tiles, int kunits, int sm_count) {
   // aim at two waves of CTAs; never more splits than K units, at most 16
   int s = (int)std::min<long>(16, std::max<long>(1, (2L * sm_count + tiles - 1) / tiles));
@@ -242,6 +250,8 @@ size_t dense_grad_scratch_floats(int N, int T, int C, int H, int W, int FH, int 
   const int splits = pick_splits(tiles, N, di.sm_count);
   const size_t simt = splits > 1 ? (size_t)splits * T * C * FH * FW : 0;
   if (H * W == 1 && FH * FW == 1 && gemm_tc_supported(N, T, C)) return std::max(simt, gemm_tc_scratch_floats(N, T, C));
+  if (H * W > 1 && conv_gemm_tc_supported(N, T, C, H, W, FH, FW))
+    return std::max(simt, conv_gemm_tc_scratch_floats(N, T, C, H, W, FH, FW));
   return simt;
 }
 
@@ -256,6 +266,9 @@ int dense_grad_launch(int N, int T, int C, int H, int W, int FH, int FW, const f
       ((reinterpret_cast<uintptr_t>(dV) | reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(G) |
         reinterpret_cast<uintptr_t>(scratch)) & 15) == 0)
     return gemm_tc_launch(N, T, C, dV, X, G, scratch, st);
+  if (H * W > 1 && scratch && conv_gemm_tc_supported(N, T, C, H, W, FH, FW) &&
+      ((reinterpret_cast<uintptr_t>(G) | reinterpret_cast<uintptr_t>(scratch)) & 15) == 0)
+    return conv_gemm_tc_launch(N, T, C, H, W, FH, FW, dV, X, G, scratch, st);
   const long tiles = (long)ceil_div(C, BN) * ceil_div(T, BM) * taps;
   const int splits = pick_splits(tiles, N, di.sm_count);
   GemmArgs g{};

@@ -17,6 +17,9 @@ RCP_CASES = [
     (73, 2, (2, 2, 2, 2), (2, 3, 2, 2), 8, 8, 1, 6),
     (74, 2, (4, 8, 8), (4, 8, 8), 14, 14, 3, 16),  # BASELINE config 4 channels at a reduced image
     (75, 1, (4, 8, 8), (4, 8, 8), 10, 12, 3, 5),   # same modes, tiles ragged in both directions
+    (76, 6, (4, 8, 8), (4, 8, 8), 14, 12, 3, 6),   # dense gradient on the tensor cores (padded-pixel GEMM, 9 taps, split K)
+    (77, 8, (4, 8, 10), (4, 6, 8), 9, 11, 3, 4),   # ... tiles ragged in T (192) and C (320), odd image
+    (78, 5, (8, 16), (16, 8), 12, 12, 5, 3),       # ... 5x5 core: 25 taps, two-pixel zero ring
 ]
 
 
