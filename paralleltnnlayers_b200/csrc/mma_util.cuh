@@ -13,14 +13,15 @@
 namespace b200cp {
 namespace mma {
 
-__device__ __forceinline__ float tf32_round(float x) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  return __uint_as_float(u);
-}
+// x rounded to tf32, round to nearest with ties away from zero -- what cvt.rna.tf32.f32 returns for every finite
+// x below the overflow threshold: half an ulp of the 10-bit mantissa is added to the magnitude bits and the low 13
+// bits are cut.  Two integer instructions; the cvt itself expands to about five on this target.  (A NaN whose
+// payload overflows into the sign comes out as -0 here, and the lo part x - hi is then NaN, so NaNs still propagate.)
+__device__ __forceinline__ uint32_t tf32_rna_bits(uint32_t x) { return (x + 0x1000u) & 0xffffe000u; }
+__device__ __forceinline__ float tf32_round(float x) { return __uint_as_float(tf32_rna_bits(__float_as_uint(x))); }
 // hi = x rounded to tf32; lo = x - hi (exact in fp32; the tensor core reads its upper 19 bits)
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  hi = tf32_rna_bits(__float_as_uint(x));
   lo = __float_as_uint(x - __uint_as_float(hi));
 }
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -41,7 +42,7 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const float* row_p
                : "r"(a));
 }
 __device__ __forceinline__ void split_tf32_bits(uint32_t x, uint32_t& hi, uint32_t& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(__uint_as_float(x)));
+  hi = tf32_rna_bits(x);
   lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(hi));
 }
 

@@ -134,10 +134,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 // ---- tf32 split --------------------------------------------------------------------
 // hi = x rounded to tf32 (10-bit mantissa), lo = x - hi (exact in fp32).  hi*b + lo*b recovers x*b
 // to about 2^-21 relative once lo is itself cut to tf32 by the tensor core.
+// Round to nearest, ties away from zero, as cvt.rna.tf32.f32 does for finite x below the overflow threshold:
+// half an ulp added to the magnitude bits, low 13 bits cut (two integer instructions).
 __device__ __forceinline__ float tf32_hi(float x) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  return __uint_as_float(u);
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
 
 }  // namespace tc
