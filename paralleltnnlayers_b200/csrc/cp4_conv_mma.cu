@@ -19,6 +19,8 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include <cooperative_groups.h>
+
 #include "mma_util.cuh"
 
 namespace b200cp {
@@ -26,6 +28,7 @@ namespace b200cp {
 namespace {
 
 using namespace mma;
+namespace cg = cooperative_groups;
 
 constexpr int kNT = 256, kWarps = 8;
 constexpr int kGC = 8;       // channels per cp.async group = one mma k-step
@@ -42,6 +45,8 @@ struct MmaGeom {
   int fch;                    // channels of factor planes staged at a time (multiple of 8, <= kFChunk)
   int early_fout;             // 1: all channels fit one chunk and the output-side planes have their own space,
                               //    so both factor sets are staged at the start, behind the first pixel copies
+  int S;                      // channel slices per tile = CTAs per cluster (1: no cluster)
+  int cin_slice, cout_slice;  // channels per slice (multiples of 8)
 };
 
 inline int pitch_mod32(int n, int want) {  // smallest p >= n with p % 32 == want
@@ -65,7 +70,7 @@ size_t mma_smem_floats(const MmaGeom& g) {
   const size_t planes = 2 * (size_t)g.fch * Planes<RP>::FIN;  // FIN >= FOUT
   const size_t planes_out = g.early_fout ? 2 * (size_t)g.fch * Planes<RP>::FOUT : 0;
   const size_t W = (size_t)g.Y * g.X * RP;
-  return std::max(fifo, Z) + P + planes + planes_out + W;
+  return std::max(fifo, Z) + P * (g.S > 1 ? 2 : 1) + planes + planes_out + W;
 }
 
 template <int RP, int FS, int MBW1, int MBW3>
@@ -88,13 +93,21 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
   float* Zs = smem;                             // [RP][ZP]: phase 2 and 3 only, over the FIFO
   constexpr int kXZ = kFifo * kGC * XP > RP * ZP ? kFifo * kGC * XP : RP * ZP;
   float* Ps = smem + kXZ;                       // [RP][PP]
-  float* Fh = Ps + (size_t)RP * PP;             // input-side factor planes hi | lo
+  float* Psum = Ps + (size_t)RP * PP;           // [RP][PP]: P summed over the cluster's channel slices (S > 1 only)
+  float* Fh = Psum + (g.S > 1 ? (size_t)RP * PP : 0);  // input-side factor planes hi | lo
   float* Fo = g.early_fout ? Fh + 2 * kFin : Fh;  // output-side planes: own space, or the input side's after phase 1
   float* Ws = Fo + 2 * (g.early_fout ? kFout : kFin);  // [Y*X][RP]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;      // mma "groupID" and "threadID in group"
 
+  // Channel slices: the S CTAs of a cluster share one tile.  Each contracts its slice of the input channels,
+  // the partial rank planes are summed through distributed shared memory, and each then produces its slice of
+  // the output channels.  Small images with many channels have too few tiles to fill the GPU otherwise.
   int b = blockIdx.x;
+  const int sl = b % g.S;
+  b /= g.S;
+  const int c_lo = min(g.Cin, sl * g.cin_slice), c_hi = min(g.Cin, c_lo + g.cin_slice);
+  const int t_lo = min(g.Cout, sl * g.cout_slice), t_hi = min(g.Cout, t_lo + g.cout_slice);
   const int tw = b % g.tilesW;
   b /= g.tilesW;
   const int th = b % g.tilesH;
@@ -114,7 +127,7 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
   }
 
   auto stage_fout = [&](int t0) {
-    const int tc = min(g.fch, g.Cout - t0);
+    const int tc = min(g.fch, t_hi - t0);
     const int tcp = (tc + 7) / 8 * 8;
     for (int i = tid; i < tcp * RP; i += kNT) {
       const int t = i / RP, r = i % RP;
@@ -152,8 +165,8 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
 
   const unsigned xw_s = (unsigned)__cvta_generic_to_shared(Xf + warp * WCOLS + lane);  // this lane's first column
   const float* xw = Xf + warp * WCOLS;
-  for (int c0 = 0; c0 < g.Cin; c0 += g.fch) {
-    const int cc = min(g.fch, g.Cin - c0);
+  for (int c0 = c_lo; c0 < c_hi; c0 += g.fch) {
+    const int cc = min(g.fch, c_hi - c0);
     const int ccp = (cc + kGC - 1) / kGC * kGC;
     const int ng = ccp / kGC;
     auto issue = [&](int grp) {
@@ -198,7 +211,7 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
       Fh[c * FIN + r] = hi;
       Fh[kFin + c * FIN + r] = tf32_round(v - hi);
     }
-    if (g.early_fout && c0 == 0) stage_fout(0);
+    if (g.early_fout && c0 == c_lo) stage_fout(t_lo);
     __syncthreads();
     for (int grp = 0; grp < ng; ++grp) {
       issue(grp + kFifo - 1);
@@ -257,7 +270,7 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
       p[(nb * 8 + 1) * PP + 8] = acc[j][nb][3];
     }
   }
-  if (save != nullptr) {
+  if (save != nullptr && g.S == 1) {
     // The rank plane at the tile's own pixels also goes to global memory (3x3, pad 1): the backward-filter kernel
     // of the same step reads it instead of contracting the channels again.  Straight from the fragments: a quarter
     // warp writes eight consecutive pixels of one plane.
@@ -282,7 +295,30 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
   }
   __syncthreads();
 
-  if (!g.early_fout) stage_fout(0);
+  const float* Pr = Ps;   // the plane phase 2 reads
+  if (g.S > 1) {
+    // sum the partial planes of the cluster's CTAs, in slice order on every CTA (identical sums everywhere)
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();                                  // every CTA's partial plane is complete
+    for (int i = tid; i < RP * PP; i += kNT) {
+      float v = 0.f;
+      for (int q = 0; q < g.S; ++q) v += cluster.map_shared_rank(Ps, q)[i];
+      Psum[i] = v;
+    }
+    cluster.sync();                                  // nobody reads this CTA's shared memory any more
+    Pr = Psum;
+    if (save != nullptr && sl == 0) {                // the summed plane at the tile's own pixels (3x3, pad 1)
+      float* sv = save + ((size_t)n * g.Rs + g.r0) * HW;
+      for (int i = tid; i < g.R * g.OPX; i += kNT) {
+        const int r = i / g.OPX, op = i - r * g.OPX;
+        const int oy = op / g.TW, ox = op - oy * g.TW;
+        const int gy = h0 + oy, gx = w0 + ox;
+        if (gy < g.H && gx < g.W) sv[(size_t)r * HW + (size_t)gy * g.W + gx] = Psum[r * PP + (oy + 1) * g.TWh + ox + 1];
+      }
+    }
+  }
+
+  if (!g.early_fout) stage_fout(t_lo);
 
   // ---------------- phase 2 ----------------
   {
@@ -300,7 +336,7 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
 #pragma unroll
         for (int j = 0; j < SW; ++j) z[j] = 0.f;
         // reads past the tile's last column stay inside the padded row and feed only outputs that are not stored
-        const float* p = Ps + (size_t)r * PP + oy * g.TWh + x0;
+        const float* p = Pr + (size_t)r * PP + oy * g.TWh + x0;
 #pragma unroll
         for (int dy = 0; dy < 3; ++dy) {
           float v[SW + 2];
@@ -327,7 +363,7 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
     } else {
       for (int op = tid / RP; op < g.OPX; op += kNT / RP) {
         const int oy = op / g.TW, ox = op - oy * g.TW;
-        const float* p = Ps + (size_t)r * PP + oy * g.TWh + ox;
+        const float* p = Pr + (size_t)r * PP + oy * g.TWh + ox;
         float z = 0.f;
         for (int y = 0; y < g.Y; ++y)
           for (int x = 0; x < g.X; ++x) z = fmaf(Ws[(y * g.X + x) * RP + r], p[y * g.TWh + x], z);
@@ -376,9 +412,9 @@ __global__ void __launch_bounds__(kNT, (RP <= 16 && MBW1 <= 2) ? 3 : 2) cp4_conv
 #pragma unroll
     for (int j = 0; j < MBW3; ++j) load_a(j, j);
   }
-  for (int t0 = 0; t0 < g.Cout; t0 += g.fch) {
-    const int tc = min(g.fch, g.Cout - t0);
-    if (t0 > 0) {
+  for (int t0 = t_lo; t0 < t_hi; t0 += g.fch) {
+    const int tc = min(g.fch, t_hi - t0);
+    if (t0 > t_lo) {
       __syncthreads();
       stage_fout(t0);
       __syncthreads();
@@ -443,11 +479,27 @@ int launch_mma(const MmaGeom& g, const Cp4Args& a, cudaStream_t st) {
   auto kern = cp4_conv_mma_kernel<RP, FS, M1, M3>;
   const size_t smem = sizeof(float) * mma_smem_floats<RP>(g);
   B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const long ctas = (long)a.N * g.tilesH * g.tilesW;
+  const long ctas = (long)a.N * g.tilesH * g.tilesW * g.S;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4: too many tiles");
   float* save = (FS == 3 && a.pad == 1) ? a.save : nullptr;
   if (a.save && !save) return fail(B200CP_ERR_UNSUPPORTED, "cp4: rank planes are saved for 3x3 filters with pad 1 only");
-  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.in, a.Fin, a.Fout, a.KH, a.KW, a.KC, a.out, save);
+  if (g.S == 1) {
+    kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.in, a.Fin, a.Fout, a.KH, a.KW, a.KC, a.out, save);
+  } else {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(kNT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)g.S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200CP_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, g, a.in, a.Fin, a.Fout, a.KH, a.KW, a.KC, a.out, save));
+  }
   B200CP_LAUNCH_OK("cp4_conv_mma_kernel");
   return B200CP_OK;
 }
@@ -470,10 +522,11 @@ template <int RP>
 bool plan_tile(const Cp4Args& a, const DeviceInfo& di, MmaGeom* out) {
   MmaGeom best{};
   double best_cost = 1e300;
-  int fTH = 0, fTW = 0;
+  int fTH = 0, fTW = 0, fS = 0;
   if (const char* e = getenv("B200CP_MMA_TILE")) {  // "TH,TW": experiments
     if (sscanf(e, "%d,%d", &fTH, &fTW) != 2) fTH = fTW = 0;
   }
+  if (const char* e = getenv("B200CP_MMA_SLICES")) fS = atoi(e);  // 1, 2, 4 or 8 channel slices per tile: tests
   for (int TW = 1; TW <= std::min(a.W, 64); ++TW) {
     if (fTW ? TW != std::min(fTW, a.W) : (TW != a.W && a.W % TW != 0 && TW % 8 != 0)) continue;
     for (int TH = 1; TH <= std::min(a.H, 64); ++TH) {
@@ -493,6 +546,7 @@ bool plan_tile(const Cp4Args& a, const DeviceInfo& di, MmaGeom* out) {
       g.fch = std::min(kFChunk, (std::max(a.Cin, a.Cout) + 7) / 8 * 8);
       g.early_fout = std::max(a.Cin, a.Cout) <= g.fch ? 1 : 0;
       const int cps_max = (RP <= 16 && g.MBW1 <= 2) ? 3 : 2;   // the kernel's launch bounds
+      g.S = 1; g.cin_slice = (a.Cin + 7) / 8 * 8; g.cout_slice = (a.Cout + 7) / 8 * 8;
       size_t smem = sizeof(float) * mma_smem_floats<RP>(g);
       int cps = (int)smem > di.smem_optin ? 0 : std::max(1, std::min(cps_max, (int)((228 * 1024) / (smem + 1024))));
       if (g.early_fout) {   // one more CTA per SM is worth more than staging the output-side factors early
@@ -509,12 +563,43 @@ bool plan_tile(const Cp4Args& a, const DeviceInfo& di, MmaGeom* out) {
       const double c1 = (double)ceil_div(a.Cin, 8) * (g.MBW1 * (3.0 * RP / 8 + 14) + 4.0 * RP / 8 + 12 + 10.0 * g.MBW1);
       const double c3 = (double)ceil_div(a.Cout, 8) * (g.MBW3 * (3.0 * RP / 8 + 10) + 4.0 * RP / 8);
       const double c2 = (double)ceil_div(TH * ceil_div(TW, 8) * RP, kNT) * 90.0;
-      const double tile = c1 + c2 + c3;
-      // measured on B200: throughput grows with the warps resident per SM, and every round of
-      // CTAs pays the latency of one tile's dependent chain (copies, barriers, stores)
-      const double occupancy = 32.0 / (cps * kWarps);
-      const double cost = (double)ctas * tile / di.sm_count * occupancy + 1200.0 * rounds;
-      if (cost < best_cost) { best_cost = cost; best = g; }
+      const double fixed = 150.0 + 10.0 * RP / kNT;   // set-up; staging the factor planes costs about 10 slots per 256 values
+      const double tile = c1 + c2 + c3 + fixed + 10.0 * (a.Cin + a.Cout) * RP / kNT;
+      // Measured on B200: the kernel is bound by dependent-issue latency, so a tile takes about the same time
+      // whether one or several CTAs share the SM (about 20 % more per extra CTA).  The grid runs as full rounds of
+      // sm_count * cps CTAs plus a last round in which each SM holds only ceil(rest / sm_count) of them.
+      auto grid_cost = [&](long n_ctas, int per_sm, double tile_slots) {
+        const long slots = (long)di.sm_count * per_sm;
+        const long full = n_ctas / slots, rest = n_ctas % slots;
+        const double lat_full = tile_slots * (1.0 + 0.2 * (per_sm - 1));
+        const int k = (int)((rest + di.sm_count - 1) / di.sm_count);
+        // a last round after full ones starts while those drain: it costs between half and all of its own latency
+        const double tail = full ? 0.5 + 0.5 * (double)rest / slots : 1.0;
+        return full * lat_full + (rest ? tile_slots * (1.0 + 0.2 * (k - 1)) * tail : 0.0);
+      };
+      const double cost = grid_cost(ctas, cps, tile);
+      (void)rounds;
+      if (cost < best_cost && (fS <= 1)) { best_cost = cost; best = g; }
+      // channel slices over a cluster of S CTAs: the two contractions shrink by S, the stencil and the exchange
+      // of the partial planes do not
+      for (int S = 2; S <= 8; S *= 2) {
+        // (only where the tiles alone leave SMs idle: with enough tiles the exchange and the repeated stencil cost
+        // more than the shorter contractions save)
+        if (fS ? S != fS : (std::min(a.Cin, a.Cout) < 16 * S || ctas >= 2 * di.sm_count)) continue;
+        MmaGeom gs = g;
+        gs.S = S;
+        gs.cin_slice = (ceil_div(a.Cin, S) + 7) / 8 * 8;
+        gs.cout_slice = (ceil_div(a.Cout, S) + 7) / 8 * 8;
+        gs.fch = std::min(kFChunk, std::max(gs.cin_slice, gs.cout_slice));
+        gs.early_fout = 0;
+        const size_t smem_s = sizeof(float) * mma_smem_floats<RP>(gs);
+        if ((int)smem_s > di.smem_optin) continue;
+        const int cps_s = std::max(1, std::min(cps_max, (int)((228 * 1024) / (smem_s + 1024))));
+        const long ctas_s = ctas * S;
+        const double tile_s = (c1 + c3 + 10.0 * (a.Cin + a.Cout) * RP / kNT) / S + c2 + fixed + 60.0 * S + 200.0;
+        const double cost_s = grid_cost(ctas_s, cps_s, tile_s);
+        if (cost_s < best_cost) { best_cost = cost_s; best = gs; }
+      }
     }
   }
   if (best.TH == 0) return false;
@@ -530,8 +615,8 @@ int run_mma(const Cp4Args& a, const DeviceInfo& di, cudaStream_t st) {
   g.R = a.R; g.Rs = a.Rs; g.r0 = a.r0; g.flip = a.flip; g.accumulate = a.accumulate;
   g.tilesH = ceil_div(a.H, g.TH); g.tilesW = ceil_div(a.W, g.TW);
   if (getenv("B200CP_DEBUG"))
-    fprintf(stderr, "[b200cp] mma tile TH=%d TW=%d blocks %d/%d per warp %d/%d smem=%zu RP=%d\n", g.TH, g.TW, g.MB1, g.MB3,
-            g.MBW1, g.MBW3, sizeof(float) * mma_smem_floats<RP>(g), RP);
+    fprintf(stderr, "[b200cp] mma tile TH=%d TW=%d blocks %d/%d per warp %d/%d slices %d smem=%zu RP=%d\n", g.TH, g.TW,
+            g.MB1, g.MB3, g.MBW1, g.MBW3, g.S, sizeof(float) * mma_smem_floats<RP>(g), RP);
   if (a.Y == 3 && a.X == 3) return dispatch_blocks<RP, 3>(g, a, st);
   return dispatch_blocks<RP, 0>(g, a, st);
 }

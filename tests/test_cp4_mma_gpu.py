@@ -31,6 +31,38 @@ def test_forward_and_backward_data_mma(case):
     check(dX, O.cp4_backward_data(dU, K0, K1, KH, KW, pad), "backward-data (mma)")
 
 
+SLICE_SHAPES = [
+    (56, 2, 512, 512, 7, 7, 3, 8, 1, 0.015),       # config 3's smallest image: whole image per tile
+    (55, 2, 256, 256, 14, 14, 3, 64, 1, 0.02),
+    (58, 3, 40, 72, 19, 23, 3, 24, 1, 0.05),       # channel counts that do not divide into equal slices of 8
+    (43, 2, 48, 64, 27, 27, 5, 4, 2, 0.1),         # 5x5 filter
+    (59, 2, 24, 24, 8, 8, 3, 80, 1, 0.1),          # rank > 64: two rank chunks accumulate into the output
+]
+
+
+@pytest.mark.parametrize("slices", [2, 4, 8])
+@pytest.mark.parametrize("case", SLICE_SHAPES, ids=lambda c: "s%d" % c[0])
+def test_channel_slices_over_a_cluster(case, slices, monkeypatch):
+    """The S CTAs of a cluster split the channels of one tile and exchange partial rank planes through
+    distributed shared memory; forced here, chosen by the planner for small images with many channels."""
+    import paralleltnnlayers_b200 as P
+    monkeypatch.setenv("B200CP_MMA_SLICES", str(slices))
+    (X, K0, K1, KH, KW, dU), pad = _inputs(case)
+    dX_, dK0, dK1, dKH, dKW, ddU = dev(X, K0, K1, KH, KW, dU)
+    U = P.cp4_conv2d_forward(dX_, dK0, dK1, dKH, dKW, pad, flags=P.PATH_MMA)
+    check(U, O.cp4_forward(X, K0, K1, KH, KW, pad), "forward (mma, %d slices)" % slices)
+    dX = P.cp4_conv2d_backward_data(ddU, dK0, dK1, dKH, dKW, pad, flags=P.PATH_MMA)
+    check(dX, O.cp4_backward_data(dU, K0, K1, KH, KW, pad), "backward-data (mma, %d slices)" % slices)
+    if case[6] == 3 and pad == 1:   # the step saves the summed rank planes for the gradient kernel
+        U2, gX2, dK = P.cp4_conv2d_step(dX_, ddU, dK0, dK1, dKH, dKW, pad)
+        monkeypatch.setenv("B200CP_MMA_SLICES", "1")
+        U1, gX1, dK1_ = P.cp4_conv2d_step(dX_, ddU, dK0, dK1, dKH, dKW, pad)
+        assert float((U2 - U1).abs().max()) <= 1e-5 * max(1.0, float(U1.abs().max()))
+        assert float((gX2 - gX1).abs().max()) <= 1e-5 * max(1.0, float(gX1.abs().max()))
+        assert float((dK - dK1_).abs().max()) <= 1e-5 * max(1.0, float(dK1_.abs().max()))
+    P.device_status()
+
+
 def test_mma_path_close_to_exact_path():
     """The three-term tf32 products stay within a few fp32 ulps of the FFMA path."""
     import paralleltnnlayers_b200 as P
