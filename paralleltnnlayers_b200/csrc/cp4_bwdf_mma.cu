@@ -447,6 +447,8 @@ struct SGeom {
   int pp;      // row pitch of the P and Q halo planes (odd)
   int vec;     // 1: TW, W and the tile origins are multiples of 4 and the tensors 16-byte aligned: 16-byte copies
   int h0, w0;  // origin of the CTA's tile (filled in by the kernel)
+  int S, t_slice, c_slice;  // channel slices per tile (gridDim.y) and channels per slice: small images with many
+                            // channels have too few tiles to fill the GPU; the slices own disjoint rows of dK0 / dK1
 };
 
 template <int RP>
@@ -670,6 +672,9 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
   g.w0 = w0;
   const size_t HW = (size_t)g.H * g.W;
   float* part = ws + (size_t)blockIdx.x * g.nparam;
+  const int sl = blockIdx.y;   // channel slice: every slice repeats the stencil phase, slice 0 writes the spatial sums
+  const int t_lo = min(g.T, sl * g.t_slice), t_hi = min(g.T, t_lo + g.t_slice);
+  const int c_lo = min(g.C, sl * g.c_slice), c_hi = min(g.C, c_lo + g.c_slice);
 
   // halo tiles of P and Q: one column per thread, one 4-byte copy per rank plane; zero outside the image and in the
   // slack columns the last strip of a row reads
@@ -710,8 +715,8 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
     const int gy = h0 + oy, gx = w0 + ox;
     const bool ok = wc < WCOLS && op < g.OPX && gy < g.H && gx < g.W;
     const int off = ok ? gy * g.W + gx : 0;
-    gpx[q] = X + (size_t)n * g.C * HW + off;
-    gpu[q] = dU + (size_t)n * g.T * HW + off;
+    gpx[q] = X + ((size_t)n * g.C + c_lo) * HW + off;
+    gpu[q] = dU + ((size_t)n * g.T + t_lo) * HW + off;
     gsz[q] = ok ? 4 : 0;
   }
   cp_async_wait<0>();
@@ -798,7 +803,7 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
     }
   }
   __syncthreads();
-  if (DOQ) {
+  if (DOQ && sl == 0) {
     for (int i = tid; i < NG * RP; i += kNT) {
       const int rr = i % RP, t = i / RP;
       float s = 0.f;
@@ -812,12 +817,16 @@ __global__ void __launch_bounds__(kNT, 2) cp4_bwdf_saved_kernel(const SGeom g_in
   constexpr bool kAllIn = kXR == kFifo * kGC * XP;   // the first two stages are exactly the FIFO, the tiles follow
   const bool allin = kAllIn && (size_t)kFifo * kGC * XP + 2 * (size_t)RP * g.pp >= (size_t)K::MB2 * kGC * XP;
   __syncthreads();   // the stencil phase is over: P and Q may be overwritten
+  const float* dUs = dU + ((size_t)n * g.T + t_lo) * HW;
+  const float* Xs = X + ((size_t)n * g.C + c_lo) * HW;
+  float* part0 = part + (size_t)t_lo * g.R;
+  float* part1 = part + (size_t)(g.T + c_lo) * g.R;
   if (allin) {
-    if (DOZ) reduce_pass<RP, MBW, true>(g, dU + (size_t)n * g.T * HW, g.T, Xf, Zs, part, gpu, gsz, tid);
-    if (DOQ) reduce_pass<RP, MBW, true>(g, X + (size_t)n * g.C * HW, g.C, Xf, Qts, part + (size_t)g.T * g.R, gpx, gsz, tid);
+    if (DOZ) reduce_pass<RP, MBW, true>(g, dUs, t_hi - t_lo, Xf, Zs, part0, gpu, gsz, tid);
+    if (DOQ) reduce_pass<RP, MBW, true>(g, Xs, c_hi - c_lo, Xf, Qts, part1, gpx, gsz, tid);
   } else {
-    if (DOZ) reduce_pass<RP, MBW, false>(g, dU + (size_t)n * g.T * HW, g.T, Xf, Zs, part, gpu, gsz, tid);
-    if (DOQ) reduce_pass<RP, MBW, false>(g, X + (size_t)n * g.C * HW, g.C, Xf, Qts, part + (size_t)g.T * g.R, gpx, gsz, tid);
+    if (DOZ) reduce_pass<RP, MBW, false>(g, dUs, t_hi - t_lo, Xf, Zs, part0, gpu, gsz, tid);
+    if (DOQ) reduce_pass<RP, MBW, false>(g, Xs, c_hi - c_lo, Xf, Qts, part1, gpx, gsz, tid);
   }
 }
 
@@ -871,7 +880,7 @@ int launch_saved_part(const SGeom& g, size_t smem, long ctas, const Cp4BwdFilter
                       cudaStream_t st) {
   auto kern = cp4_bwdf_saved_kernel<RP, MBW, CORE, PART>;
   B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)ctas, kNT, smem, st>>>(g, a.X, a.dU, P, Q, a.KH, a.KW, a.KC, (float*)a.ws);
+  kern<<<dim3((unsigned)ctas, (unsigned)g.S), kNT, smem, st>>>(g, a.X, a.dU, P, Q, a.KH, a.KW, a.KC, (float*)a.ws);
   B200CP_LAUNCH_OK("cp4_bwdf_saved_kernel");
   return B200CP_OK;
 }
@@ -911,11 +920,25 @@ int run_saved(const Cp4BwdFilterArgs& a, const float* P, const float* Q, const D
   g.N = a.N; g.C = a.C; g.T = a.T; g.H = a.H; g.W = a.W; g.R = a.R; g.Rs = a.Rs; g.r0 = a.r0;
   g.tilesH = ceil_div(a.H, g.TH); g.tilesW = ceil_div(a.W, g.TW);
   g.nparam = (a.T + a.C + (a.KC ? 9 : 6)) * a.R;
+  {
+    // channel slices where the tiles alone leave SMs idle: as many as fit one round of CTAs, at least 32 channels each
+    const long ctas = (long)a.N * g.tilesH * g.tilesW;
+    const int cps = std::max(1, std::min(2, (int)((228 * 1024) / (smem + 1024))));
+    int S = 1;
+    if (const char* e = getenv("B200CP_MMA_SLICES")) {
+      S = std::max(1, std::min(8, atoi(e)));
+    } else {
+      while (S < 8 && ctas < di.sm_count && ctas * (2 * S) <= (long)di.sm_count * cps && std::max(a.T, a.C) >= 64 * S) S *= 2;
+    }
+    g.S = S;
+    g.t_slice = (ceil_div(a.T, S) + 15) / 16 * 16;
+    g.c_slice = (ceil_div(a.C, S) + 15) / 16 * 16;
+  }
   g.vec = (g.TW % 4 == 0 && a.W % 4 == 0 && (g.MBW == 1 || g.MBW == 2 || g.MBW == 4) &&
            ((uintptr_t)a.X % 16 == 0) && ((uintptr_t)a.dU % 16 == 0) && !getenv("B200CP_NO_VEC")) ? 1 : 0;
   if (getenv("B200CP_DEBUG") && part != 3)
-    fprintf(stderr, "[b200cp] bwd-filter (saved planes) tile TH=%d TW=%d blocks per warp %d smem=%zu RP=%d vec=%d\n", g.TH, g.TW, g.MBW,
-            smem, RP, g.vec);
+    fprintf(stderr, "[b200cp] bwd-filter (saved planes) tile TH=%d TW=%d blocks per warp %d slices %d smem=%zu RP=%d vec=%d\n",
+            g.TH, g.TW, g.MBW, g.S, smem, RP, g.vec);
   switch (g.MBW) {
     case 1: return launch_saved<RP, 1>(g, smem, a, P, Q, st, part);
     case 2: return launch_saved<RP, 2>(g, smem, a, P, Q, st, part);
