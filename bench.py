@@ -162,6 +162,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc3x", "mma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"],
+                    help="gradient allreduce of the multi-GPU step: the library's peer-memory kernel, or NCCL")
     ap.add_argument("--separate", action="store_true",
                     help="step = the three entry points one after the other instead of b200cp_cp4_step")
     ap.add_argument("--watchdog", type=int, default=420, help="seconds after which a stuck run dumps its stacks and exits")
@@ -255,6 +257,18 @@ def main():
     dKs = [dK, torch.empty_like(dK)] if dist is not None else [dK]
     comm = torch.cuda.Stream() if dist is not None else None
     ar_done = [None, None]
+    p2p = None
+    if dist is not None and args.allreduce == "p2p":
+        # the library's own exchange kernel over NVLink peer memory; checked once against NCCL before it is used
+        from paralleltnnlayers_b200.dist import P2PAllreduce
+        p2p = P2PAllreduce(dK.numel())
+        probe = torch.randn(dK.numel(), device="cuda")
+        want = probe.clone()
+        dist.all_reduce(want)
+        got = p2p(probe.clone())
+        p2p.status()
+        if not torch.allclose(got, want, rtol=1e-5, atol=1e-6):
+            raise RuntimeError("peer-memory allreduce disagrees with NCCL")
 
     def step(i, st):
         dk = dKs[i % len(dKs)]
@@ -274,7 +288,10 @@ def main():
             ready.record()
             comm.wait_event(ready)
             with torch.cuda.stream(comm):
-                dist.all_reduce(dk)
+                if p2p is not None:
+                    p2p(dk)
+                else:
+                    dist.all_reduce(dk)
                 done = torch.cuda.Event()
                 done.record()
             ar_done[i % 2] = done
@@ -454,8 +471,10 @@ def main():
                            if shared else "b200cp_cp4_fwd + b200cp_cp4_bwd_data + b200cp_cp4_bwd_filter",
                    "timing": "K steps replayed as one CUDA graph between two events" if graphed else "K eager steps between two events",
                    "l2": f"{NSETS} rotating buffer sets ({NSETS * 4 * n * HW * 64 * 4 / 1e6:.0f} MB) > 126 MB L2",
-                   "collective": ("allreduce of %d packed factor-gradient floats per step, on a communication stream, "
-                                  "overlapped with the next step" % nK) if world > 1 else "none"},
+                   "collective": ("allreduce of %d packed factor-gradient floats per step (%s), on a communication stream, "
+                                  "overlapped with the next step"
+                                  % (nK, "b200cp_p2p_allreduce: one kernel over NVLink peer memory" if p2p is not None
+                                     else "NCCL")) if world > 1 else "none"},
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ks},
         "gpu_launches": launches, "clocks": clocks,

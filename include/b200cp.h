@@ -204,6 +204,30 @@ int b200cp_dense_bwd(int B, int order, const int* idims, const int* odims, int R
                      const float* const* F, float* dX, float* const* dF, void* workspace, size_t workspace_bytes,
                      void* stream, int flags);
 
+/* ---- gradient allreduce over peer memory ---------------------------------
+ * The reference is single-GPU (cudaSetDevice, Cuda_kernels/cp4Conv2d.cu:210,221); data parallelism sums the packed
+ * factor gradients of b200cp_cp4_bwd_filter / _step over the ranks.  These calls do that sum with one small kernel
+ * per step over NVLink peer memory, one process per GPU, in place of a library allreduce: every rank stores its
+ * vector into every rank's exchange region, raises a flag, waits (bounded) for the other ranks' flags and adds the
+ * rows in rank order, so all ranks hold bitwise the same result.
+ *
+ *   b200cp_p2p_init      allocates this rank's exchange region (set-up time, not in the hot path) for vectors of up
+ *                        to max_floats floats and writes its 64-byte CUDA IPC handle to handle_out;
+ *   b200cp_p2p_connect   takes all ranks' handles (world * 64 bytes, in rank order; the host exchanges them, e.g.
+ *                        with an all-gather) and maps the peers' regions; all ranks must have returned from it
+ *                        (a host barrier) before the first allreduce;
+ *   b200cp_p2p_allreduce dst[i] = sum over ranks of src[i], asynchronous on `stream`, capturable in a CUDA graph;
+ *                        every rank must issue the same sequence of calls; src and dst may be the same buffer;
+ *   b200cp_p2p_status    synchronises the device; B200CP_ERR_TIMEOUT if a wait for a peer ran out (about 0.5 s);
+ *   b200cp_p2p_destroy   unmaps and frees.
+ * world = 1 is allowed (no IPC, a copy). */
+#define B200CP_P2P_HANDLE_BYTES 64
+int b200cp_p2p_init(int rank, int world, size_t max_floats, unsigned char* handle_out, void** ctx_out);
+int b200cp_p2p_connect(void* ctx, const unsigned char* handles);
+int b200cp_p2p_allreduce(void* ctx, const float* src, float* dst, size_t n, void* stream);
+int b200cp_p2p_status(void* ctx);
+int b200cp_p2p_destroy(void* ctx);
+
 /* ---- misc --------------------------------------------------------------- */
 
 /* Synchronises the device and reports whether any tensor-path kernel gave up a bounded wait since

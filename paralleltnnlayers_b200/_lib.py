@@ -70,6 +70,11 @@ def _load():
         "b200cp_debug_tc_selftest": (i, [i, fp, fp, fp, vp, vp]),
         "b200cp_last_error_string": (C.c_char_p, []),
         "b200cp_status_string": (C.c_char_p, [i]),
+        "b200cp_p2p_init": (i, [i, i, sz, vp, pp]),
+        "b200cp_p2p_connect": (i, [vp, vp]),
+        "b200cp_p2p_allreduce": (i, [vp, fp, fp, sz, vp]),
+        "b200cp_p2p_status": (i, [vp]),
+        "b200cp_p2p_destroy": (i, [vp]),
         "b200cp_launch_count": (C.c_ulonglong, []),
         "b200cp_version": (i, []),
     }

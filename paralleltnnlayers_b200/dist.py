@@ -29,6 +29,59 @@ def allreduce_factor_grads(packed, group=None):
     return packed
 
 
+class P2PAllreduce:
+    """The gradient allreduce as one small kernel over NVLink peer memory (``b200cp_p2p_*``), one process per GPU.
+
+    Set-up (collective, outside the hot path): every rank allocates its exchange region, the 64-byte CUDA IPC
+    handles go round with ``all_gather`` and every rank maps the others' regions.  ``__call__`` then sums a float32
+    CUDA tensor over the ranks in place, asynchronously on the current stream; it can be captured in a CUDA graph.
+    All ranks get bitwise the same sums (rows added in rank order)."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, max_floats, group=None):
+        import ctypes as C
+        from . import _lib
+        self._lib, self._C = _lib, C
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.max_floats = int(max_floats)
+        handle = (C.c_ubyte * self.HANDLE_BYTES)()
+        ctx = C.c_void_p()
+        _lib.check(_lib.lib.b200cp_p2p_init(self.rank, self.world, self.max_floats, handle, C.byref(ctx)))
+        self._ctx = ctx
+        if self.world > 1:
+            mine = torch.tensor(list(handle), dtype=torch.uint8)
+            backend = dist.get_backend(group)
+            dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+            mine = mine.to(dev)
+            every = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(every, mine, group=group)
+            flat = bytes(torch.cat(every).cpu().tolist())
+            buf = (C.c_ubyte * len(flat)).from_buffer_copy(flat)
+            _lib.check(_lib.lib.b200cp_p2p_connect(self._ctx, buf))
+            dist.barrier(group)     # every rank has mapped its peers before anyone starts an exchange
+        else:
+            _lib.check(_lib.lib.b200cp_p2p_connect(self._ctx, None))
+
+    def __call__(self, t, out=None):
+        out = t if out is None else out
+        assert t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and out.is_contiguous()
+        assert out.numel() == t.numel() <= self.max_floats
+        st = torch.cuda.current_stream().cuda_stream
+        self._lib.check(self._lib.lib.b200cp_p2p_allreduce(self._ctx, t.data_ptr(), out.data_ptr(), t.numel(), st))
+        return out
+
+    def status(self):
+        """Synchronises the device; raises if a wait for a peer's flag ran out."""
+        self._lib.check(self._lib.lib.b200cp_p2p_status(self._ctx))
+
+    def close(self):
+        if self._ctx is not None:
+            self._lib.lib.b200cp_p2p_destroy(self._ctx)
+            self._ctx = None
+
+
 def cp4_data_parallel_step(X, dU, FT, FC, FY, FX, pad=1, flags=0, group=None):
     """forward, backward-data and backward-filter on this rank's shard, then the gradient allreduce.
     Returns (U, dX, (dFT, dFC, dFY, dFX)) with the gradients summed over every rank's shard."""
