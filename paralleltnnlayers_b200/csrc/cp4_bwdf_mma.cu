@@ -525,11 +525,20 @@ __device__ __forceinline__ void reduce_pass(const SGeom& g, const float* __restr
           // 16-byte copies: a lane owns four consecutive pixels (never across a tile row: TW % 4 == 0) of
           // 32 / (4*MBW) channel rows per instruction
           const unsigned dst = vdst + (unsigned)((grp % (ALLIN ? MB2 : kFifo)) * kGC * XP * 4);
+          if (grp * kGC + kGC <= cc) {      // all channels of the group exist: no per-copy selects
+            const float* sp = vsrc + coff + (size_t)vrow * HW;
 #pragma unroll
-          for (int jc = 0; jc < kGC / VCPI; ++jc) {
-            const int ch = jc * VCPI + vrow;
-            const bool cin = grp * kGC + ch < cc;
-            cp_async16_s(dst + (unsigned)(jc * VCPI * XP * 4), cin ? vsrc + coff + (size_t)ch * HW : src_n, cin ? vsz : 0);
+            for (int jc = 0; jc < kGC / VCPI; ++jc) {
+              cp_async16_s(dst + (unsigned)(jc * VCPI * XP * 4), sp, vsz);
+              sp += (size_t)VCPI * HW;
+            }
+          } else {
+#pragma unroll
+            for (int jc = 0; jc < kGC / VCPI; ++jc) {
+              const int ch = jc * VCPI + vrow;
+              const bool cin = grp * kGC + ch < cc;
+              cp_async16_s(dst + (unsigned)(jc * VCPI * XP * 4), cin ? vsrc + coff + (size_t)ch * HW : src_n, cin ? vsz : 0);
+            }
           }
         } else {
           const unsigned dst = xw_s + (unsigned)((grp % (ALLIN ? MB2 : kFifo)) * kGC * XP * 4);
