@@ -48,20 +48,35 @@ class P2PAllreduce:
         self.max_floats = int(max_floats)
         handle = (C.c_ubyte * self.HANDLE_BYTES)()
         ctx = C.c_void_p()
-        _lib.check(_lib.lib.b200cp_p2p_init(self.rank, self.world, self.max_floats, handle, C.byref(ctx)))
-        self._ctx = ctx
+        self._ctx = None
+        err = None
+        try:
+            _lib.check(_lib.lib.b200cp_p2p_init(self.rank, self.world, self.max_floats, handle, C.byref(ctx)))
+            self._ctx = ctx
+        except Exception as e:          # keep taking part in the collectives below: all ranks fail together
+            err = e
         if self.world > 1:
-            mine = torch.tensor(list(handle), dtype=torch.uint8)
             backend = dist.get_backend(group)
             dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
-            mine = mine.to(dev)
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
             every = [torch.empty_like(mine) for _ in range(self.world)]
             dist.all_gather(every, mine, group=group)
-            flat = bytes(torch.cat(every).cpu().tolist())
-            buf = (C.c_ubyte * len(flat)).from_buffer_copy(flat)
-            _lib.check(_lib.lib.b200cp_p2p_connect(self._ctx, buf))
-            dist.barrier(group)     # every rank has mapped its peers before anyone starts an exchange
+            if err is None:
+                try:
+                    flat = bytes(torch.cat(every).cpu().tolist())
+                    buf = (C.c_ubyte * len(flat)).from_buffer_copy(flat)
+                    _lib.check(_lib.lib.b200cp_p2p_connect(self._ctx, buf))
+                except Exception as e:
+                    err = e
+            # every rank has mapped its peers before anyone starts an exchange; a failure anywhere fails everywhere
+            ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32, device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
+                self.close()
+                raise RuntimeError(f"peer-memory allreduce set-up failed on some rank (this rank: {err})")
         else:
+            if err is not None:
+                raise err
             _lib.check(_lib.lib.b200cp_p2p_connect(self._ctx, None))
 
     def __call__(self, t, out=None):
