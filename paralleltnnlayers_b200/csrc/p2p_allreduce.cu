@@ -97,6 +97,8 @@ using namespace b200cp;
 
 extern "C" {
 
+int b200cp_p2p_destroy(void* ctx);
+
 int b200cp_p2p_init(int rank, int world, size_t max_floats, unsigned char* handle_out, void** ctx_out) {
   if (!handle_out || !ctx_out) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_init: null argument");
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || max_floats == 0)
@@ -105,27 +107,30 @@ int b200cp_p2p_init(int rank, int world, size_t max_floats, unsigned char* handl
   P2PCtx* c = new P2PCtx();
   c->rank = rank; c->world = world; c->max_floats = max_floats;
   c->row = (max_floats + 3) / 4 * 4;
-  B200CP_CUDA_OK(cudaGetDevice(&c->device));
-  c->bytes = flags_offset(c->row, world) + 2 * (size_t)kP2PCtas * kMaxWorld * sizeof(unsigned);
-  B200CP_CUDA_OK(cudaMalloc(&c->base, c->bytes));
-  B200CP_CUDA_OK(cudaMemset(c->base, 0, c->bytes));
+  c->base = nullptr; c->d_data = nullptr; c->d_flags = nullptr; c->d_seq = nullptr; c->d_status = nullptr;
   for (int p = 0; p < kMaxWorld; ++p) { c->peer[p] = nullptr; c->opened[p] = false; }
-  c->peer[rank] = c->base;
-  B200CP_CUDA_OK(cudaMalloc(&c->d_data, sizeof(float*) * kMaxWorld));
-  B200CP_CUDA_OK(cudaMalloc(&c->d_flags, sizeof(unsigned*) * kMaxWorld));
-  B200CP_CUDA_OK(cudaMalloc(&c->d_seq, sizeof(unsigned) * kP2PCtas));
-  B200CP_CUDA_OK(cudaMemset(c->d_seq, 0, sizeof(unsigned) * kP2PCtas));
-  B200CP_CUDA_OK(cudaMalloc(&c->d_status, sizeof(int)));
-  B200CP_CUDA_OK(cudaMemset(c->d_status, 0, sizeof(int)));
-  static_assert(sizeof(cudaIpcMemHandle_t) == B200CP_P2P_HANDLE_BYTES, "IPC handle size");
+  c->bytes = flags_offset(c->row, world) + 2 * (size_t)kP2PCtas * kMaxWorld * sizeof(unsigned);
   cudaIpcMemHandle_t h;
-  if (world > 1) {
-    B200CP_CUDA_OK(cudaIpcGetMemHandle(&h, c->base));
-  } else {
-    memset(&h, 0, sizeof(h));
+  memset(&h, 0, sizeof(h));
+  static_assert(sizeof(cudaIpcMemHandle_t) == B200CP_P2P_HANDLE_BYTES, "IPC handle size");
+  // every allocation of the context, or none: a failure frees what exists and reports the CUDA error
+  cudaError_t e = cudaGetDevice(&c->device);
+  if (e == cudaSuccess) e = cudaMalloc(&c->base, c->bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->base, 0, c->bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_data, sizeof(float*) * kMaxWorld);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_flags, sizeof(unsigned*) * kMaxWorld);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_seq, sizeof(unsigned) * kP2PCtas);
+  if (e == cudaSuccess) e = cudaMemset(c->d_seq, 0, sizeof(unsigned) * kP2PCtas);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, sizeof(int));
+  if (e == cudaSuccess && world > 1) e = cudaIpcGetMemHandle(&h, c->base);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    b200cp_p2p_destroy(c);
+    return fail(B200CP_ERR_CUDA, "b200cp_p2p_init: %s", cudaGetErrorString(e));
   }
+  c->peer[rank] = c->base;
   memcpy(handle_out, &h, sizeof(h));
-  B200CP_CUDA_OK(cudaDeviceSynchronize());
   *ctx_out = c;
   return B200CP_OK;
 }
