@@ -234,16 +234,6 @@ int b200cp_p2p_destroy(void* ctx);
  * the last call (B200CP_ERR_TIMEOUT), clearing the record.  B200CP_OK otherwise. */
 int b200cp_device_status(void);
 
-/* Diagnostic: the tensor-path forward with the first CTA's rank-R intermediate P copied out
- * (P_block0: [RP][Mmax] floats, may be NULL).  terms = 3 (split) or 1 (single tf32 pass). */
-int b200cp_debug_cp4_tc(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,
-                        const float* KH, const float* KW, float* U, float* P_block0, int terms, void* stream);
-
-/* Diagnostic: one tcgen05.mma, D[128x16] = A[128x8] * B[16x8]^T (all device pointers, row-major).
- * mode 0: A staged K-major without swizzle; mode 1: A staged MN-major with the 128-byte swizzle.
- * *status (device int) is 0 on success, 1 if the bounded wait for the MMA ran out. */
-int b200cp_debug_tc_selftest(int mode, const float* A, const float* B, float* D, int* status, void* stream);
-
 /* Text of the last error raised on the calling thread ("" if none). */
 const char* b200cp_last_error_string(void);
 const char* b200cp_status_string(int status);

@@ -66,8 +66,6 @@ def _load():
         "b200cp_dense_bwd_workspace_bytes": (sz, [i, i, ip, ip, i, i]),
         "b200cp_dense_bwd": (i, [i, i, ip, ip, i, fp, fp, pp, fp, pp, vp, sz, vp, i]),
         "b200cp_device_status": (i, []),
-        "b200cp_debug_cp4_tc": (i, [sp, fp, fp, fp, fp, fp, fp, fp, i, vp]),
-        "b200cp_debug_tc_selftest": (i, [i, fp, fp, fp, vp, vp]),
         "b200cp_last_error_string": (C.c_char_p, []),
         "b200cp_status_string": (C.c_char_p, [i]),
         "b200cp_p2p_init": (i, [i, i, sz, vp, pp]),
@@ -78,14 +76,25 @@ def _load():
         "b200cp_launch_count": (C.c_ulonglong, []),
         "b200cp_version": (i, []),
     }
-    for name, (res, args) in sig.items():
-        fn = getattr(lib, name)      # AttributeError if the ABI and the library disagree
-        fn.restype = res
-        fn.argtypes = args
-    return lib, tuple(sig)
+    # test and diagnostic entry points (include/b200cp_test.h)
+    test_sig = {
+        "b200cp_debug_cp4_tc": (i, [sp, fp, fp, fp, fp, fp, fp, fp, i, vp]),
+        "b200cp_debug_tc_selftest": (i, [i, fp, fp, fp, vp, vp]),
+        "b200cp_test_set_band_rows": (None, [i]),
+        "b200cp_test_set_band_trace": (None, [vp]),
+        "b200cp_test_set_band_tensor_loads": (None, [i]),
+        "b200cp_test_set_p2p_wait_cycles": (None, [C.c_longlong]),
+        "b200cp_test_p2p_connect_local": (i, [vp, pp]),
+    }
+    for table in (sig, test_sig):
+        for name, (res, args) in table.items():
+            fn = getattr(lib, name)      # AttributeError if the ABI and the library disagree
+            fn.restype = res
+            fn.argtypes = args
+    return lib, tuple(sig), tuple(test_sig)
 
 
-lib, EXPORTS = _load()
+lib, EXPORTS, TEST_EXPORTS = _load()
 
 
 def check(status):

@@ -6,6 +6,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "b200cp_test.h"
 
 namespace b200cp {
 
@@ -79,10 +80,8 @@ const bool g_auto_mma = [] {
   return !(e && e[0] == '0');
 }();
 
-int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, const float* K1, const float* KH,
-             const float* KW, float* out, cudaStream_t st, int flags, bool backward, const float* KC = nullptr,
-             float* save = nullptr) {
-  const int path = path_of(flags);
+Cp4Args conv_args(const b200cp_tensor_shape* s, const float* in, const float* K0, const float* K1, const float* KH,
+                  const float* KW, float* out, bool backward, const float* KC, float* save) {
   Cp4Args a{};
   a.N = s->N; a.H = s->H; a.W = s->W; a.Y = s->Y; a.X = s->X; a.pad = s->pad;
   a.Cin = backward ? s->T : s->C;
@@ -93,6 +92,18 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
   a.flip = backward ? 1 : 0;
   a.Rs = s->Rank;
   a.R = s->Rank;
+  return a;
+}
+
+bool takes_mma(int path, const float* KC, const float* save) {
+  return KC || save || path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma);
+}
+
+int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, const float* K1, const float* KH,
+             const float* KW, float* out, cudaStream_t st, int flags, bool backward, const float* KC = nullptr,
+             float* save = nullptr) {
+  const int path = path_of(flags);
+  Cp4Args a = conv_args(s, in, K0, K1, KH, KW, out, backward, KC, save);
   if (KC && path != B200CP_PATH_AUTO && path != B200CP_PATH_MMA)
     return fail(B200CP_ERR_UNSUPPORTED, "the three-factor CP conv runs on the mma path only (flags AUTO or MMA)");
   if (path == B200CP_PATH_TC3X || path == B200CP_PATH_TC1X) return cp4_tc_launch(a, path == B200CP_PATH_TC3X ? 3 : 1, nullptr, st);
@@ -101,11 +112,16 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
     if (int rc = device_info(&di)) return rc;
     if (cp4_tc_supported(a, di, nullptr)) return cp4_tc_launch(a, 3, nullptr, st);
   }
+  const bool mma = takes_mma(path, KC, save);
+  if (mma && s->Rank <= 32) {   // row bands with TMA loads where the shape allows them
+    bool done = false;
+    if (int rc = cp4_band_launch(&a, 1, st, &done)) return rc;
+    if (done) return B200CP_OK;
+  }
   for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);
     a.accumulate = r0 > 0;
-    const bool mma = KC || save || path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma);
     if (int rc = (mma ? cp4_mma_launch(a, st) : cp4_simt_launch(a, st))) return rc;
   }
   return B200CP_OK;
@@ -352,8 +368,17 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
     B200CP_CUDA_OK(cudaEventRecord(fk->fork, st));
     B200CP_CUDA_OK(cudaStreamWaitEvent(fk->side, fk->fork, 0));
   }
-  if (int rc = run_conv(s, X, K0, K1, KH, KW, U, st, flags, false, nullptr, P)) return rc;
-  if (int rc = run_conv(s, dU, K0, K1, KH, KW, dX, fork ? fk->side : st, flags, true, nullptr, Q)) return rc;
+  // forward and backward-data: one launch of the band kernel carries both where the shape allows it; otherwise
+  // two launches side by side
+  bool both = false;
+  if (s->Rank <= 32) {
+    Cp4Args cv[2] = {conv_args(s, X, K0, K1, KH, KW, U, false, nullptr, P), conv_args(s, dU, K0, K1, KH, KW, dX, true, nullptr, Q)};
+    if (int rc = cp4_band_launch(cv, 2, st, &both)) return rc;
+  }
+  if (!both) {
+    if (int rc = run_conv(s, X, K0, K1, KH, KW, U, st, flags, false, nullptr, P)) return rc;
+    if (int rc = run_conv(s, dU, K0, K1, KH, KW, dX, fork ? fk->side : st, flags, true, nullptr, Q)) return rc;
+  }
   Cp4BwdFilterArgs a{};
   a.N = s->N; a.C = s->C; a.T = s->T; a.H = s->H; a.W = s->W; a.F = 3; a.pad = 1;
   a.Rs = s->Rank;
@@ -660,6 +685,8 @@ int b200cp_device_status(void) {
   if (v) return fail(B200CP_ERR_TIMEOUT, "a bounded wait ran out in block %d (code %d)", v & 0xffff, v >> 16);
   if (int rc = gemm_tc_status(&v)) return rc;
   if (v) return fail(B200CP_ERR_TIMEOUT, "gradient GEMM: a bounded wait ran out in block %d", v & 0xffff);
+  if (int rc = band_device_status(&v)) return rc;
+  if (v) return fail(B200CP_ERR_TIMEOUT, "cp4 band kernel: a bounded wait ran out in block %d", v & 0xffff);
   return B200CP_OK;
 }
 

@@ -66,6 +66,11 @@ int cp4_simt_launch(const Cp4Args& a, cudaStream_t st);
 // same arguments; channel contractions on the warp-level tensor path (mma.sync, three tf32 terms)
 int cp4_mma_launch(const Cp4Args& a, cudaStream_t st);
 
+// Full-width row bands, TMA loads (3x3 filters, pad 1, W a multiple of 4, at most 32 ranks per launch): one or two
+// convolutions of the same image size in one launch.  *done = false: not a shape this kernel takes.
+int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done);
+int band_device_status(int* out);
+
 struct Cp4BwdFilterArgs {
   int N, C, T, H, W, F, pad;
   int R, Rs, r0;

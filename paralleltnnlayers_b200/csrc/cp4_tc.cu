@@ -58,10 +58,6 @@ struct TcGeom {
 
 __device__ __forceinline__ int floor4(int v) { return v - (((v % 4) + 4) % 4); }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 // Bounded wait shared by the three roles: gives up after about a second, or as soon as another
 // role has given up (the flag), so that every thread reaches the common exit.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -138,8 +134,10 @@ __global__ void __launch_bounds__(kNT) cp4_tc_kernel(const TcGeom g, const __gri
                                                      const float* __restrict__ Fin, const float* __restrict__ Fout,
                                                      const float* __restrict__ KH, const float* __restrict__ KW,
                                                      float* __restrict__ out, float* __restrict__ dbgP) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // pointer arithmetic on the shared array keeps every access a shared-space access (a round trip through an
+  // integer would turn them into generic loads and stores); the pad aligns the base to the swizzle atom
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   float* Ws = reinterpret_cast<float*>(sm + g.oWs);
   float* Ps = reinterpret_cast<float*>(sm + g.oPs);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + g.oBar);

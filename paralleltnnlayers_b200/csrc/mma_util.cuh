@@ -32,6 +32,14 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// The same instruction kept in program order: the issue order of independent accumulator chains is part of the
+// design (consecutive mma on one accumulator must be far enough apart to hide its latency).
+__device__ __forceinline__ void mma_tf32_ordered(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
 // Four 8 x 4 tiles of 32-bit values (ldmatrix on 8 x 8 b16 tiles): lane l gives the address of row l%8 of tile l/8
 // (16-byte aligned); every thread receives element (row lane/4, column lane%4) of each tile -- the layout of the
 // tf32 A fragment rows and of a "col" B fragment whose K index is contiguous in shared memory.

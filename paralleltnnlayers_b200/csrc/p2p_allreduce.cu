@@ -6,15 +6,19 @@
 //   1. the rank stores its vector into slot s, row `rank`, of EVERY rank's region (plain peer stores),
 //   2. fences and raises flag (s, rank) in every region to the step's sequence number,
 //   3. waits until all `world` flags of slot s in its OWN region carry that number (a bounded wait: about half a
-//      second, then a status word is set and the kernel leaves),
+//      second, then a status word is set, the result is filled with NaN -- a missed exchange cannot pass for a sum --
+//      and the kernel leaves; b200cp_p2p_status reports it),
 //   4. adds the `world` rows of its own region in rank order, so every rank gets bitwise the same sums.
+// Flags are written with st.release.sys after a system-scope fence and polled with ld.acquire.sys.
 // Two slots alternate.  A rank that writes slot s for step q has finished step q - 1, for which it needed every
 // peer's flag of step q - 1; a peer raises that flag in its launch q - 1, which runs after its launch q - 2 has read
 // slot s.  So a slot is never overwritten while a peer still reads it.  The sequence number lives in device memory and is advanced by the kernel, so a captured CUDA graph can
 // be replayed.  No NCCL kernel, no multicast, no peer loads: a CTA of 256 threads that fits next to the compute kernels.
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
+#include "b200cp_test.h"
 
 namespace b200cp {
 
@@ -23,6 +27,17 @@ namespace {
 constexpr int kMaxWorld = 16;
 constexpr int kP2PThreads = 256;
 constexpr int kP2PCtas = 4;   // CTAs of one exchange; each moves a quarter of the vector and has its own flags
+constexpr long long kDefaultWaitCycles = 1000000000ll;   // about half a second
+std::atomic<long long> g_wait_cycles{kDefaultWaitCycles};
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 struct P2PCtx {
   int rank, world, device;
@@ -43,11 +58,16 @@ __host__ __device__ inline size_t flags_offset(size_t row, int world) { return 2
 __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(float* const* __restrict__ data,
                                                                     unsigned* const* __restrict__ flags, unsigned* seqs,
                                                                     int* status, int rank, int world, size_t row,
-                                                                    const float* src, float* dst, size_t n) {
+                                                                    const float* src, float* dst, size_t n,
+                                                                    long long wait_cycles) {
   // (src and dst may be the same buffer: a CTA reads and writes only its own part of the vector)
   const int cta = blockIdx.x, tid = threadIdx.x;
   __shared__ unsigned s_seq;
-  if (tid == 0) s_seq = seqs[cta] + 1;
+  __shared__ int s_missed;
+  if (tid == 0) {
+    s_seq = seqs[cta] + 1;
+    s_missed = 0;
+  }
   __syncthreads();
   const unsigned seq = s_seq;
   const int slot = seq & 1;
@@ -61,32 +81,36 @@ __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(float* const
   }
   __threadfence_system();
   __syncthreads();
-  // 2. flag (slot, cta, rank) of every region
+  // 2. flag (slot, cta, rank) of every region: the CTA's stores were fenced above by the threads that made them;
+  //    the flag-writing thread fences again after the barrier and stores with release semantics
   if (tid < world) {
-    volatile unsigned* f = flags[tid] + ((size_t)slot * kP2PCtas + cta) * kMaxWorld + rank;
-    *f = seq;
+    __threadfence_system();
+    st_release_sys(flags[tid] + ((size_t)slot * kP2PCtas + cta) * kMaxWorld + rank, seq);
   }
   // 3. all flags of the own region
-  bool ok = true;
   if (tid < world) {
-    volatile unsigned* f = flags[rank] + ((size_t)slot * kP2PCtas + cta) * kMaxWorld + tid;
+    const unsigned* f = flags[rank] + ((size_t)slot * kP2PCtas + cta) * kMaxWorld + tid;
     const long long t0 = clock64();
-    while ((int)(*f - seq) < 0) {
-      if (clock64() - t0 > 1000000000ll) { ok = false; break; }   // about half a second: give up, never hang
+    while ((int)(ld_acquire_sys(f) - seq) < 0) {
+      if (clock64() - t0 > wait_cycles) {   // give up, never hang
+        s_missed = 1;
+        atomicExch(status, 1 + rank);
+        break;
+      }
       __nanosleep(64);
     }
   }
-  if (!ok) atomicExch(status, 1 + rank);
   __threadfence_system();
   __syncthreads();
-  // 4. the rows of the own region, in rank order
+  // 4. the rows of the own region, in rank order; NaN where a peer's part never arrived
+  const bool missed = s_missed != 0;
   const float* own = data[rank] + (size_t)slot * world * row;
   for (size_t i = lo + tid; i < hi; i += kP2PThreads) {
     float s = 0.f;
     for (int p = 0; p < world; ++p) s += __ldcg(own + (size_t)p * row + i);
-    dst[i] = s;
+    dst[i] = missed ? __int_as_float(0x7fc00000) : s;
   }
-  if (tid == 0) seqs[cta] = seq;
+  if (tid == 0) seqs[cta] = seq;   // the sequence advances either way: the next exchange lines up with the peers' again
 }
 
 }  // namespace
@@ -161,8 +185,30 @@ int b200cp_p2p_allreduce(void* ctx, const float* src, float* dst, size_t n, void
   if (!c || !src || !dst) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_allreduce: null argument");
   if (n > c->max_floats) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_allreduce: %zu floats, room for %zu", n, c->max_floats);
   p2p_allreduce_kernel<<<kP2PCtas, kP2PThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      c->d_data, c->d_flags, c->d_seq, c->d_status, c->rank, c->world, c->row, src, dst, n);
+      c->d_data, c->d_flags, c->d_seq, c->d_status, c->rank, c->world, c->row, src, dst, n, g_wait_cycles.load());
   B200CP_LAUNCH_OK("p2p_allreduce_kernel");
+  return B200CP_OK;
+}
+
+void b200cp_test_set_p2p_wait_cycles(long long cycles) { g_wait_cycles.store(cycles > 0 ? cycles : kDefaultWaitCycles); }
+
+// Test hook: the ranks of a single-process world (contexts made by b200cp_p2p_init in this process, in rank order)
+// map each other's regions directly instead of through CUDA IPC.
+int b200cp_test_p2p_connect_local(void* ctx, void* const* all_ctx) {
+  P2PCtx* c = static_cast<P2PCtx*>(ctx);
+  if (!c || !all_ctx) return fail(B200CP_ERR_INVALID_ARG, "b200cp_test_p2p_connect_local: null argument");
+  float* data[kMaxWorld] = {};
+  unsigned* flags[kMaxWorld] = {};
+  for (int p = 0; p < c->world; ++p) {
+    P2PCtx* o = static_cast<P2PCtx*>(all_ctx[p]);
+    if (!o || o->world != c->world || o->row != c->row || o->rank != p)
+      return fail(B200CP_ERR_INVALID_ARG, "b200cp_test_p2p_connect_local: context %d does not belong to this world", p);
+    c->peer[p] = o->base;
+    data[p] = static_cast<float*>(o->base);
+    flags[p] = reinterpret_cast<unsigned*>(static_cast<char*>(o->base) + flags_offset(c->row, c->world));
+  }
+  B200CP_CUDA_OK(cudaMemcpy(c->d_data, data, sizeof(data), cudaMemcpyHostToDevice));
+  B200CP_CUDA_OK(cudaMemcpy(c->d_flags, flags, sizeof(flags), cudaMemcpyHostToDevice));
   return B200CP_OK;
 }
 

@@ -227,6 +227,16 @@ def device_status():
     check(lib.b200cp_device_status())
 
 
+def set_band_rows(rows):
+    """Test hook: force the band height of the row-band CP4 kernel (0: the planner chooses)."""
+    lib.b200cp_test_set_band_rows(int(rows))
+
+
+def set_band_tensor_loads(on):
+    """Test hook: the row-band kernel loads its input with 4-D tensor-map boxes (True) or 1-D bulk copies (False)."""
+    lib.b200cp_test_set_band_tensor_loads(1 if on else 0)
+
+
 def debug_cp4_tc(Input, FT, FC, FY, FX, pad=1, terms=3, p_floats=0):
     """Diagnostic forward on the tensor path; also returns the first CTA's rank-R intermediate."""
     Input, FT, FC, FY, FX = (_dev(t, n) for t, n in ((Input, "Input"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))

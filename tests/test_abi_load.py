@@ -16,6 +16,19 @@ def test_exports_match_header(lib_built):
         assert hasattr(lib, name), f"{name} is declared in include/b200cp.h but not exported"
 
 
+def test_test_header_exports(lib_built):
+    """The test-only header (diagnostics, test hooks) is exported and bound too, apart from the product interface."""
+    from paralleltnnlayers_b200 import _lib
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    hdr = re.sub(r"/\*.*?\*/", "", open(os.path.join(root, "include", "b200cp_test.h")).read(), flags=re.S)
+    declared = set(re.findall(r"\b(b200cp_[a-z0-9_]+)\s*\(", hdr))
+    assert declared == set(_lib.TEST_EXPORTS)
+    lib = ctypes.CDLL(lib_built)
+    for name in declared:
+        assert hasattr(lib, name)
+    assert not declared & set(_lib.EXPORTS)
+
+
 def test_python_binding_covers_header(lib_built):
     from paralleltnnlayers_b200 import _lib
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
