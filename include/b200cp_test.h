@@ -30,6 +30,10 @@ void b200cp_test_set_band_rows(int rows);
  * 0 = one 1-D bulk copy per channel (cp.async.bulk; the default).  Process-wide. */
 void b200cp_test_set_band_tensor_loads(int on);
 
+/* Output contraction of the row-band kernel: 1 = tcgen05.mma with the accumulators in tensor memory where the shape
+ * allows it, 0 = mma.sync with the output staged in shared memory (the default: it measures faster).  Process-wide. */
+void b200cp_test_set_band_tcgen05(int on);
+
 /* Diagnostics: the row-band kernel writes 64 cycle stamps (long long) per CTA for its first 512 CTAs into this
  * device buffer (512 * 64 * 8 bytes); NULL switches it off.  Process-wide. */
 void b200cp_test_set_band_trace(void* device_buffer);

@@ -65,6 +65,7 @@ struct BandGeom {
   int tensor;                       // 1: one 4-D tensor-map load per stage; 0: one 1-D bulk copy per channel
   int NB3;                          // n-blocks (8 pixels) of phase 3
   int obuf;                         // output tiles in shared memory (2: a tile drains while the next one fills)
+  int NMB, ncols;                   // tcgen05 phase 3: blocks of 128 own pixels, TMEM columns allocated
   int XP, PP, ZP, OP, FP1, FP2;     // row pitches (floats): stage channel, P plane, Z plane, output tile, factor planes
   int CoutPad;                      // rows of the Fout planes (multiple of 16, maximum over the two convolutions)
   int stage_floats;
@@ -115,7 +116,8 @@ __device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, %0;
 
 // NBW1: halo n-blocks (8 pixels) per consumer warp in phase 1; warp w owns blocks w, w + 9, w + 18, ...  Blocks past
 // the band are computed on whatever the shared memory holds there and never stored: no mma sits under a branch.
-template <int RP, int NBW1>
+// TC3: phase 3 on the fifth-generation tensor cores (tcgen05.mma, accumulators in TMEM) instead of mma.sync.
+template <int RP, int NBW1, bool TC3>
 __global__ void __launch_bounds__(kNT, RP <= 16 ? 2 : 1)
 cp4_band_kernel(const BandGeom g, const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                 const BandProb p0, const BandProb p1) {
@@ -134,7 +136,9 @@ cp4_band_kernel(const BandGeom g, const __grid_constant__ CUtensorMap map0, cons
   float* Ws = reinterpret_cast<float*>(sm + g.oW);    // [9][RP]
   uint64_t* full = reinterpret_cast<uint64_t*>(sm + g.oBar);
   uint64_t* empty = full + kMaxStages;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxStages);
+  uint64_t* d2bar = empty + kMaxStages;               // [4] tcgen05 phase 3: accumulator of a pixel block complete
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(d2bar + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d2bar + 4) + 1;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;
@@ -149,7 +153,7 @@ cp4_band_kernel(const BandGeom g, const __grid_constant__ CUtensorMap map0, cons
   const int S = g.stages;
   // halo rows [ra, rb) of the band lie inside the image (halo row i is image row h0 - 1 + i)
   const int ra = h0 == 0 ? 1 : 0, rb = min(g.TH + 2, g.H - h0 + 1);
-  if (smem_u32(sm) & 127) {   // cannot happen with the launch this file does; never run on a misaligned base
+  if (smem_u32(sm) & (TC3 ? 1023 : 127)) {   // cannot happen with the launch this file does; never run on a misaligned base
     if (tid == 0) atomicCAS(&g_band_status, 0, (2 << 16) | (int)(blockIdx.x & 0xffff));
     return;
   }
@@ -162,6 +166,8 @@ cp4_band_kernel(const BandGeom g, const __grid_constant__ CUtensorMap map0, cons
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], kCons);
     }
+    if (TC3)
+      for (int i = 0; i < 4; ++i) mbar_init(&d2bar[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
     if (g.tensor) tma_prefetch_desc(map);
@@ -171,6 +177,10 @@ cp4_band_kernel(const BandGeom g, const __grid_constant__ CUtensorMap map0, cons
   float acc[MB][NBW1][4];
   if (warp == kCons) {
     // ================= producer: streams the band's channels through the ring =====================================
+    if (TC3) {   // this warp also owns the CTA's tensor memory: allocated here, released at the very end
+      tc::tmem_alloc(tmem_slot, (uint32_t)g.ncols);
+      tc::tc_fence_before_sync();
+    }
     const uint32_t row_bytes = (uint32_t)W * 4u;
     const float* src0 = p.in + ((size_t)n * p.Cin * g.H + (size_t)(h0 - 1 + ra)) * W;   // channel 0, first row inside
     if (g.stagger > 0 && (int)blockIdx.x >= g.sm_count && (int)blockIdx.x < 2 * g.sm_count) {
@@ -214,14 +224,16 @@ cp4_band_kernel(const BandGeom g, const __grid_constant__ CUtensorMap map0, cons
         F1[r * FP1 + c] = hi;
         F1[kF1 + r * FP1 + c] = tf32_round(v - hi);
       }
-      const int kF2 = g.CoutPad * FP2;
+      if (!TC3) {
+        const int kF2 = g.CoutPad * FP2;
 #pragma unroll 4
-      for (int i = tid; i < g.CoutPad * RP; i += NTC) {
-        const int t = i / RP, r = i - t * RP;
-        const float v = (r < g.R && t < p.Cout) ? __ldg(p.Fout + (size_t)t * g.Rs + g.r0 + r) : 0.f;
-        const float hi = tf32_round(v);
-        F2[t * FP2 + r] = hi;
-        F2[kF2 + t * FP2 + r] = tf32_round(v - hi);
+        for (int i = tid; i < g.CoutPad * RP; i += NTC) {
+          const int t = i / RP, r = i - t * RP;
+          const float v = (r < g.R && t < p.Cout) ? __ldg(p.Fout + (size_t)t * g.Rs + g.r0 + r) : 0.f;
+          const float hi = tf32_round(v);
+          F2[t * FP2 + r] = hi;
+          F2[kF2 + t * FP2 + r] = tf32_round(v - hi);
+        }
       }
       for (int i = tid; i < 9 * RP; i += NTC) {
         const int r = i % RP, yx = i / RP, y = yx / 3, x = yx - y * 3;
@@ -337,7 +349,25 @@ cp4_band_kernel(const BandGeom g, const __grid_constant__ CUtensorMap map0, cons
     stamp(2);
   }
   __syncthreads();   // the ring is free: every stage has landed and has been read
-  const bool aborted = *abort_flag != 0;   // uniform: nobody waits on an mbarrier past this point
+  const bool aborted = *abort_flag != 0;   // uniform: no thread is inside a wait at this point
+  uint32_t tmem_base = 0;
+  if (TC3) {
+    tc::tc_fence_after_sync();
+    tmem_base = *tmem_slot;
+    // Fout as the B operand of tcgen05.mma (K-major core matrices, no swizzle): element (t, r) at
+    // (t/8) * RP*32 + (r/4) * 128 + (t%8) * 16 + (r%4) * 4 bytes, hi | lo.  It takes the place of the phase-1 factor
+    // planes, which nobody reads any more.
+    uint8_t* b2 = sm + g.oF1;
+    const int plane = g.CoutPad * RP * 4;
+    for (int i = tid; i < g.CoutPad * RP; i += kNT) {
+      const int t = i / RP, r = i - t * RP;
+      const float v = (r < g.R && t < p.Cout) ? __ldg(p.Fout + (size_t)t * g.Rs + g.r0 + r) : 0.f;
+      const float hi = tf32_round(v);
+      const int o = (t >> 3) * (RP * 32) + (r >> 2) * 128 + (t & 7) * 16 + (r & 3) * 4;
+      *reinterpret_cast<float*>(b2 + o) = hi;
+      *reinterpret_cast<float*>(b2 + plane + o) = tf32_round(v - hi);
+    }
+  }
 
   // P fragments -> Ps[r][halo px]
   const int own_rows = min(g.TH, g.H - h0);            // band rows inside the image
@@ -405,16 +435,112 @@ cp4_band_kernel(const BandGeom g, const __grid_constant__ CUtensorMap map0, cons
           z[j] = fmaf(w[dy * 3 + 2], v[j + 2], z[j]);
         }
       }
-      float* zd = Zs + r * ZP + oy * W + x0;
-      *reinterpret_cast<float4*>(zd) = make_float4(z[0], z[1], z[2], z[3]);
-      if (hi_ok) *reinterpret_cast<float4*>(zd + 4) = make_float4(z[4], z[5], z[6], z[7]);
+      if (TC3) {
+        // Z as the A operand of tcgen05.mma, already split: blocks of 128 pixels x 8 ranks, pixels contiguous
+        // ("MN-major"), rows of 32 pixels = 128 bytes per rank, the four 32-byte chunks of a row permuted by the
+        // rank (the 128-byte swizzle with 32-byte atoms); hi plane, then lo plane
+        uint8_t* zp = reinterpret_cast<uint8_t*>(Zs) + (r >> 3) * 4096 + (r & 7) * 128;
+        const int planeZ = g.NMB * KS3 * 4096;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (h == 0 || hi_ok) {
+            const int q = oy * W + x0 + 4 * h;
+            const int o = (q >> 7) * (KS3 * 4096) + ((q & 127) >> 5) * 1024 + ((((q & 31) >> 3) ^ (r & 3)) << 5) + (q & 7) * 4;
+            float4 hi4, lo4;
+            hi4.x = tf32_round(z[4 * h + 0]); hi4.y = tf32_round(z[4 * h + 1]);
+            hi4.z = tf32_round(z[4 * h + 2]); hi4.w = tf32_round(z[4 * h + 3]);
+            lo4.x = z[4 * h + 0] - hi4.x; lo4.y = z[4 * h + 1] - hi4.y; lo4.z = z[4 * h + 2] - hi4.z; lo4.w = z[4 * h + 3] - hi4.w;
+            *reinterpret_cast<float4*>(zp + o) = hi4;
+            *reinterpret_cast<float4*>(zp + planeZ + o) = lo4;
+          }
+        }
+      } else {
+        float* zd = Zs + r * ZP + oy * W + x0;
+        *reinterpret_cast<float4*>(zd) = make_float4(z[0], z[1], z[2], z[3]);
+        if (hi_ok) *reinterpret_cast<float4*>(zd + 4) = make_float4(z[4], z[5], z[6], z[7]);
+      }
       oy += dy_step;
       sx += dx_step;
       if (sx >= spr) { sx -= spr; ++oy; }
     }
   }
+  if (TC3) {
+    tc::fence_proxy_async();     // this thread's writes of Z and of the Fout operand become visible to the tensor core
+    tc::tc_fence_before_sync();
+  }
   __syncthreads();
   stamp(4);
+
+  if (TC3) {
+    // ---- phase 3 on tcgen05 ------------------------------------------------------------------------------------------
+    // out[px, t] = sum_r Z[px, r] Fout[t, r] per block of 128 own pixels: M = 128, N = CoutPad, K = 8 ranks per
+    // instruction, three instructions per K step (lo*hi + hi*lo + hi*hi), accumulators in tensor memory, one column
+    // range per pixel block.  One thread issues everything; each block's completion arrives on its own mbarrier and
+    // the warps read their lane quarter out (tcgen05.ld) and store it: a warp instruction writes 32 consecutive pixels
+    // of one channel, i.e. one whole line.
+    const int vpx = own_rows * W;
+    if (!aborted && warp == kCons && lane == 0) {
+      tc::tc_fence_after_sync();
+      const uint32_t idesc = tc::make_idesc_tf32((uint32_t)g.CoutPad, 1, 0);
+      const uint64_t dA = tc::make_smem_desc(0, 1024, 512, tc::kSwizzle128B_32B);
+      const uint64_t dB = tc::make_smem_desc(0, 128, RP * 32, tc::kSwizzleNone);
+      const uint32_t zhi = smem_u32(Zs), zlo = zhi + (uint32_t)(g.NMB * KS3 * 4096);
+      const uint32_t bhi = smem_u32(sm + g.oF1), blo = bhi + (uint32_t)(g.CoutPad * RP * 4);
+      for (int mb = 0; mb < g.NMB; ++mb) {
+        const uint32_t tD = tmem_base + (uint32_t)(mb * g.CoutPad);
+#pragma unroll
+        for (int ks = 0; ks < KS3; ++ks) {
+          const uint32_t ao = (uint32_t)((mb * KS3 + ks) * 4096), bo = (uint32_t)(ks * 256);
+          const uint64_t ah = dA + (uint64_t)((zhi + ao) >> 4), al = dA + (uint64_t)((zlo + ao) >> 4);
+          const uint64_t bh = dB + (uint64_t)((bhi + bo) >> 4), bl = dB + (uint64_t)((blo + bo) >> 4);
+          tc::mma_tf32_ss(tD, al, bh, idesc, ks != 0);
+          tc::mma_tf32_ss(tD, ah, bl, idesc, true);
+          tc::mma_tf32_ss(tD, ah, bh, idesc, true);
+        }
+        tc::mma_commit(&d2bar[mb]);
+      }
+    }
+    if (!aborted) {
+      const int qd = warp & 3;                       // the TMEM lane quarter this warp may read
+      const int nq = (kWarps - qd + 3) >> 2;         // warps that share it
+      float* outp = p.out + (size_t)n * p.Cout * HW + (size_t)h0 * W;
+      for (int mb = warp >> 2; mb < g.NMB; mb += nq) {
+        if (mb * 128 + qd * 32 >= vpx) continue;     // nothing of this quarter lies inside the band
+        if (mb < 4) stamp(16 + 4 * mb);
+        bool ok3 = wait_or_abort(&d2bar[mb], 0, abort_flag);
+        ok3 = __all_sync(0xffffffffu, ok3);
+        if (!ok3) break;
+        if (mb < 4) stamp(17 + 4 * mb);
+        tc::tc_fence_after_sync();
+        const int px = mb * 128 + qd * 32 + lane;
+        float* o = outp + px;
+        const uint32_t ta = tmem_base + ((uint32_t)(qd * 32) << 16) + (uint32_t)(mb * g.CoutPad);
+        for (int c0 = 0; c0 < g.CoutPad; c0 += 16) {
+          float v[16];
+          tc::tmem_ld16(ta + (uint32_t)c0, v);
+          if (px < vpx) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (c0 + i < p.Cout) o[(size_t)(c0 + i) * HW] = v[i];
+          }
+        }
+        if (mb < 4) stamp(18 + 4 * mb);
+      }
+    }
+    stamp(5);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kCons) {
+      tc::tc_fence_after_sync();
+      tc::tmem_dealloc(tmem_base, (uint32_t)g.ncols);
+    }
+    if (*abort_flag) {
+      if (tid == 0) atomicCAS(&g_band_status, 0, (1 << 16) | (int)(blockIdx.x & 0xffff));
+      const long long t0 = clock64();
+      while (clock64() - t0 < 400000) {}
+    }
+    return;
+  }
 
   // ---- phase 3 ----------------------------------------------------------------------------------------------------
   // n-block nb = warp + 10 i covers own pixels [8 nb, 8 nb + 8); a group of NG blocks per warp covers 80 NG
@@ -575,12 +701,35 @@ std::atomic<int> g_band_th{[] {   // forced band height: B200CP_BAND_TH at load,
 struct BandPlan {
   BandGeom g;
   int RP, NBW1;
+  bool tc3;
   size_t smem;
   int per_sm;
 };
 
-bool fill_plan(int RP, int N, int H, int W, int Cin_max, int Cout_max, int TH, int tensor, const DeviceInfo& di,
-               BandPlan* out) {
+int next_pow2_cols(int v) {
+  int p = 32;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+// Phase 3 on tcgen05 (B200CP_BAND_TC3=1, or the test hook) or on mma.sync (default).  Measured at N=32, C=T=64,
+// 56x56, R=16: 23.3 us against 21.9 us -- the accumulators leave tensor memory one pixel per lane, so the stores are
+// 4 bytes per lane, and the stencil has to write its result split and swizzled; the mma.sync form copies its
+// staged tile out 16 bytes per lane.
+std::atomic<int> g_band_tc3{[] {
+  const char* e = getenv("B200CP_BAND_TC3");
+  return e ? atoi(e) : 0;
+}()};
+// Cycles by which the producer of the second CTA of every SM delays its first load (B200CP_BAND_STAGGER).  Two CTAs
+// that start together load, compute and store in lockstep; a shift of about 1.5 us lets one compute while the
+// other's input arrives (measured: 22.5 -> 21.0 us per convolution at the size above).
+const int g_band_stagger = [] {
+  const char* e = getenv("B200CP_BAND_STAGGER");
+  return e ? atoi(e) : 3000;
+}();
+
+bool fill_plan(int RP, int N, int H, int W, int Cin_max, int Cout_max, int TH, int tensor, bool want_tc3,
+               const DeviceInfo& di, BandPlan* out) {
   BandGeom g{};
   g.N = N; g.H = H; g.W = W;
   g.TH = TH;
@@ -611,11 +760,19 @@ bool fill_plan(int RP, int N, int H, int W, int Cin_max, int Cout_max, int TH, i
   g.FP1 = CinPad + 4;
   g.FP2 = RP + 4;
   g.CoutPad = (Cout_max + 15) / 16 * 16;
-  const size_t planeP = align_up((size_t)RP * g.PP * 4, 128), planeZ = align_up((size_t)RP * g.ZP * 4, 128);
-  const size_t tile = (size_t)16 * g.OP * 4;
+  // tcgen05 phase 3: the accumulators of all pixel blocks must fit the CTA's share of tensor memory
+  g.NMB = ceil_div(g.OPX, 128);
+  g.ncols = next_pow2_cols(g.NMB * g.CoutPad);
+  const int cap0 = RP <= 16 ? 2 : 1;
+  const bool tc3 = want_tc3 && RP == 16 && g.CoutPad <= 256 && g.ncols * cap0 <= 512;
+  const size_t planeP = align_up((size_t)RP * g.PP * 4, 1024);
+  const size_t planeZ = tc3 ? (size_t)2 * g.NMB * (RP / 8) * 4096 : align_up((size_t)RP * g.ZP * 4, 128);
+  const size_t tile = tc3 ? 0 : (size_t)16 * g.OP * 4;
   // blocks past the band read up to this far behind the last stage
   const size_t slack = (size_t)std::max(0, kCons * 8 * NBW1 - g.XP) * 4 + 128;
-  const size_t fixed = (size_t)2 * RP * g.FP1 * 4 + (size_t)2 * g.CoutPad * g.FP2 * 4 + (size_t)9 * RP * 4 + 128 + 128;
+  const size_t f1 = (size_t)2 * RP * g.FP1 * 4;
+  const size_t f2 = (size_t)2 * g.CoutPad * (tc3 ? RP : g.FP2) * 4;   // tcgen05: dense operand in place of the F1 planes
+  const size_t fixed = (tc3 ? align_up(std::max(f1, f2), 128) : f1 + f2) + (size_t)9 * RP * 4 + 128 + 256;
   const int nst = ceil_div(Cin_max, g.CB);
   const int cap = RP <= 16 ? 2 : 1;   // the kernel's launch bounds
   // ring depth: as deep as two resident CTAs allow, at least three stages.  After phase 1 the ring's space holds the
@@ -623,13 +780,13 @@ bool fill_plan(int RP, int N, int H, int W, int Cin_max, int Cout_max, int TH, i
   int S = std::min(kMaxStages, std::max(2, nst));
   size_t ring = 0, total = 0;
   for (;; --S) {
-    ring = align_up(std::max((size_t)S * g.stage_floats * 4 + slack, std::max(planeP, tile) + planeZ), 128);
+    ring = align_up(std::max((size_t)S * g.stage_floats * 4 + slack, std::max(planeP, tile) + planeZ), 1024);
     total = ring + fixed;
     if (S <= 3 || total + 1024 <= (size_t)(228 * 1024) / cap) break;
   }
   // a second output tile (one drains while the next fills) where it costs no residency
-  const size_t ring2 = std::max(ring, align_up(2 * tile + planeZ, 128));
-  if (ring2 + fixed + 1024 <= (size_t)(228 * 1024) / cap || (ring2 + fixed) / 1024 == total / 1024) {
+  const size_t ring2 = std::max(ring, align_up(2 * tile + planeZ, 1024));
+  if (!tc3 && (ring2 + fixed + 1024 <= (size_t)(228 * 1024) / cap || (ring2 + fixed) / 1024 == total / 1024)) {
     ring = ring2;
     total = ring + fixed;
   }
@@ -638,14 +795,21 @@ bool fill_plan(int RP, int N, int H, int W, int Cin_max, int Cout_max, int TH, i
   g.oZ = (int)(ring - planeZ);
   g.obuf = 2 * tile <= (size_t)g.oZ ? 2 : 1;
   size_t o = ring;
-  g.oF1 = (int)o; o += (size_t)2 * RP * g.FP1 * 4;
-  g.oF2 = (int)o; o += (size_t)2 * g.CoutPad * g.FP2 * 4;
+  g.oF1 = (int)o;
+  if (tc3) {
+    g.oF2 = g.oF1;
+    o += align_up(std::max(f1, f2), 128);
+  } else {
+    o += f1;
+    g.oF2 = (int)o; o += f2;
+  }
   g.oW = (int)o; o += (size_t)9 * RP * 4;
   o = align_up(o, 16);
-  g.oBar = (int)o; o += 128;
+  g.oBar = (int)o; o += 256;
   out->g = g;
   out->RP = RP;
   out->NBW1 = NBW1;
+  out->tc3 = tc3;
   out->smem = o;
   out->per_sm = std::max(1, std::min(cap, (int)((228 * 1024) / (out->smem + 1024))));
   return true;
@@ -653,20 +817,22 @@ bool fill_plan(int RP, int N, int H, int W, int Cin_max, int Cout_max, int TH, i
 
 // band height: least estimated time.  A band costs its two contractions (halo rows for the first) plus a fixed part;
 // the busiest SM runs ceil(tiles / SMs) of them, and two resident CTAs overlap each other's phases.
-bool plan_band(int RP, int N, int H, int W, int Cin, int Cout, int nconv, const DeviceInfo& di, BandPlan* best) {
+bool plan_band(int RP, int N, int H, int W, int Cin, int Cout, int nconv, bool accumulate, const DeviceInfo& di,
+               BandPlan* best) {
   const int tensor = g_band_tensor.load(std::memory_order_relaxed);
+  const bool want_tc3 = !accumulate && g_band_tc3.load(std::memory_order_relaxed) != 0;
   const int forced = g_band_th.load(std::memory_order_relaxed);
   if (forced) {
     // the first height from the forced one upwards that the kernel can take
     for (int TH = std::min(forced, H); TH <= std::min(H, 62); ++TH)
-      if (fill_plan(RP, N, H, W, Cin, Cout, TH, tensor, di, best)) return true;
+      if (fill_plan(RP, N, H, W, Cin, Cout, TH, tensor, want_tc3, di, best)) return true;
     return false;
   }
   double best_cost = 1e300;
   bool found = false;
   for (int TH = 1; TH <= std::min(H, 62); ++TH) {
     BandPlan pl;
-    if (!fill_plan(RP, N, H, W, Cin, Cout, TH, tensor, di, &pl)) continue;
+    if (!fill_plan(RP, N, H, W, Cin, Cout, TH, tensor, want_tc3, di, &pl)) continue;
     const long tiles = (long)nconv * pl.g.tiles;
     const long per_sm = (tiles + di.sm_count - 1) / di.sm_count;
     const double tile = (double)(TH + 2) * W * (Cin + 24.0) + (double)TH * W * (Cout + 40.0) + 6000.0;
@@ -676,10 +842,10 @@ bool plan_band(int RP, int N, int H, int W, int Cin, int Cout, int nconv, const 
   return found;
 }
 
-template <int RP, int NBW1>
+template <int RP, int NBW1, bool TC3>
 int launch_band(const BandPlan& pl, const CUtensorMap& m0, const CUtensorMap& m1, const BandProb& p0, const BandProb& p1,
                 int nconv, cudaStream_t st) {
-  auto kern = cp4_band_kernel<RP, NBW1>;
+  auto kern = cp4_band_kernel<RP, NBW1, TC3>;
   B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
   const long ctas = (long)nconv * pl.g.tiles;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4: too many tiles");
@@ -727,11 +893,13 @@ int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done
   int cin = 0, cout = 0;
   for (int i = 0; i < nconv; ++i) { cin = std::max(cin, convs[i].Cin); cout = std::max(cout, convs[i].Cout); }
   BandPlan pl;
-  if (!plan_band(RP, a.N, a.H, a.W, cin, cout, nconv, di, &pl)) return B200CP_OK;
+  bool accumulate = false;
+  for (int i = 0; i < nconv; ++i) accumulate = accumulate || convs[i].accumulate;
+  if (!plan_band(RP, a.N, a.H, a.W, cin, cout, nconv, accumulate, di, &pl)) return B200CP_OK;
   pl.g.R = a.R; pl.g.Rs = a.Rs; pl.g.r0 = a.r0;
   pl.g.trace = g_band_trace.load(std::memory_order_relaxed);
   pl.g.sm_count = di.sm_count;
-  { const char* e = getenv("B200CP_BAND_STAGGER"); pl.g.stagger = e ? atoi(e) : 0; }
+  pl.g.stagger = g_band_stagger;
   CUtensorMap m[2];
   BandProb p[2];
   std::memset(m, 0, sizeof(m));
@@ -742,11 +910,15 @@ int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done
     p[i] = make_prob(c);
   }
   if (getenv("B200CP_DEBUG"))
-    fprintf(stderr, "[b200cp] band TH=%d bands=%d CB=%d stages=%d tensor=%d obuf=%d NB3=%d RP=%d NBW1=%d smem=%zu per_sm=%d convs=%d\n",
-            pl.g.TH, pl.g.bands, pl.g.CB, pl.g.stages, pl.g.tensor, pl.g.obuf, pl.g.NB3, pl.RP, pl.NBW1, pl.smem, pl.per_sm, nconv);
+    fprintf(stderr, "[b200cp] band TH=%d bands=%d CB=%d stages=%d tensor=%d obuf=%d tc3=%d NMB=%d ncols=%d RP=%d NBW1=%d smem=%zu per_sm=%d convs=%d\n",
+            pl.g.TH, pl.g.bands, pl.g.CB, pl.g.stages, pl.g.tensor, pl.g.obuf, (int)pl.tc3, pl.g.NMB, pl.g.ncols, pl.RP, pl.NBW1, pl.smem, pl.per_sm, nconv);
   int rc = B200CP_ERR_UNSUPPORTED;
-#define BAND_CASE(RPV, NB) case NB: rc = launch_band<RPV, NB>(pl, m[0], m[1], p[0], p[1], nconv, st); break;
-  if (pl.RP == 16) {
+#define BAND_CASE(RPV, NB) case NB: rc = launch_band<RPV, NB, false>(pl, m[0], m[1], p[0], p[1], nconv, st); break;
+#define BAND_CASE_TC(NB) case NB: rc = launch_band<16, NB, true>(pl, m[0], m[1], p[0], p[1], nconv, st); break;
+  if (pl.tc3) {
+    switch (pl.NBW1) { BAND_CASE_TC(1) BAND_CASE_TC(2) BAND_CASE_TC(3) BAND_CASE_TC(4) BAND_CASE_TC(5) BAND_CASE_TC(6)
+                       BAND_CASE_TC(7) BAND_CASE_TC(8) }
+  } else if (pl.RP == 16) {
     switch (pl.NBW1) { BAND_CASE(16, 1) BAND_CASE(16, 2) BAND_CASE(16, 3) BAND_CASE(16, 4) BAND_CASE(16, 5) BAND_CASE(16, 6)
                        BAND_CASE(16, 7) BAND_CASE(16, 8) }
   } else {
@@ -754,6 +926,7 @@ int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done
                        BAND_CASE(32, 7) BAND_CASE(32, 8) }
   }
 #undef BAND_CASE
+#undef BAND_CASE_TC
   if (rc) return rc;
   *done = true;
   return B200CP_OK;
@@ -761,6 +934,7 @@ int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done
 
 void band_force_rows(int rows) { g_band_th.store(rows > 0 ? rows : 0); }
 void band_force_tensor(int on) { g_band_tensor.store(on ? 1 : 0); }
+void band_force_tc3(int on) { g_band_tc3.store(on ? 1 : 0); }
 void band_set_trace(long long* p) { g_band_trace.store(p); }
 
 int band_device_status(int* out) {
@@ -776,4 +950,5 @@ int band_device_status(int* out) {
 
 extern "C" void b200cp_test_set_band_rows(int rows) { b200cp::band_force_rows(rows); }
 extern "C" void b200cp_test_set_band_tensor_loads(int on) { b200cp::band_force_tensor(on); }
+extern "C" void b200cp_test_set_band_tcgen05(int on) { b200cp::band_force_tc3(on); }
 extern "C" void b200cp_test_set_band_trace(void* device_buffer) { b200cp::band_set_trace(static_cast<long long*>(device_buffer)); }

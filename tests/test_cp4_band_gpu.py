@@ -29,20 +29,25 @@ def _inputs(case):
     return O.make_cp4_inputs(seed, N, C, T, H, W, 3, 3, R, factor_std=std)
 
 
+@pytest.mark.parametrize("tcgen05", [True, False], ids=["tcgen05", "mmasync"])
 @pytest.mark.parametrize("tensor_loads", [False, True], ids=["bulk", "tensormap"])
 @pytest.mark.parametrize("case", BAND_SHAPES, ids=lambda c: "s%d" % c[0])
-def test_band_forward_and_backward_data(case, tensor_loads):
-    """Both ways of loading the band: one 1-D bulk copy per channel (default; the padding rows are zeroed by the
-    CTA), or one 4-D tensor-map box per stage (the padding rows are the map's out-of-range fill)."""
+def test_band_forward_and_backward_data(case, tensor_loads, tcgen05):
+    """Both ways of loading the band -- one 1-D bulk copy per channel (default; the padding rows are zeroed by the
+    CTA), or one 4-D tensor-map box per stage (the padding rows are the map's out-of-range fill) -- and both forms of
+    the output contraction: mma.sync with the output staged in shared memory (default), or tcgen05.mma with the
+    accumulators in tensor memory."""
     import paralleltnnlayers_b200 as P
     X, K0, K1, KH, KW, dU = _inputs(case)
     t = dev(X, K0, K1, KH, KW, dU)
     P.set_band_tensor_loads(tensor_loads)
+    P.set_band_tcgen05(tcgen05)
     try:
         U = P.cp4_conv2d_forward(*t[:5], 1)
         dX = P.cp4_conv2d_backward_data(t[5], *t[1:5], 1)
     finally:
         P.set_band_tensor_loads(False)
+        P.set_band_tcgen05(False)
     check(U, O.cp4_forward(X, K0, K1, KH, KW, 1), "forward (band)")
     check(dX, O.cp4_backward_data(dU, K0, K1, KH, KW, 1), "backward-data (band)")
     P.device_status()
