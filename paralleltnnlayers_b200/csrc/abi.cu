@@ -333,7 +333,7 @@ size_t b200cp_cp4_step_workspace_bytes(const b200cp_tensor_shape* s, int flags) 
   const size_t plain = b200cp_cp4_bwd_filter_workspace_bytes(s, flags);
   if (!step_shares_planes(s, flags)) return plain;
   const size_t plane = align_up((size_t)s->N * s->Rank * s->H * s->W * sizeof(float), 256);
-  return 2 * plane + std::max(plain, cp4_bwd_filter_saved_workspace(*s));
+  return 2 * plane + std::max(std::max(plain, cp4_bwd_filter_saved_workspace(*s)), cp4_grad_band_workspace(*s));
 }
 
 int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0, const float* K1,
@@ -384,6 +384,14 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
   a.Rs = s->Rank;
   a.X = X; a.dU = dU; a.K0 = K0; a.K1 = K1; a.KH = KH; a.KW = KW; a.dK = dK_packed;
   a.ws = part; a.ws_bytes = workspace_bytes - 2 * plane;
+  if (both && s->Rank <= 16) {
+    // one more launch: both halves of the factor gradients over the same row bands, then the sum of the bands
+    a.r0 = 0;
+    a.R = (int)s->Rank;
+    bool done = false;
+    if (int rc = cp4_grad_band_launch(a, P, Q, st, &done)) return rc;
+    if (done) return B200CP_OK;
+  }
   if (fork && s->Rank <= 64) {
     // the gradient kernel in two halves, also side by side: the dK0 half follows the forward on the caller's
     // stream, the dK1 / spatial half follows backward-data on the side stream once the forward's plane is there
@@ -432,7 +440,7 @@ int b200cp_cp4_bwd_data_save(const b200cp_tensor_shape* s, const float* dU, cons
 size_t b200cp_cp4_bwd_filter_saved_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
   (void)flags;
   if (check_shape(s, "b200cp_cp4_bwd_filter_saved_workspace_bytes")) return 0;
-  return cp4_bwd_filter_saved_workspace(*s);
+  return std::max(cp4_bwd_filter_saved_workspace(*s), cp4_grad_band_workspace(*s));
 }
 
 int b200cp_cp4_bwd_filter_saved(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* P,
@@ -448,6 +456,13 @@ int b200cp_cp4_bwd_filter_saved(const b200cp_tensor_shape* s, const float* X, co
   a.Rs = s->Rank;
   a.X = X; a.dU = dU; a.KH = KH; a.KW = KW; a.dK = dK_packed;
   a.ws = workspace; a.ws_bytes = workspace_bytes;
+  if (s->Rank <= 16) {
+    a.r0 = 0;
+    a.R = (int)s->Rank;
+    bool done = false;
+    if (int rc = cp4_grad_band_launch(a, P, Q, static_cast<cudaStream_t>(stream), &done)) return rc;
+    if (done) return B200CP_OK;
+  }
   for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);
@@ -687,6 +702,8 @@ int b200cp_device_status(void) {
   if (v) return fail(B200CP_ERR_TIMEOUT, "gradient GEMM: a bounded wait ran out in block %d", v & 0xffff);
   if (int rc = band_device_status(&v)) return rc;
   if (v) return fail(B200CP_ERR_TIMEOUT, "cp4 band kernel: a bounded wait ran out in block %d", v & 0xffff);
+  if (int rc = grad_band_device_status(&v)) return rc;
+  if (v) return fail(B200CP_ERR_TIMEOUT, "cp4 gradient band kernel: a bounded wait ran out in block %d", v & 0xffff);
   return B200CP_OK;
 }
 

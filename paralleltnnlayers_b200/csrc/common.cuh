@@ -94,6 +94,12 @@ int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const
 // dK[row*Rs + r0 + r] = sum over parts of partial[part][row*R + r], in a fixed order
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
                                cudaStream_t st);
+// the same gradients over full-width row bands (bulk / tensor-map loads, 3x3, W % 4 == 0, at most 16 ranks);
+// *done = false: not a shape this kernel takes
+bool cp4_grad_band_supported(const Cp4BwdFilterArgs& a);
+size_t cp4_grad_band_workspace(const b200cp_tensor_shape& s);
+int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, bool* done);
+int grad_band_device_status(int* out);
 size_t cp4_bwd_filter_static_scratch_bytes();
 int cp4_bwd_filter_static_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);
 int cp4_bwd_filter_full_launch(const b200cp_tensor_shape& s, const float* X, const float* dU, float* dK,
