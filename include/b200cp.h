@@ -98,6 +98,12 @@ int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const fl
 int b200cp_cp4_bwd_filter_noalloc(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
                                   const float* K1, const float* KH, const float* KW, float* dK_packed, void* stream);
 
+/* *exceeds = number of elements with max(|a-b|/|a|, |a-b|/|b|) > tolerance (|a-b| where a or b is zero), counted on
+ * the device; A and B are device (or managed) arrays of n floats.  Synchronises `stream`.  Replaces the count kernel
+ * behind AllClose (Cuda_kernels/Utils.cu:143-180): AllClose(A, B, tol) == (*exceeds == 0). */
+int b200cp_allclose_count(const float* A, const float* B, size_t n, float tolerance, unsigned long long* exceeds,
+                          void* stream);
+
 /* Dense filter gradient dK[t,c,y,x] = sum_{n,h,w} dU[n,t,h,w] Xpad[n,c,h+y,w+x].
  * Replaces cp4_conv2d_backward_filter_full_gpu (Cuda_kernels/cp4Conv2dBackwardFilter.cuh:7-11). */
 int b200cp_cp4_bwd_filter_full(const b200cp_tensor_shape* s, const float* X, const float* dU, float* dK, void* stream);
@@ -106,6 +112,12 @@ int b200cp_cp4_bwd_filter_full(const b200cp_tensor_shape* s, const float* X, con
  * Cuda_kernels/Utils.cu:36-98). */
 int b200cp_cp4_recompose(const b200cp_tensor_shape* s, const float* K0, const float* K1, const float* KH,
                          const float* KW, float* K, void* stream);
+
+/* 1 when b200cp_cp4_step / _fwd_save / _bwd_data_save / _bwd_filter_saved share the rank planes for this shape and
+ * flags (3x3 filter, pad 1, default or mma path, not switched off by B200CP_STEP_NO_SHARE / B200CP_AUTO_MMA=0), else
+ * 0: the one rule callers such as an autograd function should ask instead of restating it.  No counterpart in the
+ * reference, which has no backward-filter kernel (Cuda_kernels/cp4Conv2dBackwardFilter.cu:64-257 are host loops). */
+int b200cp_cp4_shares_planes(const b200cp_tensor_shape* s, int flags);
 
 /* One training step on device buffers: U = forward(X), dX = backward-data(dU) and the packed factor gradients,
  * the three results of b200cp_cp4_fwd, _bwd_data and _bwd_filter on the same inputs.  Inside one call the work

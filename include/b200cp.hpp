@@ -209,16 +209,12 @@ inline Tensor cp4recom(Tensor const& FK, Tensor const& FC, Tensor const& FH, Ten
   b200cp_detail::cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
   return Out;
 }
-// max(|a-b|/|a|, |a-b|/|b|) <= tolerance for every element (Cuda_kernels/Utils.cu:143-180)
+// max(|a-b|/|a|, |a-b|/|b|) <= tolerance for every element, counted on the device (Cuda_kernels/Utils.cu:143-180)
 inline bool AllClose(Tensor const& A, Tensor const& B, float tolerance = 1e-3f) {
   if (A.size() != B.size()) return false;
-  b200cp_detail::cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
-  for (size_t i = 0; i < A.size(); ++i) {
-    const float a = A.m_data[i], b = B.m_data[i], d = std::fabs(a - b);
-    if (d == 0.f) continue;
-    if (std::fmax(d / std::fabs(a), d / std::fabs(b)) > tolerance) return false;
-  }
-  return true;
+  unsigned long long exceeds = 0;
+  b200cp_detail::check(b200cp_allclose_count(A.m_data, B.m_data, A.size(), tolerance, &exceeds, nullptr), "AllClose");
+  return exceeds == 0;
 }
 
 namespace CP {

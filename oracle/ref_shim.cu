@@ -54,6 +54,21 @@ __attribute__((visibility("default"))) int ref_cp4_forward(const unsigned* s, co
   cudaFree(dIn); cudaFree(dFT); cudaFree(dFC); cudaFree(dFY); cudaFree(dFX); cudaFree(dOut);
   return e == cudaSuccess ? 0 : 2;
 }
+// the reference's own timing: mean microseconds over `profcount` launches (its PROFCOUNT loop); negative on error
+__attribute__((visibility("default"))) float ref_cp4_forward_time(const unsigned* s, const float* In, const float* FT,
+                                                                  const float* FC, const float* FY, const float* FX,
+                                                                  unsigned profcount) {
+  const tensor_shape p = to_shape(s);
+  const size_t nin = (size_t)p.N * p.C * p.H * p.W, nout = (size_t)p.N * p.T * p.H * p.W;
+  float *dIn = to_dev(In, nin), *dFT = to_dev(FT, p.T * p.Rank), *dFC = to_dev(FC, p.C * p.Rank),
+        *dFY = to_dev(FY, p.Y * p.Rank), *dFX = to_dev(FX, p.X * p.Rank), *dOut = nullptr;
+  if (cudaMalloc(&dOut, nout * sizeof(float)) != cudaSuccess) return -1.f;
+  cp4_conv2d_forward_gpu(p, dIn, dFT, dFC, dFY, dFX, dOut, 3);   // warm-up
+  const float us = cp4_conv2d_forward_gpu(p, dIn, dFT, dFC, dFY, dFX, dOut, profcount);
+  const cudaError_t e = cudaDeviceSynchronize();
+  cudaFree(dIn); cudaFree(dFT); cudaFree(dFC); cudaFree(dFY); cudaFree(dFX); cudaFree(dOut);
+  return e == cudaSuccess ? us : -1.f;
+}
 #endif
 
 #ifdef REF_BWD

@@ -24,8 +24,58 @@ def available():
 
 def _lib(n):
     if n not in _libs:
-        _libs[n] = C.CDLL(os.path.join(_HERE, "_ref", f"libcp4ref_{n}.so"))
+        name = f"libtvmref_{n[4:]}.so" if n.startswith("tvm_") else f"libcp4ref_{n}.so"
+        _libs[n] = C.CDLL(os.path.join(_HERE, "_ref", name))
     return _libs[n]
+
+
+def tvm_available():
+    return all(os.path.exists(os.path.join(_HERE, "_ref", f"libtvmref_{n}.so")) for n in ("rcp", "dense", "cp3", "cp4"))
+
+
+# the one shape each TensorFlow-op kernel of the reference is compiled for (Kernels/*.cc):
+# inputs in launcher order, then the output
+TVM_SHAPES = {
+    "rcp": ([(1, 4, 4, 32, 32), (4, 4, 11), (4, 4, 11), (3, 3, 11)], (1, 4, 4, 32, 32)),
+    "dense": ([(1, 16, 16, 16), (16, 4, 137), (16, 4, 137), (16, 4, 137)], (1, 4, 4, 4)),
+    "cp3": ([(1, 16, 32, 32), (16, 6), (3, 3, 6), (6, 16)], (1, 16, 32, 32)),
+    "cp4": ([(1, 16, 32, 32), (16, 6), (3, 6), (3, 6), (16, 6)], (1, 16, 32, 32)),
+}
+
+
+def tvm_inputs(op, seed):
+    """Seeded inputs of the op's compiled shape, uniform in [0, 1) like the reference's tests
+    (test/test_conv2d_rcp.py:22-25, test_dense_cp.py:22-25, test_conv2d_cp.py:12-15, test_conv2d_cp4.py:13-17)."""
+    rng = np.random.default_rng(seed)
+    return [rng.uniform(0, 1, size=s).astype(np.float32) for s in TVM_SHAPES[op][0]]
+
+
+def tvm_run(op, arrays):
+    """Run ``Conv2dRcpFusedNchwKernelLauncher`` (Kernels/rcp_fused_nchw.cu:80), ``DenseCpKernelLauncher``
+    (dense_cp.cu:48), ``Conv2dCpFusedNchwKernelLauncher`` (cp_fused_nchw.cu:454) or
+    ``Cp4Conv2dFusedNchwKernelLauncher`` (cp4_conv_nchw.cu:88) on host arrays of the compiled shape."""
+    shapes, oshape = TVM_SHAPES[op]
+    arrs = [_f(a) for a in arrays]
+    assert [a.shape for a in arrs] == [tuple(s) for s in shapes], "this kernel takes one literal shape"
+    lib = _lib("tvm_" + op)
+    out = np.zeros(oshape, np.float32)
+    ptrs = (C.c_void_p * len(arrs))(*[a.ctypes.data for a in arrs])
+    rc = lib.ref_tvm_run(ptrs, _p(out))
+    assert rc == 0, rc
+    return out
+
+
+def forward_time(X, K0, K1, KH, KW, pad, profcount=47):
+    """Mean microseconds of the reference's own forward kernel over ``profcount`` launches, as its launcher measures
+    them (cp4_conv2d_forward_gpu's PROFCOUNT loop, Cuda_kernels/cp4Conv2dForward.cu:245-327)."""
+    X, K0, K1, KH, KW = map(_f, (X, K0, K1, KH, KW))
+    N, C_, H, W = X.shape
+    T, R = K0.shape
+    assert R in (1, 2, 4, 8, 16) and (T + C_ + KH.shape[0] + KW.shape[0]) * R <= 16384
+    fn = _lib("fwd").ref_cp4_forward_time
+    fn.restype = C.c_float
+    return float(fn(_shape(N, C_, T, H, W, KH.shape[0], KW.shape[0], R, pad), _p(X), _p(K0), _p(K1), _p(KH), _p(KW),
+                    C.c_uint(profcount)))
 
 
 def _f(a):

@@ -11,7 +11,7 @@ import importlib
 
 _LIB_NAMES = ("B200CPError", "LIB_PATH", "PATH_AUTO", "PATH_MMA", "PATH_SIMT", "PATH_TC1X", "PATH_TC3X", "TensorShape",
               "launch_count")
-_OPS_NAMES = ("CP3Conv2dFunction", "conv2d_cp_fused_nchw", "cp3_conv2d_backward_data", "cp3_conv2d_backward_filter",
+_OPS_NAMES = ("allclose", "CP3Conv2dFunction", "conv2d_cp_fused_nchw", "cp3_conv2d_backward_data", "cp3_conv2d_backward_filter",
               "cp3_conv2d_forward", "CP4Conv2dFunction", "CPDenseFunction", "RCPConv2dFunction", "conv2d_rcp_fused_nchw",
               "cp4_conv2d_backward_data", "cp4_conv2d_backward_filter", "cp4_conv2d_backward_filter_full",
               "cp4_conv2d_forward", "cp4_conv2d_nchw", "cp4_conv2d_step", "cp4_conv2d_step_host", "cp4_conv2d_step_host_submit",

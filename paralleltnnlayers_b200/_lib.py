@@ -45,6 +45,8 @@ def _load():
         "b200cp_cp4_bwd_filter_noalloc": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp]),
         "b200cp_cp4_bwd_filter_full": (i, [sp, fp, fp, fp, vp]),
         "b200cp_cp4_recompose": (i, [sp, fp, fp, fp, fp, fp, vp]),
+        "b200cp_allclose_count": (i, [fp, fp, sz, C.c_float, C.POINTER(C.c_ulonglong), vp]),
+        "b200cp_cp4_shares_planes": (i, [sp, i]),
         "b200cp_cp4_step_workspace_bytes": (sz, [sp, i]),
         "b200cp_cp4_step": (i, [sp, fp, fp, fp, fp, fp, fp, fp, fp, fp, vp, sz, vp, i]),
         "b200cp_cp4_fwd_save": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp, i]),

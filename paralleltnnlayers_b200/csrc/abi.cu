@@ -299,13 +299,41 @@ int b200cp_cp4_recompose(const b200cp_tensor_shape* s, const float* K0, const fl
   return cp4_recompose_launch(*s, K0, K1, KH, KW, K, static_cast<cudaStream_t>(stream));
 }
 
+// The reference's AllClose (Cuda_kernels/Utils.cu:159-180): the count of elements out of tolerance, computed on the
+// device; the one word comes back through a pinned-free synchronous copy (this is a test helper, not a hot call).
+int b200cp_allclose_count(const float* A, const float* B, size_t n, float tolerance, unsigned long long* exceeds,
+                          void* stream) {
+  if (!exceeds) return fail(B200CP_ERR_INVALID_ARG, "b200cp_allclose_count: exceeds is null");
+  if (n)
+    if (int rc = check_ptrs("b200cp_allclose_count", {A, B})) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned long long* d = nullptr;
+  B200CP_CUDA_OK(cudaMalloc(&d, sizeof(unsigned long long)));
+  int rc = allclose_count_launch(A, B, n, tolerance, d, st);
+  cudaError_t e = cudaSuccess;
+  if (!rc) e = cudaMemcpyAsync(exceeds, d, sizeof(unsigned long long), cudaMemcpyDeviceToHost, st);
+  if (!rc && e == cudaSuccess) e = cudaStreamSynchronize(st);
+  cudaFree(d);
+  if (rc) return rc;
+  if (e != cudaSuccess) return fail(B200CP_ERR_CUDA, "b200cp_allclose_count: %s", cudaGetErrorString(e));
+  return B200CP_OK;
+}
+
 // One training step on device buffers: forward, backward-data and backward-filter.  With 3x3 filters (pad 1) on the
 // default path the two convolutions also write their rank planes P = K1^T X and Q = K0^T dU into the workspace and
 // the factor gradients are computed from those, without contracting the channels a second time.
+// (the two switches are read once, when the library is loaded)
+static const bool g_step_no_share = getenv("B200CP_STEP_NO_SHARE") != nullptr;
+static const bool g_step_no_fork = getenv("B200CP_STEP_NO_FORK") != nullptr;
 static bool step_shares_planes(const b200cp_tensor_shape* s, int flags) {
   const int path = path_of(flags);
   return s->Y == 3 && s->X == 3 && s->pad == 1 && (path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma)) &&
-         !getenv("B200CP_STEP_NO_SHARE");
+         !g_step_no_share;
+}
+
+int b200cp_cp4_shares_planes(const b200cp_tensor_shape* s, int flags) {
+  if (check_shape(s, "b200cp_cp4_shares_planes")) return 0;
+  return step_shares_planes(s, flags) ? 1 : 0;
 }
 
 // a second stream and two events per device: forward and backward-data of a step are independent and run side by
@@ -359,14 +387,31 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
   int dev = 0;
   B200CP_CUDA_OK(cudaGetDevice(&dev));
   StepFork* fk = nullptr;
-  const bool fork = dev >= 0 && dev < 64 && !getenv("B200CP_STEP_NO_FORK");
+  const bool fork = dev >= 0 && dev < 64 && !g_step_no_fork;
   // the fork / join pairs of two host threads must not interleave on the shared side stream
   std::unique_lock<std::mutex> lk(g_step_mu, std::defer_lock);
+  // Whatever way this call ends, the side stream is joined back into the caller's stream: an error return must not
+  // leave a stream capture of the caller with an unjoined branch.
+  struct Rejoin {
+    StepFork* fk = nullptr;
+    cudaStream_t st = nullptr;
+    bool joined = false;
+    void join() {
+      if (fk && !joined) {
+        joined = true;
+        cudaEventRecord(fk->join, fk->side);
+        cudaStreamWaitEvent(st, fk->join, 0);
+      }
+    }
+    ~Rejoin() { join(); }
+  } rejoin;
   if (fork) {
     lk.lock();
     if (int rc = step_fork(dev, &fk)) return rc;
     B200CP_CUDA_OK(cudaEventRecord(fk->fork, st));
     B200CP_CUDA_OK(cudaStreamWaitEvent(fk->side, fk->fork, 0));
+    rejoin.fk = fk;
+    rejoin.st = st;
   }
   // forward and backward-data: one launch of the band kernel carries both where the shape allows it; otherwise
   // two launches side by side
@@ -389,6 +434,7 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
     a.r0 = 0;
     a.R = (int)s->Rank;
     bool done = false;
+    rejoin.join();   // nothing ran on the side stream
     if (int rc = cp4_grad_band_launch(a, P, Q, st, &done)) return rc;
     if (done) return B200CP_OK;
   }
@@ -401,14 +447,10 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
     if (int rc = cp4_bwd_filter_saved_launch(a, P, Q, st, 1)) return rc;
     B200CP_CUDA_OK(cudaStreamWaitEvent(fk->side, fk->fwd_done, 0));
     if (int rc = cp4_bwd_filter_saved_launch(a, P, Q, fk->side, 2)) return rc;
-    B200CP_CUDA_OK(cudaEventRecord(fk->join, fk->side));
-    B200CP_CUDA_OK(cudaStreamWaitEvent(st, fk->join, 0));
+    rejoin.join();
     return cp4_bwd_filter_saved_launch(a, P, Q, st, 3);
   }
-  if (fork) {
-    B200CP_CUDA_OK(cudaEventRecord(fk->join, fk->side));
-    B200CP_CUDA_OK(cudaStreamWaitEvent(st, fk->join, 0));
-  }
+  rejoin.join();
   for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);
@@ -507,7 +549,7 @@ int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, co
   float *dXin, *dUout, *dF, *ddU = nullptr, *ddX = nullptr, *ddK = nullptr, *ws = nullptr;
   const size_t b0 = (size_t)slot * 8;
   size_t wsb = 0;
-  if (bwd) wsb = b200cp_cp4_bwd_filter_workspace_bytes(s, 0);
+  if (bwd) wsb = b200cp_cp4_step_workspace_bytes(s, flags);
   // a (re)allocation frees a buffer the other slot's queued work may still use: drain first
   {
     const size_t want[7] = {nX * 4, nU * 4, nK * 4, bwd ? nU * 4 : 0, bwd ? nX * 4 : 0, bwd ? nK * 4 : 0, 0};
@@ -540,24 +582,20 @@ int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, co
     B200CP_CUDA_OK(cudaEventRecord(ev[1], c.s_in));
   }
   B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_cmp, ev[0], 0));
-  if (U) {
+  if (!bwd) {
     if (int rc = b200cp_cp4_fwd(s, dXin, dK0, dK1, dKH, dKW, dUout, c.s_cmp, flags)) return rc;
     B200CP_CUDA_OK(cudaEventRecord(ev[2], c.s_cmp));
     B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_out, ev[2], 0));
     B200CP_CUDA_OK(cudaMemcpyAsync(U, dUout, nU * 4, cudaMemcpyDeviceToHost, c.s_out));
-  }
-  if (bwd) {
+  } else {
+    // the whole step in one call: the convolutions share their rank planes with the factor gradients
     B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_cmp, ev[1], 0));
-    if (int rc = b200cp_cp4_bwd_data(s, ddU, dK0, dK1, dKH, dKW, ddX, c.s_cmp, flags)) return rc;
-    B200CP_CUDA_OK(cudaEventRecord(ev[3], c.s_cmp));
-    B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_out, ev[3], 0));
-    B200CP_CUDA_OK(cudaMemcpyAsync(dX, ddX, nX * 4, cudaMemcpyDeviceToHost, c.s_out));
     // the factor gradients have no tcgen05 kernel: a forced tcgen05 path applies to the two convolutions only
-    const int pf = path_of(flags);
-    const int fflags = (pf == B200CP_PATH_TC3X || pf == B200CP_PATH_TC1X) ? (flags & ~B200CP_PATH_MASK) : flags;
-    if (int rc = b200cp_cp4_bwd_filter(s, dXin, ddU, dK0, dK1, dKH, dKW, ddK, ws, wsb, c.s_cmp, fflags)) return rc;
+    if (int rc = b200cp_cp4_step(s, dXin, ddU, dK0, dK1, dKH, dKW, dUout, ddX, ddK, ws, wsb, c.s_cmp, flags)) return rc;
     B200CP_CUDA_OK(cudaEventRecord(ev[4], c.s_cmp));
     B200CP_CUDA_OK(cudaStreamWaitEvent(c.s_out, ev[4], 0));
+    if (U) B200CP_CUDA_OK(cudaMemcpyAsync(U, dUout, nU * 4, cudaMemcpyDeviceToHost, c.s_out));
+    B200CP_CUDA_OK(cudaMemcpyAsync(dX, ddX, nX * 4, cudaMemcpyDeviceToHost, c.s_out));
     B200CP_CUDA_OK(cudaMemcpyAsync(dK_packed, ddK, nK * 4, cudaMemcpyDeviceToHost, c.s_out));
   }
   B200CP_CUDA_OK(cudaEventRecord(ev[5], c.s_out));

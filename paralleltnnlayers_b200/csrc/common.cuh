@@ -43,6 +43,19 @@ struct DeviceInfo {
 };
 int device_info(DeviceInfo* out);  // status
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel, device and size instead of once per launch:
+// `slot` is a function-local static array of 64 zero-initialised atomics, one per device ordinal.
+inline cudaError_t ensure_dynamic_smem(const void* kernel, std::atomic<int>* slot, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (slot[dev].load(std::memory_order_relaxed) >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) slot[dev].store(bytes, std::memory_order_relaxed);
+  return e;
+}
+
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -70,6 +83,7 @@ int cp4_mma_launch(const Cp4Args& a, cudaStream_t st);
 // convolutions of the same image size in one launch.  *done = false: not a shape this kernel takes.
 int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done);
 int band_device_status(int* out);
+long long* band_trace_buffer();   // diagnostics buffer set by b200cp_test_set_band_trace (null: off)
 
 struct Cp4BwdFilterArgs {
   int N, C, T, H, W, F, pad;
@@ -107,6 +121,10 @@ int cp4_bwd_filter_full_launch(const b200cp_tensor_shape& s, const float* X, con
 int cp4_recompose_launch(const b200cp_tensor_shape& s, const float* K0, const float* K1, const float* KH,
                          const float* KW, float* K, cudaStream_t st);
 
+
+// *count_dev = number of elements whose relative difference exceeds tol (Cuda_kernels/Utils.cu:143-156)
+int allclose_count_launch(const float* A, const float* B, size_t n, float tol, unsigned long long* count_dev,
+                          cudaStream_t st);
 
 struct TcPlan {
   int TH = 0, RP = 0;

@@ -817,11 +817,39 @@ bool fill_plan(int RP, int N, int H, int W, int Cin_max, int Cout_max, int TH, i
 
 // band height: least estimated time.  A band costs its two contractions (halo rows for the first) plus a fixed part;
 // the busiest SM runs ceil(tiles / SMs) of them, and two resident CTAs overlap each other's phases.
+bool plan_band_search(int RP, int N, int H, int W, int Cin, int Cout, int nconv, int tensor, bool want_tc3, int forced,
+                      const DeviceInfo& di, BandPlan* best);
+
+// The search runs once per shape: a training loop asks for the same few plans again and again.
 bool plan_band(int RP, int N, int H, int W, int Cin, int Cout, int nconv, bool accumulate, const DeviceInfo& di,
                BandPlan* best) {
   const int tensor = g_band_tensor.load(std::memory_order_relaxed);
   const bool want_tc3 = !accumulate && g_band_tc3.load(std::memory_order_relaxed) != 0;
   const int forced = g_band_th.load(std::memory_order_relaxed);
+  struct Entry {
+    int key[12];
+    bool ok;
+    BandPlan plan;
+  };
+  thread_local Entry cache[8];
+  thread_local int used = 0, next = 0;
+  const int key[12] = {RP, N, H, W, Cin, Cout, nconv, tensor, want_tc3 ? 1 : 0, forced, di.sm_count, di.smem_optin};
+  for (int i = 0; i < used; ++i)
+    if (std::memcmp(cache[i].key, key, sizeof(key)) == 0) {
+      if (cache[i].ok) *best = cache[i].plan;
+      return cache[i].ok;
+    }
+  Entry& e = cache[next];
+  next = (next + 1) % 8;
+  used = std::min(used + 1, 8);
+  std::memcpy(e.key, key, sizeof(key));
+  e.ok = plan_band_search(RP, N, H, W, Cin, Cout, nconv, tensor, want_tc3, forced, di, &e.plan);
+  if (e.ok) *best = e.plan;
+  return e.ok;
+}
+
+bool plan_band_search(int RP, int N, int H, int W, int Cin, int Cout, int nconv, int tensor, bool want_tc3, int forced,
+                      const DeviceInfo& di, BandPlan* best) {
   if (forced) {
     // the first height from the forced one upwards that the kernel can take
     for (int TH = std::min(forced, H); TH <= std::min(H, 62); ++TH)
@@ -846,7 +874,8 @@ template <int RP, int NBW1, bool TC3>
 int launch_band(const BandPlan& pl, const CUtensorMap& m0, const CUtensorMap& m1, const BandProb& p0, const BandProb& p1,
                 int nconv, cudaStream_t st) {
   auto kern = cp4_band_kernel<RP, NBW1, TC3>;
-  B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+  static std::atomic<int> smem_set[64];
+  B200CP_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_set, (int)pl.smem));
   const long ctas = (long)nconv * pl.g.tiles;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4: too many tiles");
   kern<<<(unsigned)ctas, kNT, pl.smem, st>>>(pl.g, m0, m1, p0, p1);
@@ -909,7 +938,8 @@ int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done
       if (int rc = band_map(c.in, c.N, c.Cin, c.H, c.W, pl.g.TH + 2, pl.g.CB, &m[i])) return rc;
     p[i] = make_prob(c);
   }
-  if (getenv("B200CP_DEBUG"))
+  static const bool debug = getenv("B200CP_DEBUG") != nullptr;
+  if (debug)
     fprintf(stderr, "[b200cp] band TH=%d bands=%d CB=%d stages=%d tensor=%d obuf=%d tc3=%d NMB=%d ncols=%d RP=%d NBW1=%d smem=%zu per_sm=%d convs=%d\n",
             pl.g.TH, pl.g.bands, pl.g.CB, pl.g.stages, pl.g.tensor, pl.g.obuf, (int)pl.tc3, pl.g.NMB, pl.g.ncols, pl.RP, pl.NBW1, pl.smem, pl.per_sm, nconv);
   int rc = B200CP_ERR_UNSUPPORTED;
@@ -936,6 +966,7 @@ void band_force_rows(int rows) { g_band_th.store(rows > 0 ? rows : 0); }
 void band_force_tensor(int on) { g_band_tensor.store(on ? 1 : 0); }
 void band_force_tc3(int on) { g_band_tc3.store(on ? 1 : 0); }
 void band_set_trace(long long* p) { g_band_trace.store(p); }
+long long* band_trace_buffer() { return g_band_trace.load(std::memory_order_relaxed); }
 
 int band_device_status(int* out) {
   int v = 0, zero = 0;

@@ -573,4 +573,38 @@ int cp4_recompose_launch(const b200cp_tensor_shape& s, const float* K0, const fl
   return B200CP_OK;
 }
 
+// ---- AllClose (Cuda_kernels/Utils.cu:143-180) --------------------------------------------------------------
+// Number of elements whose relative difference max(|a-b|/|a|, |a-b|/|b|) (the absolute difference where a or b is
+// zero) exceeds `tol`: a grid-stride loop, a warp and block sum, one atomic per block.
+namespace {
+__global__ void __launch_bounds__(256) relative_delta_count_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                                   size_t n, float tol, unsigned long long* count) {
+  unsigned mine = 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float a = A[i], b = B[i], d = fabsf(a - b);
+    const float err = (a == 0.f || b == 0.f) ? d : fmaxf(d / fabsf(a), d / fabsf(b));
+    mine += !(err <= tol);   // a NaN difference counts as exceeding
+  }
+  __shared__ unsigned warp_sum[8];
+  for (int o = 16; o; o >>= 1) mine += __shfl_down_sync(0xffffffffu, mine, o);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned s = 0;
+    for (int w = 0; w < 8; ++w) s += warp_sum[w];
+    if (s) atomicAdd(count, (unsigned long long)s);
+  }
+}
+}  // namespace
+
+int allclose_count_launch(const float* A, const float* B, size_t n, float tol, unsigned long long* count_dev,
+                          cudaStream_t st) {
+  B200CP_CUDA_OK(cudaMemsetAsync(count_dev, 0, sizeof(unsigned long long), st));
+  if (n == 0) return B200CP_OK;
+  const unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 148 * 8);
+  relative_delta_count_kernel<<<blocks, 256, 0, st>>>(A, B, n, tol, count_dev);
+  B200CP_LAUNCH_OK("relative_delta_count_kernel");
+  return B200CP_OK;
+}
+
 }  // namespace b200cp

@@ -17,6 +17,7 @@
 // (formulas: Cuda_kernels/cp4Conv2dForward.cu:84-133, cp4Conv2dBackwardData.cu:57-108).
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include <cooperative_groups.h>
@@ -478,7 +479,8 @@ template <int RP, int FS, int M1, int M3>
 int launch_mma(const MmaGeom& g, const Cp4Args& a, cudaStream_t st) {
   auto kern = cp4_conv_mma_kernel<RP, FS, M1, M3>;
   const size_t smem = sizeof(float) * mma_smem_floats<RP>(g);
-  B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  static std::atomic<int> smem_set[64];
+  B200CP_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_set, (int)smem));
   const long ctas = (long)a.N * g.tilesH * g.tilesW * g.S;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4: too many tiles");
   float* save = (FS == 3 && a.pad == 1) ? a.save : nullptr;
@@ -519,14 +521,42 @@ int dispatch_blocks(const MmaGeom& g, const Cp4Args& a, cudaStream_t st) {
 }
 
 template <int RP>
+bool plan_tile_search(const Cp4Args& a, const DeviceInfo& di, int fTH, int fTW, int fS, MmaGeom* out);
+
+// The tile search runs once per shape and forced setting: the plan of the last few shapes is kept per host thread.
+template <int RP>
 bool plan_tile(const Cp4Args& a, const DeviceInfo& di, MmaGeom* out) {
-  MmaGeom best{};
-  double best_cost = 1e300;
   int fTH = 0, fTW = 0, fS = 0;
   if (const char* e = getenv("B200CP_MMA_TILE")) {  // "TH,TW": experiments
     if (sscanf(e, "%d,%d", &fTH, &fTW) != 2) fTH = fTW = 0;
   }
   if (const char* e = getenv("B200CP_MMA_SLICES")) fS = atoi(e);  // 1, 2, 4 or 8 channel slices per tile: tests
+  struct Entry {
+    int key[14];
+    bool ok;
+    MmaGeom g;
+  };
+  thread_local Entry cache[8];
+  thread_local int used = 0, next = 0;
+  const int key[14] = {a.N, a.Cin, a.Cout, a.H, a.W, a.Y, a.X, a.pad, a.R, fTH, fTW, fS, di.sm_count, di.smem_optin};
+  for (int i = 0; i < used; ++i)
+    if (std::memcmp(cache[i].key, key, sizeof(key)) == 0) {
+      if (cache[i].ok) *out = cache[i].g;
+      return cache[i].ok;
+    }
+  Entry& e = cache[next];
+  next = (next + 1) % 8;
+  used = std::min(used + 1, 8);
+  std::memcpy(e.key, key, sizeof(key));
+  e.ok = plan_tile_search<RP>(a, di, fTH, fTW, fS, &e.g);
+  if (e.ok) *out = e.g;
+  return e.ok;
+}
+
+template <int RP>
+bool plan_tile_search(const Cp4Args& a, const DeviceInfo& di, int fTH, int fTW, int fS, MmaGeom* out) {
+  MmaGeom best{};
+  double best_cost = 1e300;
   for (int TW = 1; TW <= std::min(a.W, 64); ++TW) {
     if (fTW ? TW != std::min(fTW, a.W) : (TW != a.W && a.W % TW != 0 && TW % 8 != 0)) continue;
     for (int TH = 1; TH <= std::min(a.H, 64); ++TH) {
@@ -614,7 +644,8 @@ int run_mma(const Cp4Args& a, const DeviceInfo& di, cudaStream_t st) {
   g.N = a.N; g.Cin = a.Cin; g.Cout = a.Cout; g.H = a.H; g.W = a.W; g.Y = a.Y; g.X = a.X; g.pad = a.pad;
   g.R = a.R; g.Rs = a.Rs; g.r0 = a.r0; g.flip = a.flip; g.accumulate = a.accumulate;
   g.tilesH = ceil_div(a.H, g.TH); g.tilesW = ceil_div(a.W, g.TW);
-  if (getenv("B200CP_DEBUG"))
+  static const bool debug = getenv("B200CP_DEBUG") != nullptr;
+  if (debug)
     fprintf(stderr, "[b200cp] mma tile TH=%d TW=%d blocks %d/%d per warp %d/%d slices %d smem=%zu RP=%d\n", g.TH, g.TW,
             g.MB1, g.MB3, g.MBW1, g.MBW3, g.S, sizeof(float) * mma_smem_floats<RP>(g), RP);
   if (a.Y == 3 && a.X == 3) return dispatch_blocks<RP, 3>(g, a, st);

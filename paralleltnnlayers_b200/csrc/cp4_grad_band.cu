@@ -55,6 +55,7 @@ struct GradGeom {
   int stages, stage_bytes, chmax;         // ring depth, bytes per stage, channel rows per stage (max(T, C) padded to 16)
   int nparam;                             // floats of a band's partial vector: (T + C + 6) * R
   int oP, oQ, oZ, oW, oRed, oBar;         // byte offsets: Q plane first (ring space from the start), then P; Z; weights
+  long long* trace;                       // diagnostics: 32 cycle stamps per CTA for the first 1024 CTAs (null: off)
 };
 
 __device__ __forceinline__ bool try_wait(uint32_t bar, uint32_t parity) {
@@ -133,6 +134,9 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
     return;
   }
 
+  long long* tr = (g.trace != nullptr && blockIdx.x < 1024 && tid == 0) ? g.trace + (size_t)blockIdx.x * 32 : nullptr;
+  auto stamp = [&](int k) { if (tr) tr[k] = clock64(); };
+  stamp(0);
   if (tid == 0) {
     for (int i = 0; i < S; ++i) {
       mbar_init(&full[i], 1);
@@ -216,8 +220,10 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
         Zs[r * ZP + own_rows * W + q] = 0.f;
       }
     }
+    stamp(1);
     bool ok = wait_or_abort(planes_full, 0, abort_flag);
     consumers_sync();
+    stamp(2);
     ok = ok && !*abort_flag;
 
     // ---- stencil: strips of 8 pixels, one rank per thread ------------------------------------------------------------
@@ -316,6 +322,7 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
     __syncwarp();
     if (lane == 0) mbar_arrive(planes_free);   // this warp reads the halo planes no more: their space joins the ring
     consumers_sync();                          // Z is complete; the spatial sums are in place
+    stamp(3);
     if (kind && ok && tid < 6 * RP) {
       // spatial sums of rank r over the threads that worked on it, in thread order
       const int r = tid % RP, k = tid / RP;
@@ -347,6 +354,7 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
         ok = wait_or_abort(&full[slot], par, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (s < 16) stamp(8 + s);
         if (active) {
           const uint8_t* st = sm + g.oQ + (size_t)slot * g.stage_bytes;
           for (int ks = kp; ks < kChunk / 8; ks += KS) {
@@ -377,6 +385,7 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
         if (lane == 0) mbar_arrive(&empty[slot]);
         if (++slot == S) { slot = 0; par ^= 1; }
       }
+      stamp(4);
       // the KS partial sums of a channel block meet in shared memory and are added in phase order
       mma_sync();
       float* rw = red + warp * (NMB * 256);
@@ -405,6 +414,8 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
       }
     }
   }
+  stamp(5);
+  if (tr) { unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid)); tr[6] = smid; tr[7] = kind; }
   __syncthreads();
   if (*abort_flag) {
     if (tid == 0) atomicCAS(&g_grad_band_status, 0, (1 << 16) | (int)(blockIdx.x & 0xffff));
@@ -469,7 +480,36 @@ const int g_grad_band_th = [] {
   return e ? atoi(e) : 0;
 }();
 
+bool plan_grad_search(const Cp4BwdFilterArgs& a, const DeviceInfo& di, GradGeom* out, size_t* smem_out, int* nmb_out);
+
+// The search runs once per shape (and pointer alignment class): a training loop asks for the same plan every step.
 bool plan_grad(const Cp4BwdFilterArgs& a, const DeviceInfo& di, GradGeom* out, size_t* smem_out, int* nmb_out) {
+  struct Entry {
+    int key[12];
+    bool ok;
+    GradGeom g;
+    size_t smem;
+    int nmb;
+  };
+  thread_local Entry cache[4];
+  thread_local int used = 0, next = 0;
+  const int aligned = !((reinterpret_cast<uintptr_t>(a.X) & 15) || (reinterpret_cast<uintptr_t>(a.dU) & 15));
+  const int key[12] = {a.N, a.C, a.T, a.H, a.W, a.F, a.pad, a.R, a.KC ? 1 : 0, aligned, di.sm_count, di.smem_optin};
+  for (int i = 0; i < used; ++i)
+    if (std::memcmp(cache[i].key, key, sizeof(key)) == 0) {
+      if (cache[i].ok) { *out = cache[i].g; *smem_out = cache[i].smem; *nmb_out = cache[i].nmb; }
+      return cache[i].ok;
+    }
+  Entry& e = cache[next];
+  next = (next + 1) % 4;
+  used = std::min(used + 1, 4);
+  std::memcpy(e.key, key, sizeof(key));
+  e.ok = plan_grad_search(a, di, &e.g, &e.smem, &e.nmb);
+  if (e.ok) { *out = e.g; *smem_out = e.smem; *nmb_out = e.nmb; }
+  return e.ok;
+}
+
+bool plan_grad_search(const Cp4BwdFilterArgs& a, const DeviceInfo& di, GradGeom* out, size_t* smem_out, int* nmb_out) {
   if (g_grad_band_off) return false;
   if (a.F != 3 || a.pad != 1 || a.KC) return false;
   if (a.W % 4 != 0 || (a.H * a.W) % 4 != 0 || a.R > 16 || a.R < 1) return false;
@@ -557,24 +597,28 @@ int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float*
   if ((reinterpret_cast<uintptr_t>(P) & 15) || (reinterpret_cast<uintptr_t>(Q) & 15)) return B200CP_OK;
   g.N = a.N; g.H = a.H; g.W = a.W; g.C = a.C; g.T = a.T; g.R = a.R; g.Rs = a.Rs; g.r0 = a.r0;
   g.nparam = (a.T + a.C + 6) * a.R;
+  g.trace = band_trace_buffer();
   const size_t need = (size_t)g.tiles * g.nparam * sizeof(float);
   if (a.ws_bytes < need)
     return fail(B200CP_ERR_WORKSPACE, "cp4 bwd-filter (bands): workspace of %zu bytes needed, %zu given", need, a.ws_bytes);
   CUtensorMap mU, mX;
   if (int rc = chunk_map(a.dU, a.N, a.T, a.H, a.W, g.chmax, &mU)) return rc;
   if (int rc = chunk_map(a.X, a.N, a.C, a.H, a.W, g.chmax, &mX)) return rc;
-  if (getenv("B200CP_DEBUG"))
+  static const bool debug = getenv("B200CP_DEBUG") != nullptr;
+  if (debug)
     fprintf(stderr, "[b200cp] grad band TH=%d bands=%d chunks=%d stages=%d stage=%d smem=%zu NMB=%d\n", g.TH, g.bands, g.nchunk,
             g.stages, g.stage_bytes, smem, nmb);
   const long ctas = 2L * g.tiles;
   if (ctas > 0x7fffffffL) return fail(B200CP_ERR_UNSUPPORTED, "cp4 bwd-filter: too many tiles");
   if (nmb == 1) {
     auto kern = cp4_grad_band_kernel<1>;
-    B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static std::atomic<int> smem_set[64];
+    B200CP_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_set, (int)smem));
     kern<<<(unsigned)ctas, kNT, smem, st>>>(g, mU, mX, P, Q, a.KH, a.KW, (float*)a.ws);
   } else {
     auto kern = cp4_grad_band_kernel<2>;
-    B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static std::atomic<int> smem_set[64];
+    B200CP_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_set, (int)smem));
     kern<<<(unsigned)ctas, kNT, smem, st>>>(g, mU, mX, P, Q, a.KH, a.KW, (float*)a.ws);
   }
   B200CP_LAUNCH_OK("cp4_grad_band_kernel");

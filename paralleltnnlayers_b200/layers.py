@@ -18,27 +18,31 @@ DEFAULT_FACTORIZATION_BASE = 16       # test/layers.py:17
 
 
 def generate_shape(number, order=None, base=None, reverse=False):
-    """Factor a power of two into mode sizes (test/layers.py:22-48): with ``base`` as many modes of size ``base`` as
-    fit (a small remainder is folded into the first mode); with ``order`` the twos are dealt round-robin."""
+    """Mode sizes of a power of two ``number = 2**e``, the rule of the reference's ``generate_shape``
+    (test/layers.py:22-48), stated on the exponents.
+
+    ``base = 2**b``: ``e = q*b + s`` gives ``q`` modes of size ``base``; the left-over ``2**s`` becomes a mode of its
+    own when it is at least ``sqrt(base)`` (``2*s >= b``) or when there is no other mode, else it is folded into the
+    first mode.  ``order``: the ``e`` twos are dealt to ``order`` modes in turn, so the first ``e % order`` modes get
+    one more.  ``reverse`` flips the list.
+    """
     if number <= 0 or number & (number - 1):
         raise ValueError("generate_shape supports powers of two only")
     if (order is None) == (base is None):
         raise ValueError("give either order or base")
-    if order is None:
-        shape = []
-        while number >= base:
-            shape.append(base)
-            number //= base
-        if number * number >= base or not shape:
-            shape.append(number)
-        else:
-            shape[0] *= number
+    e = number.bit_length() - 1
+    if order is not None:
+        shape = [1 << (e // order + (1 if k < e % order else 0)) for k in range(order)]
     else:
-        shape, l = [1] * order, 0
-        while number > 1:
-            shape[l] *= 2
-            l = (l + 1) % order
-            number //= 2
+        if base < 2 or base & (base - 1):
+            raise ValueError("base must be a power of two")
+        b = base.bit_length() - 1
+        q, s = divmod(e, b)
+        shape = [base] * q
+        if q == 0 or 2 * s >= b:
+            shape.append(1 << s)
+        else:
+            shape[0] <<= s
     return shape[::-1] if reverse else shape
 
 

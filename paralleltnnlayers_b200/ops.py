@@ -115,6 +115,18 @@ def cp4recom(FT, FC, FY, FX):
     return K
 
 
+def allclose(A, B, tolerance=1e-3):
+    """``AllClose`` (Cuda_kernels/Utils.cu:159-180): True when no element's relative difference
+    max(|a-b|/|a|, |a-b|/|b|) exceeds ``tolerance``; the count runs on the device."""
+    A, B = _dev(A, "A"), _dev(B, "B")
+    if A.numel() != B.numel():
+        return False
+    n = C.c_ulonglong(0)
+    with torch.cuda.device(A.device):
+        check(lib.b200cp_allclose_count(_p(A), _p(B), A.numel(), C.c_float(tolerance), C.byref(n), _stream()))
+    return n.value == 0
+
+
 def cp4_conv2d_step(X, dU, FT, FC, FY, FX, pad=1, flags=0):
     """One training step on device tensors (``b200cp_cp4_step``): returns (U, dX, dK_packed); the work forward,
     backward-data and backward-filter share is done once."""
@@ -135,7 +147,8 @@ def cp4_conv2d_step(X, dU, FT, FC, FY, FX, pad=1, flags=0):
 
 
 def _shares_planes(s, flags):
-    return s.Y == 3 and s.X == 3 and s.pad == 1 and (flags & 7) in (0, 4)
+    """The library's own rule (``b200cp_cp4_shares_planes``): shape, path flags and its environment switches."""
+    return bool(lib.b200cp_cp4_shares_planes(C.byref(s), flags))
 
 
 def cp4_conv2d_forward_save(Input, FT, FC, FY, FX, pad=1, flags=0):
@@ -447,8 +460,8 @@ class CP4Conv2dFunction(torch.autograd.Function):
     def forward(ctx, x, FT, FC, FY, FX, pad=1, flags=0):
         ctx.pad, ctx.flags = pad, flags
         # with 3x3 filters the forward keeps its rank plane for the factor gradients (a quarter of x at C = 4R)
-        ctx.shared = (FY.shape[0] == 3 and FX.shape[0] == 3 and pad == 1 and (flags & 7) in (0, 4) and
-                      any(t.requires_grad for t in (FT, FC, FY, FX)))
+        ctx.shared = (any(t.requires_grad for t in (FT, FC, FY, FX)) and x.dim() == 4 and
+                      _shares_planes(_shape_from(x, FT, FC, FY, FX, pad), flags))
         if ctx.shared:
             y, P = cp4_conv2d_forward_save(x, FT, FC, FY, FX, pad, flags)
             ctx.save_for_backward(x, FT, FC, FY, FX, P)

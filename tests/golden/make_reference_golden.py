@@ -2,10 +2,12 @@
 kernels (oracle/_ref, built from the reference sources by oracle/build_ref.py)
 on seeded inputs.  Needs a GPU; run from the repository root:
 
-    python tests/golden/make_reference_golden.py [out.npz]
+    python tests/golden/make_reference_golden.py out.npz
 
 Inputs are not stored: each case is (seed, shape) and is regenerated with
-oracle.cp_oracle.make_cp4_inputs.  The outputs are the reference's fp32 results.
+oracle.cp_oracle.make_cp4_inputs (the CP4 kernels of Cuda_kernels/) or
+oracle.reference_cuda.tvm_inputs (the four fixed-shape TensorFlow-op kernels of
+Kernels/).  The outputs are the reference's fp32 results.
 """
 import os
 import sys
@@ -36,9 +38,31 @@ BWD_FILTER_CASES = {
 }
 
 
+# the fixed-shape TensorFlow-op kernels: name -> (op, seed); shapes in oracle.reference_cuda.TVM_SHAPES
+TVM_CASES = {"tvm_rcp": ("rcp", 201), "tvm_dense": ("dense", 202), "tvm_cp3": ("cp3", 203), "tvm_cp4": ("cp4", 204)}
+
+
+def tvm_oracle(op, arrs):
+    """What the float64 oracle gives for the op's inputs, in the op's own output shape."""
+    if op == "rcp":      # test/test_conv2d_rcp.py:41-45
+        U, K0, K1, KC = arrs
+        return O.rcp_forward(U.reshape(1, 16, 32, 32), [K0, K1], KC).reshape(1, 4, 4, 32, 32)
+    if op == "dense":    # test/test_dense_cp.py:39
+        U, K0, K1, K2 = arrs
+        return O.dense_cp_forward_einsum3(U, K0, K1, K2)
+    if op == "cp3":      # test/test_conv2d_cp.py:19,33-38: K0 [C,R], K1 [FH,FW,R], K2 [R,T]
+        U, K0, K1, K2 = arrs
+        return O.cp3_forward(U, K2.T, K0, K1, 1)
+    U, K0, K1, K2, K3 = arrs   # test/test_conv2d_cp4.py:25: K0 [C,R], K1 [FH,R], K2 [FW,R], K3 [T,R]
+    return O.cp4_forward(U, K3, K0, K1, K2, 1)
+
+
 def main(out):
     assert RC.available(), "oracle/_ref libraries are missing (python -m oracle.build_ref)"
     res = {}
+    if RC.tvm_available():
+        for name, (op, seed) in TVM_CASES.items():
+            res[name] = RC.tvm_run(op, RC.tvm_inputs(op, seed))
     for name, (seed, N, C, T, H, W, F, R, pad, std) in FWD_CASES.items():
         X, K0, K1, KH, KW, dU = O.make_cp4_inputs(seed, N, C, T, H, W, F, F, R, factor_std=std)
         res[name] = RC.forward(X, K0, K1, KH, KW, pad)
@@ -56,4 +80,6 @@ def main(out):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "cp4_reference_golden.npz"))
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    main(sys.argv[1])

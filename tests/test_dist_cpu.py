@@ -59,3 +59,53 @@ def test_two_ranks_reduce_to_the_full_batch_gradient():
         assert p.exitcode == 0
     assert sorted(r for r, _ in res) == [0, 1]
     assert all(e < 1e-10 for _, e in res)
+
+
+def _worker_layers(rank, world, port, q):
+    """The packed-gradient helpers of the reshaped-CP and dense layers: pack, one allreduce, unpack."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        errs = []
+        # dense: per-shard oracle gradients, packed like dense_data_parallel_step packs them
+        B = 6
+        X, F, dY = O.make_dense_inputs(3, B, (2, 3), (3, 2), 4)
+        s, c = D.shard_batch(B, rank, world)
+        _, dF = O.dense_cp_backward(X[s:s + c], dY[s:s + c], F)
+        like = [torch.from_numpy(np.ascontiguousarray(a)) for a in dF]
+        packed = D._pack(like)
+        D.allreduce_factor_grads(packed)
+        _, full = O.dense_cp_backward(X, dY, F)
+        for a, b in zip(D._unpack(packed, like), full):
+            errs.append(float(np.abs(a.numpy() - b).max()))
+        # reshaped-CP conv
+        N = 4
+        Xr, A, S, dV = O.make_rcp_inputs(4, N, (2, 2), (2, 3), 5, 4, 3, 3, 3)
+        s, c = D.shard_batch(N, rank, world)
+        _, dA, dS = O.rcp_backward(Xr[s:s + c], dV[s:s + c], A, S)
+        like = [torch.from_numpy(np.ascontiguousarray(a)) for a in list(dA) + [dS]]
+        packed = D._pack(like)
+        assert packed.numel() == sum(a.size for a in A) + S.size
+        D.allreduce_factor_grads(packed)
+        _, fA, fS = O.rcp_backward(Xr, dV, A, S)
+        for a, b in zip(D._unpack(packed, like), list(fA) + [fS]):
+            errs.append(float(np.abs(a.numpy() - b).max()))
+        q.put((rank, max(errs)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_reduce_the_dense_and_rcp_gradients():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_layers, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(e < 1e-9 for _, e in res), res

@@ -118,3 +118,34 @@ def test_shape_list_bench_writes_the_reference_csv(tmp_path):
     rows = out.read_text().strip().split("\n")
     assert rows[0].startswith("1 16 13 13 1 32 3 3, ") and rows[1].startswith("1 48 27 27 2 64 5 5, ")
     assert all(len(r.split(", ")) == 4 and all(float(v) > 0 for v in r.split(", ")[1:]) for r in rows)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("switch", ["B200CP_STEP_NO_SHARE", "B200CP_AUTO_MMA"])
+def test_layer_forward_backward_with_the_sharing_switched_off(switch):
+    """The library reads its switches when it is loaded, so this runs in a fresh process: with the rank planes not
+    shared (B200CP_STEP_NO_SHARE=1) or the mma path off (B200CP_AUTO_MMA=0) a CP4Conv2d layer must still run its
+    forward and backward (through the plain kernels) and agree with the oracle."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import numpy as np, torch
+import paralleltnnlayers_b200 as P
+from oracle import cp_oracle as O
+X, K0, K1, KH, KW, dU = O.make_cp4_inputs(5, 2, 8, 8, 12, 12, 3, 3, 4, factor_std=0.3)
+t = [torch.from_numpy(a).cuda().requires_grad_(True) for a in (X, K0, K1, KH, KW)]
+y = P.CP4Conv2dFunction.apply(*t, 1, 0)
+y.backward(torch.from_numpy(dU).cuda())
+ref = O.cp4_backward_filter(X, dU, K0, K1, KH, KW, 1)
+assert np.allclose(y.detach().cpu().numpy(), O.cp4_forward(X, K0, K1, KH, KW, 1), rtol=1e-4, atol=1e-5)
+assert np.allclose(t[0].grad.cpu().numpy(), O.cp4_backward_data(dU, K0, K1, KH, KW, 1), rtol=1e-4, atol=1e-5)
+for g, r in zip(t[1:], ref):
+    assert np.allclose(g.grad.cpu().numpy(), r, rtol=1e-4, atol=1e-5 * max(1.0, float(np.abs(r).max())))
+print("ok")
+'''
+    env = dict(os.environ)
+    env[switch] = "0" if switch == "B200CP_AUTO_MMA" else "1"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr

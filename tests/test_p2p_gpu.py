@@ -43,6 +43,95 @@ def test_single_rank_exchange_and_graph_replay():
     ar.close()
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_exchange_recovers():
+    """Two ranks of one process on one GPU, driven one after the other with a wait limit of about a millisecond.
+    The rank launched first stores its vector and raises its flags, finds its peer's flag missing, gives up within
+    the limit (the kernel returns by itself: nothing is trapped or left spinning), fills its result with NaN and
+    records the time-out; the rank launched second finds the first one's data in place and gets the correct sum.
+    The next exchange, in the opposite order, behaves the same way: the contexts stay usable."""
+    import ctypes as C
+    import paralleltnnlayers_b200 as P
+    lib = P._lib.lib
+    n = 777
+    ctxs = []
+    handle = (C.c_ubyte * 64)()
+    for r in range(2):
+        c = C.c_void_p()
+        P._lib.check(lib.b200cp_p2p_init(r, 2, 1024, handle, C.byref(c)))
+        ctxs.append(c)
+    arr = (C.c_void_p * 2)(*[c.value for c in ctxs])
+    for c in ctxs:
+        P._lib.check(lib.b200cp_test_p2p_connect_local(c, arr))
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    lib.b200cp_test_set_p2p_wait_cycles(2_000_000)          # about a millisecond
+    try:
+        for order in ((1, 0), (0, 1)):
+            v = [torch.randn(n, device="cuda") for _ in range(2)]
+            out = [torch.zeros(n, device="cuda") for _ in range(2)]
+            first, second = order
+            P._lib.check(lib.b200cp_p2p_allreduce(ctxs[first], v[first].data_ptr(), out[first].data_ptr(), n, st))
+            torch.cuda.synchronize()                          # the kernel came back by itself
+            assert lib.b200cp_p2p_status(ctxs[first]) == -5   # B200CP_ERR_TIMEOUT
+            assert b"waited in vain" in lib.b200cp_last_error_string()
+            assert torch.isnan(out[first]).all()              # a missed exchange cannot pass for a sum
+            P._lib.check(lib.b200cp_p2p_allreduce(ctxs[second], v[second].data_ptr(), out[second].data_ptr(), n, st))
+            torch.cuda.synchronize()
+            P._lib.check(lib.b200cp_p2p_status(ctxs[second]))
+            assert torch.equal(out[second], v[0] + v[1])
+            assert lib.b200cp_p2p_status(ctxs[first]) == 0    # the record was cleared when it was read
+    finally:
+        lib.b200cp_test_set_p2p_wait_cycles(0)
+        for c in ctxs:
+            lib.b200cp_p2p_destroy(c)
+
+
+def _worker_free_running(rank, world, port, q):
+    """A few hundred exchanges with nothing between them -- eager, then as a replayed CUDA graph -- so that a rank
+    can run ahead of its peer by the one exchange the two slots allow.  Inputs with sums known in closed form."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from paralleltnnlayers_b200.dist import P2PAllreduce
+    n = 2144
+    ar = P2PAllreduce(n)
+    base = torch.arange(n, device="cuda", dtype=torch.float32)
+    ok = True
+    src = torch.empty(n, device="cuda")
+    outs = [torch.empty(n, device="cuda") for _ in range(300)]
+    for it in range(300):                                  # eager, no collective in between
+        src.copy_(base * (rank + 1) + it)
+        ar(src, outs[it])
+    torch.cuda.synchronize()
+    tri = world * (world + 1) // 2
+    for it in range(300):
+        ok = ok and torch.equal(outs[it], base * tri + world * it)
+    # a captured sequence, replayed: every replay advances the device-side sequence numbers by its 50 exchanges
+    step = torch.zeros(1, device="cuda")
+    acc = torch.zeros(n, device="cuda")
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for _ in range(50):
+                src.copy_(base * (rank + 1) + step)
+                ar(src, outs[0])
+                acc.add_(outs[0])
+                step.add_(1)
+        for _ in range(4):
+            g.replay()
+        torch.cuda.synchronize()
+    k = 200
+    ok = ok and torch.allclose(acc, base * tri * k + world * (k * (k - 1) / 2), rtol=1e-6, atol=1e-3)
+    ar.status()
+    q.put((rank, bool(ok)))
+    torch.cuda.synchronize()
+    dist.barrier()
+    ar.close()
+    dist.destroy_process_group()
+
+
 def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
@@ -71,12 +160,13 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_match_nccl():
+@pytest.mark.parametrize("worker,port", [(_worker, 29533), (_worker_free_running, 29534)], ids=["vs_nccl", "free_running"])
+def test_two_ranks_match_nccl(worker, port):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     world = 2
-    procs = [ctx.Process(target=_worker, args=(r, world, 29533, q)) for r in range(world)]
+    procs = [ctx.Process(target=worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=240) for _ in range(world)]

@@ -51,3 +51,28 @@ def test_reference_backward_filter_matches_oracle():
     for a, b, c in zip(ref, orc, got):
         check(a, b, "reference bwd-filter vs oracle", rtol=1e-3, atol=1e-4)
         check(c, b, "library bwd-filter vs oracle", rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.skipif(not RC.tvm_available(), reason="oracle/_ref TVM-kernel libraries not built")
+@pytest.mark.parametrize("op", ["rcp", "dense", "cp3", "cp4"])
+def test_reference_op_kernels_match_oracle_and_library(op):
+    """The reference's fixed-shape TensorFlow-op kernels (Kernels/rcp_fused_nchw.cu, dense_cp.cu, cp_fused_nchw.cu,
+    cp4_conv_nchw.cu) run here on their one compiled shape: reference == oracle == this library's op of the same name."""
+    import importlib.util
+    import os
+    import paralleltnnlayers_b200 as P
+    spec = importlib.util.spec_from_file_location(
+        "mk", os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "make_reference_golden.py"))
+    mk = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mk)
+    arrs = RC.tvm_inputs(op, 300 + len(op))
+    ref = RC.tvm_run(op, arrs)
+    orc = mk.tvm_oracle(op, arrs)
+    # the dense kernel's own sequential fp32 sum is 2e-4 off float64 (its test allows 1e-2, test/test_dense_cp.py:43)
+    loose = 1e-3 if op == "dense" else 2e-5
+    check(ref, orc, f"reference {op} kernel vs oracle", rtol=loose, atol=1e-5)
+    t = dev(*arrs)
+    got = {"rcp": P.conv2d_rcp_fused_nchw, "dense": P.dense_cp, "cp3": P.conv2d_cp_fused_nchw, "cp4": P.cp4_conv2d_nchw}[op](*t)
+    check(got.reshape(ref.shape), orc, f"library {op} op vs oracle", rtol=1e-4, atol=1e-5 * max(1.0, float(np.abs(orc).max())))
+    check(got.reshape(ref.shape), ref, f"library {op} op vs reference kernel", rtol=max(loose, 1e-4),
+          atol=1e-5 * max(1.0, float(np.abs(orc).max())))
