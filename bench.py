@@ -9,9 +9,11 @@ One step = forward, backward-data and backward-filter over one batch (plus the a
 of the packed factor gradients when more than one GPU runs).  Batches are sharded across
 ranks (weak scaling: every rank owns N=32 images).
 
-Timing: CUDA events on the launching stream; a barrier + synchronize on both sides; the
-maximum over ranks.  Every step uses the next of several distinct buffer sets so that a set
-is evicted from L2 before it is used again.  Rank 0 prints one JSON line.
+Timing: the K steps are captured once as a CUDA graph and replayed REPLAYS times inside the timed
+region (a barrier + synchronize on both sides); every replay has its own pair of CUDA events on the
+launching stream and the reported time per step is the median replay (maximum over ranks).  Every
+step uses the next of several distinct buffer sets so that a set is evicted from L2 before it is
+used again.  Rank 0 prints one JSON line.
 """
 from __future__ import annotations
 
@@ -33,6 +35,7 @@ CFG = dict(N=32, C=64, T=64, H=56, W=56, F=3, R=16, pad=1)
 WORKLOAD = "cp4_conv2d fwd+bwd_data+bwd_filter N=32/GPU C=T=64 56x56 3x3 R=16 same-pad fp32"
 METRIC = "CP4 conv fwd+bwd images/sec"
 FALLBACK_HBM_GBS = 6650.0
+REPLAYS = 10          # replays of the K-step graph inside the timed region; the median is reported
 
 
 def make_inputs(seed, n):
@@ -154,6 +157,89 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def graph_time_us(fn, reps, replays=3):
+    """fn(i) launched `reps` times inside one CUDA graph; microseconds per call, best of `replays` replays."""
+    for i in range(2):
+        fn(i)
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    best = float("inf")
+    with torch.cuda.stream(st):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(reps):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        for _ in range(replays):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            g.replay()
+            e1.record(st)
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / reps * 1e3)
+        del g
+    return best
+
+
+def extra_configs(P, world, rank, reduce_fn, max_over_ranks):
+    """Step times of the other benchmark configurations at a FIXED global batch (strong scaling: every rank owns
+    1 / world of it), each step followed by the allreduce of its packed factor gradients on the same stream:
+    config 3 at (C=T=128, 28x28, R=16) and (C=T=512, 7x7, R=64), global N = 64; config 5, global batch 4096."""
+    out = {"scaling": "strong", "world": world}
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+    for (C, H, R, seed) in ((128, 28, 16, 3), (512, 7, 64, 13)):
+        n = max(1, 64 // world)
+        rng = np.random.default_rng(seed * 100 + rank)
+        std = 1.0 / np.sqrt(9 * C)
+        K = [dev(rng.normal(0, std, size=(d, R))) for d in (C, C, 3, 3)]
+        nsets = int(min(12, max(2, 300e6 // (4 * n * C * H * H * 4) + 1)))
+        Xs = [dev(rng.uniform(-1, 1, size=(n, C, H, H))) for _ in range(nsets)]
+        dUs = [dev(rng.normal(0, 1, size=(n, C, H, H))) for _ in range(nsets)]
+
+        def step(i):
+            U, dX, dK = P.cp4_conv2d_step(Xs[i % nsets], dUs[i % nsets], *K, 1)
+            reduce_fn(dK)
+        us = max_over_ranks(graph_time_us(step, 12))
+        key = f"cfg3_C{C}_{H}x{H}_R{R}"
+        out[key] = {"images_per_rank": n, "step_us": us, "images_per_s": world * n / (us * 1e-6),
+                    "grad_floats": (2 * C + 6) * R}
+        del Xs, dUs
+        torch.cuda.empty_cache()
+    B = max(1, 4096 // world)
+    rng = np.random.default_rng(3000 + rank)
+    F = [dev(rng.normal(0, 0.35, size=(8, 8, 32))) for _ in range(4)]
+    Xs = [dev(rng.normal(0, 1, size=(B, 4096))) for _ in range(3)]
+    dYs = [dev(rng.normal(0, 1, size=(B, 4096))) for _ in range(3)]
+
+    def dstep(i):
+        Y = P.dense_cp(Xs[i % 3], *F)
+        dX, dF = P.dense_cp_backward(Xs[i % 3], dYs[i % 3], *F)
+        reduce_fn(torch.cat([g.reshape(-1) for g in dF]))
+    us = max_over_ranks(graph_time_us(dstep, 4))
+    out["cfg5_dense_8x8x8x8_R32"] = {"samples_per_rank": B, "step_us": us, "samples_per_s": world * B / (us * 1e-6),
+                                    "grad_floats": 4 * 8 * 8 * 32}
+    return out
+
+
+def reference_gpu_forward_us():
+    """The reference's own forward kernel (compiled unmodified for this GPU by oracle/build_ref.py) timed by its own
+    PROFCOUNT loop (47 launches, Cuda_kernels/cp4Conv2dForward.cu:245-327; bench/BenchBothTime.cu:90) at config 1 and
+    config 2.  Forward only; part of the CPU-baseline leg: it is the checker's code, not the product's."""
+    try:
+        from oracle import cp_oracle as O
+        from oracle import reference_cuda as RC
+        if not RC.available():
+            return {"unavailable": "oracle/_ref is not built"}
+        out = {}
+        for name, (seed, N, C, T, H, R, std) in {"config1": (0, 1, 16, 16, 32, 8, 0.5), "config2": (1, 32, 64, 64, 56, 16, None)}.items():
+            X, K0, K1, KH, KW, _ = O.make_cp4_inputs(seed, N, C, T, H, H, 3, 3, R, factor_std=std)
+            out[name] = RC.forward_time(X, K0, K1, KH, KW, 1, 47)
+        return out
+    except Exception as e:     # the baseline leg never takes the product's numbers down with it
+        return {"unavailable": str(e)[:200]}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -162,6 +248,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc3x", "mma"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the step times of the other configurations")
     ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"],
                     help="gradient allreduce of the multi-GPU step: the library's peer-memory kernel, or NCCL")
     ap.add_argument("--separate", action="store_true",
@@ -353,7 +440,7 @@ def main():
     launches = P.launch_count() - l0 if graphed else None
     run_steps()                      # one untimed replay (graph upload, caches)
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(REPLAYS)]
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -361,19 +448,21 @@ def main():
     barrier()
     if launches is None:
         l0 = P.launch_count()
-    e0.record()
-    run_steps()
-    e1.record()
+    for a, b in evs:
+        a.record()
+        run_steps()
+        b.record()
     barrier()
     if launches is None:
-        launches = P.launch_count() - l0
-    ms = e0.elapsed_time(e1)
+        launches = (P.launch_count() - l0) // REPLAYS
+    replay_ms = sorted(a.elapsed_time(b) for a, b in evs)
+    ms = float(np.median(replay_ms))
     if p2p is not None:
         p2p.status()        # raises if an exchange gave up waiting for a peer: the timed steps would not be valid
     # the three kernels on their own, K back-to-back launches each, same rotating buffers, same run
     kt = []
     kernels = [("cp4_fwd", k_fwd, 0), ("cp4_bwd_data", k_bwdd, 0), ("cp4_bwd_filter", k_bwdf, 0)]
-    if shared:   # the kernels of the step: extra bytes = the rank planes written / read
+    if shared:   # the kernels of the step; third entry: bytes of rank planes they move on top of the algorithmic bytes
         kernels += [("cp4_fwd_save", k_fwd_save, 4 * plane_floats), ("cp4_bwd_data_save", k_bwdd_save, 4 * plane_floats),
                     ("cp4_bwd_filter_saved", k_bwdf_saved, 8 * plane_floats)]
         k_fwd_save(0, cur_stream())      # the planes the saved-plane kernel reads
@@ -382,12 +471,16 @@ def main():
         run_k, _ = many(fn, K)
         run_k()
         torch.cuda.synchronize()
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a0.record()
-        run_k()
-        a1.record()
-        torch.cuda.synchronize()
-        kt.append(a0.elapsed_time(a1) / K)
+        reps = []
+        for _ in range(5):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            run_k()
+            a1.record()
+            torch.cuda.synchronize()
+            reps.append(a0.elapsed_time(a1) / K)
+        kt.append(float(np.median(reps)))
+        del run_k
     clocks = sampler.stop() if rank == 0 else None
     mean_ms = np.array(kt)
     if dist is not None:
@@ -412,7 +505,8 @@ def main():
         if dist is not None:   # the gradient exchange of a data-parallel step, on the host-visible result
             g = houts[slot][2].cuda(non_blocking=True)
             dist.all_reduce(g)
-            houts[slot][2].copy_(g)
+            houts[slot][2].copy_(g, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
         return float(houts[slot][2][0])   # the host reads the step's result
 
     def run_e2e(steps):
@@ -428,31 +522,77 @@ def main():
     run_e2e(Ks)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    # the copies alone (same bytes, both directions at once on two streams, no kernels): what the host link gives
+    # this rank while every other rank does the same
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    dbuf = [torch.empty_like(Xd), torch.empty_like(dUd)]
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(Ks):
+        with torch.cuda.stream(s_in):
+            dbuf[0].copy_(hX, non_blocking=True)
+            dbuf[1].copy_(hdU, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            houts[0][0].copy_(dbuf[0], non_blocking=True)
+            houts[0][1].copy_(dbuf[1], non_blocking=True)
+    torch.cuda.synchronize()
+    copy_s = time.perf_counter() - t0
     if dist is not None:
-        te = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        te = torch.tensor([e2e_s, copy_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_s = float(te.item())
+        e2e_s, copy_s = float(te[0].item()), float(te[1].item())
     h2d = 4 * (X.size + dU.size + sum(a.numel() for a in hf))
     d2h = 4 * sum(a.numel() for a in houts[0])
     e2e = world * n * Ks / e2e_s
+    copy_gbs = (h2d + d2h) * Ks / copy_s / 1e9          # per rank, both directions together
+    e2e_gbs = (h2d + d2h) * Ks / e2e_s / 1e9
+
+    # ---- the other configurations, strong scaling, in the same run --------------------------------------------
+    extra = None
+    if not args.no_extra:
+        def reduce_fn(t):
+            if dist is not None:
+                dist.all_reduce(t)
+
+        def max_over_ranks(v):
+            if dist is None:
+                return v
+            tv = torch.tensor([v], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tv, op=dist.ReduceOp.MAX)
+            return float(tv.item())
+        extra = extra_configs(P, world, rank, reduce_fn, max_over_ranks)
+        # what a caller without a CUDA graph pays per step of the headline configuration (host launch path included)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(K):
+            step(i, cur_stream())
+        join_comm()
+        torch.cuda.synchronize()
+        extra["cfg2_eager_step_us"] = max_over_ranks((time.perf_counter() - t0) / K * 1e6)
+        extra["cfg2_graph_step_us"] = ms / K * 1e3
 
     def leave():
-        # CUDA graphs that captured NCCL work keep the communicator busy and make destroy_process_group() wait for
-        # ever; all results are out, so leave without tearing NCCL down
+        # release everything that holds the communicator (captured graphs, the exchange regions), then tear down
         sys.stdout.flush()
         sys.stderr.flush()
         if dist is not None:
             torch.cuda.synchronize()
-            os._exit(0)
+            if p2p is not None:
+                p2p.close()
+            dist.barrier()
+            dist.destroy_process_group()
 
+    del run_steps          # the captured graphs go before the process group does
     if rank != 0:
         leave()
         return
 
     # ---- roofline of the dominant kernel ---------------------------------------------------------
     names = [k[0] for k in kernels]
+    # algorithmic bytes of every kernel: input + output tensor once, the factors once; the rank planes a kernel
+    # of the step writes or reads on top of that are traffic, not algorithmic bytes
     base_bytes = 4 * n * HW * (c["C"] + c["T"]) + 4 * c["R"] * (c["T"] + c["C"] + 2 * c["F"])
-    kbytes = [base_bytes + k[2] for k in kernels]
+    kbytes = [base_bytes for k in kernels]
     in_step = range(3, 6) if shared else range(0, 3)      # the kernels the timed step launches
     dom = max(in_step, key=lambda i: mean_ms[i])
     alg_bytes = kbytes[dom]
@@ -463,9 +603,12 @@ def main():
         traffic = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json"))).get(names[dom])
     except Exception:
         pass
+    step_us = ms / K * 1e3
     roofline = {"bound": "hbm", "kernel": names[dom], "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                 "algorithmic_bytes_per_launch": alg_bytes,
+                "plane_bytes_per_launch": {k[0]: k[2] for k in kernels if k[2]},
+                "step": {"bytes": 3 * base_bytes, "us": step_us, "frac": 3 * base_bytes / (step_us * 1e-6) / 1e9 / peak},
                 "per_kernel_us": {nm: float(v * 1e3) for nm, v in zip(names, mean_ms)},
                 "per_kernel_frac": {nm: float(b / (v * 1e-3) / 1e9 / peak) for nm, v, b in zip(names, mean_ms, kbytes)},
                 "kernels_in_step": [names[i] for i in in_step]}
@@ -477,6 +620,8 @@ def main():
         cpu = {"value": ips, "unit": "images/s", "cores": torch.get_num_threads(), "kind": "port",
                "sample": f"{done} full steps of N={n} in {dt * done:.1f} s (torch-CPU restatement of the reference's "
                          "unfused composition, forward + autograd backward)"}
+        if world == 1:
+            cpu["reference_gpu_forward_us"] = reference_gpu_forward_us()
 
     line = {
         "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
@@ -485,14 +630,20 @@ def main():
         "config": {"workload": WORKLOAD, "images_per_step_per_gpu": n, "path": args.path,
                    "step": "b200cp_cp4_step: forward, backward-data and backward-filter in one call, rank planes shared"
                            if shared else "b200cp_cp4_fwd + b200cp_cp4_bwd_data + b200cp_cp4_bwd_filter",
-                   "timing": "K steps replayed as one CUDA graph between two events" if graphed else "K eager steps between two events",
+                   "timing": (f"K steps captured as one CUDA graph, replayed {REPLAYS} times, each replay between its own two "
+                              "events; median replay") if graphed else f"K eager steps, {REPLAYS} times; median",
+                   "replay_ms": [round(x, 4) for x in replay_ms],
                    "l2": f"{NSETS} rotating buffer sets ({NSETS * 4 * n * HW * 64 * 4 / 1e6:.0f} MB) > 126 MB L2",
                    "collective": ("allreduce of %d packed factor-gradient floats per step (%s), on a communication stream, "
                                   "overlapped with the next step"
                                   % (nK, "b200cp_p2p_allreduce: one kernel over NVLink peer memory" if p2p is not None
                                      else "NCCL")) if world > 1 else "none"},
         "roofline": roofline, "cpu_baseline": cpu,
-        "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ks},
+        "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ks,
+                "copy_gbs_per_rank": e2e_gbs, "copy_only_gbs_per_rank": copy_gbs,
+                "note": "host buffers through b200cp_cp4_step_host_submit / _wait (b200cp_cp4_step inside); the copies "
+                        "alone, both directions at once, reach copy_only_gbs_per_rank on this host"},
+        "extra": extra,
         "gpu_launches": launches, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
