@@ -34,6 +34,10 @@ void b200cp_test_set_band_tensor_loads(int on);
  * allows it, 0 = mma.sync with the output staged in shared memory (the default: it measures faster).  Process-wide. */
 void b200cp_test_set_band_tcgen05(int on);
 
+/* The row-stream convolution kernel (tried before the row bands): 0 = off, 1 = on, -1 = what the environment
+ * variable B200CP_STREAM says (on unless it is 0).  Process-wide. */
+void b200cp_test_set_stream(int on);
+
 /* Diagnostics: the row-band kernel writes 64 cycle stamps (long long) per CTA for its first 512 CTAs into this
  * device buffer (512 * 64 * 8 bytes); NULL switches it off.  Process-wide. */
 void b200cp_test_set_band_trace(void* device_buffer);

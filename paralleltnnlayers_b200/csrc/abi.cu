@@ -115,6 +115,8 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
   const bool mma = takes_mma(path, KC, save);
   if (mma && s->Rank <= 32) {   // row bands with TMA loads where the shape allows them
     bool done = false;
+    if (int rc = cp4_stream_launch(&a, 1, st, &done)) return rc;
+    if (done) return B200CP_OK;
     if (int rc = cp4_band_launch(&a, 1, st, &done)) return rc;
     if (done) return B200CP_OK;
   }
@@ -418,7 +420,9 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
   bool both = false;
   if (s->Rank <= 32) {
     Cp4Args cv[2] = {conv_args(s, X, K0, K1, KH, KW, U, false, nullptr, P), conv_args(s, dU, K0, K1, KH, KW, dX, true, nullptr, Q)};
-    if (int rc = cp4_band_launch(cv, 2, st, &both)) return rc;
+    if (int rc = cp4_stream_launch(cv, 2, st, &both)) return rc;
+    if (!both)
+      if (int rc = cp4_band_launch(cv, 2, st, &both)) return rc;
   }
   if (!both) {
     if (int rc = run_conv(s, X, K0, K1, KH, KW, U, st, flags, false, nullptr, P)) return rc;
@@ -740,6 +744,8 @@ int b200cp_device_status(void) {
   if (v) return fail(B200CP_ERR_TIMEOUT, "gradient GEMM: a bounded wait ran out in block %d", v & 0xffff);
   if (int rc = band_device_status(&v)) return rc;
   if (v) return fail(B200CP_ERR_TIMEOUT, "cp4 band kernel: a bounded wait ran out in block %d", v & 0xffff);
+  if (int rc = stream_device_status(&v)) return rc;
+  if (v) return fail(B200CP_ERR_TIMEOUT, "cp4 row-stream kernel: a bounded wait ran out in block %d", v & 0xffff);
   if (int rc = grad_band_device_status(&v)) return rc;
   if (v) return fail(B200CP_ERR_TIMEOUT, "cp4 gradient band kernel: a bounded wait ran out in block %d", v & 0xffff);
   return B200CP_OK;

@@ -83,6 +83,10 @@ int cp4_mma_launch(const Cp4Args& a, cudaStream_t st);
 // convolutions of the same image size in one launch.  *done = false: not a shape this kernel takes.
 int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done);
 int band_device_status(int* out);
+// Row stream (one persistent CTA per SM; 3x3, pad 1, W a multiple of 8 that is 8 or 24 modulo 32, at most 16 ranks,
+// channels in multiples of 8 / 16): the same contract as cp4_band_launch.
+int cp4_stream_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done);
+int stream_device_status(int* out);
 long long* band_trace_buffer();   // diagnostics buffer set by b200cp_test_set_band_trace (null: off)
 
 struct Cp4BwdFilterArgs {

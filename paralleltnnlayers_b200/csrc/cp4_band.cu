@@ -962,6 +962,11 @@ int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done
   return B200CP_OK;
 }
 
+// (W, H, C, N) view of an NCHW tensor with box (W, rows, cb, 1), from the per-thread cache of recent maps
+int band_tensor_map(const float* ptr, int N, int C, int H, int W, int rows, int cb, CUtensorMap* out) {
+  return band_map(ptr, N, C, H, W, rows, cb, out);
+}
+
 void band_force_rows(int rows) { g_band_th.store(rows > 0 ? rows : 0); }
 void band_force_tensor(int on) { g_band_tensor.store(on ? 1 : 0); }
 void band_force_tc3(int on) { g_band_tc3.store(on ? 1 : 0); }

@@ -255,6 +255,11 @@ def set_band_tcgen05(on):
     lib.b200cp_test_set_band_tcgen05(1 if on else 0)
 
 
+def set_stream(on):
+    """Test hook: the row-stream convolution kernel off (0 / False), on (1 / True) or as the environment says (-1)."""
+    lib.b200cp_test_set_stream(int(on))
+
+
 def debug_cp4_tc(Input, FT, FC, FY, FX, pad=1, terms=3, p_floats=0):
     """Diagnostic forward on the tensor path; also returns the first CTA's rank-R intermediate."""
     Input, FT, FC, FY, FX = (_dev(t, n) for t, n in ((Input, "Input"), (FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))

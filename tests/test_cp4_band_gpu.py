@@ -11,6 +11,15 @@ from tests.gpu_util import check, dev
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(autouse=True)
+def _row_bands_only():
+    """The row-stream kernel is tried first on the shapes it takes; these tests are about the row bands."""
+    import paralleltnnlayers_b200 as P
+    P.set_stream(0)
+    yield
+    P.set_stream(-1)
+
 # (seed, N, C, T, H, W, R, factor std)
 BAND_SHAPES = [
     (70, 2, 64, 64, 56, 56, 16, 1.0 / 24),    # BASELINE config 2 at N = 2: bands of 7 rows, consecutive n-blocks

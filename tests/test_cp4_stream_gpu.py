@@ -1,0 +1,71 @@
+"""Parity of the row-stream CP4 kernel (one persistent CTA per SM, rows handed from warp group to warp group) with
+the float64 oracle at the fp32 tolerance (rtol 1e-4, atol 1e-5): row lists shorter and longer than the grid, ranges
+that start and end inside images, ranks below 16, channel counts that leave output m-blocks unused, the three-factor
+core, accumulation into the output, and the two-convolution launch of the training step with its saved rank planes."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cp_oracle as O
+from tests.gpu_util import check, dev
+
+pytestmark = pytest.mark.gpu
+
+# (seed, N, C, T, H, W, R, factor std): W is 8, 24, 40 or 56; C a multiple of 8, T of 16
+STREAM_SHAPES = [
+    (170, 2, 64, 64, 56, 56, 16, 1.0 / 24),   # BASELINE config 2 at N = 2: 112 rows, fewer than CTAs
+    (171, 9, 64, 64, 56, 56, 16, 1.0 / 24),   # 504 rows: ranges of 3-4 rows that cross image borders
+    (172, 3, 16, 32, 5, 24, 7, 0.2),          # short images, rank padded to 16, half of an m-block group unused
+    (173, 5, 24, 48, 3, 8, 16, 0.15),         # one pixel block per row
+    (174, 2, 40, 16, 9, 40, 3, 0.1),
+    (175, 1, 8, 16, 1, 8, 1, 0.5),            # a single row
+    (176, 4, 16, 16, 100, 24, 8, 0.3),        # tall images
+    (177, 2, 128, 80, 30, 56, 12, 0.03),      # 80 output channels: 5 m-blocks
+]
+
+
+def _inputs(case):
+    seed, N, C, T, H, W, R, std = case
+    return O.make_cp4_inputs(seed, N, C, T, H, W, 3, 3, R, factor_std=std)
+
+
+@pytest.fixture(autouse=True)
+def _stream_on():
+    import paralleltnnlayers_b200 as P
+    P.set_stream(1)
+    yield
+    P.set_stream(-1)
+
+
+@pytest.mark.parametrize("case", STREAM_SHAPES, ids=lambda c: "s%d" % c[0])
+def test_stream_forward_and_backward_data(case):
+    import paralleltnnlayers_b200 as P
+    X, K0, K1, KH, KW, dU = _inputs(case)
+    t = dev(X, K0, K1, KH, KW, dU)
+    U = P.cp4_conv2d_forward(*t[:5], 1)
+    dX = P.cp4_conv2d_backward_data(t[5], *t[1:5], 1)
+    P.device_status()
+    check(U, O.cp4_forward(X, K0, K1, KH, KW, 1), "forward (stream)")
+    check(dX, O.cp4_backward_data(dU, K0, K1, KH, KW, 1), "backward-data (stream)")
+    # the row bands compute the same sums in another order
+    P.set_stream(0)
+    U2 = P.cp4_conv2d_forward(*t[:5], 1)
+    assert float((U - U2).abs().max()) <= 4e-6 * float(U2.abs().max())
+
+
+@pytest.mark.parametrize("case", [STREAM_SHAPES[0], STREAM_SHAPES[1], STREAM_SHAPES[6]], ids=lambda c: "s%d" % c[0])
+def test_stream_step(case):
+    """b200cp_cp4_step: both convolutions as one row list, rank planes saved for the factor gradients."""
+    import paralleltnnlayers_b200 as P
+    X, K0, K1, KH, KW, dU = _inputs(case)
+    t = dev(X, K0, K1, KH, KW, dU)
+    U, gX, dK = P.cp4_conv2d_step(t[0], t[5], *t[1:5], 1)
+    P.device_status()
+    check(U, O.cp4_forward(X, K0, K1, KH, KW, 1), "step forward")
+    check(gX, O.cp4_backward_data(dU, K0, K1, KH, KW, 1), "step backward-data")
+    off = 0
+    for r, nm in zip(O.cp4_backward_filter(X, dU, K0, K1, KH, KW, 1), ("dK0", "dK1", "dKH", "dKW")):
+        check(dK[off:off + r.size].view(*r.shape), r, "step " + nm, rtol=1e-4, atol=1e-5 * max(1.0, float(np.abs(r).max())))
+        off += r.size
+    U2, gX2, dK2 = P.cp4_conv2d_step(t[0], t[5], *t[1:5], 1)
+    assert torch.equal(U, U2) and torch.equal(gX, gX2) and torch.equal(dK, dK2)
