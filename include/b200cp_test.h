@@ -38,6 +38,10 @@ void b200cp_test_set_band_tcgen05(int on);
  * variable B200CP_STREAM says (on unless it is 0).  Process-wide. */
 void b200cp_test_set_stream(int on);
 
+/* Number of launches of the row-stream kernel by this process so far: a test that means to exercise that kernel
+ * checks that the count moved. */
+long long b200cp_test_stream_launches(void);
+
 /* Diagnostics: the row-band kernel writes 64 cycle stamps (long long) per CTA for its first 512 CTAs into this
  * device buffer (512 * 64 * 8 bytes); NULL switches it off.  Process-wide. */
 void b200cp_test_set_band_trace(void* device_buffer);

@@ -87,6 +87,7 @@ def _load():
         "b200cp_test_set_band_tensor_loads": (None, [i]),
         "b200cp_test_set_band_tcgen05": (None, [i]),
         "b200cp_test_set_stream": (None, [i]),
+        "b200cp_test_stream_launches": (C.c_longlong, []),
         "b200cp_test_set_p2p_wait_cycles": (None, [C.c_longlong]),
         "b200cp_test_p2p_connect_local": (i, [vp, pp]),
     }

@@ -115,13 +115,14 @@ struct RingPos {
 struct Segment {
   int conv, n, y0, len;
 };
-__device__ __forceinline__ bool next_segment(long long& cur, long long end, const StreamGeom& g, Segment& s) {
+// (row indices are 32-bit: the launcher refuses row lists of 2^31 rows or more)
+__device__ __forceinline__ bool next_segment(int& cur, int end, const StreamGeom& g, Segment& s) {
   if (cur >= end) return false;
-  const long long img = cur / g.H;
-  s.y0 = (int)(cur - img * g.H);
-  s.len = (int)min((long long)(g.H - s.y0), end - cur);
-  s.conv = (int)(img / g.N);
-  s.n = (int)(img - (long long)s.conv * g.N);
+  const int img = cur / g.H;
+  s.y0 = cur - img * g.H;
+  s.len = min(g.H - s.y0, end - cur);
+  s.conv = img >= g.N ? 1 : 0;
+  s.n = img - s.conv * g.N;
   cur += s.len;
   return true;
 }
@@ -179,10 +180,12 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
   }
   __syncthreads();
 
-  const long long G = (long long)g.nconv * g.N * H;
-  const long long ga = G * (long long)blockIdx.x / (long long)gridDim.x;
-  const long long gb = G * ((long long)blockIdx.x + 1) / (long long)gridDim.x;
-  long long cur = ga;
+  // rows [ga, gb) of the list: the first (G mod grid) CTAs take one row more
+  const int G = g.nconv * g.N * H;
+  const int per = G / (int)gridDim.x, rem = G - per * (int)gridDim.x;
+  const int ga = (int)blockIdx.x * per + min((int)blockIdx.x, rem);
+  const int gb = ga + per + ((int)blockIdx.x < rem ? 1 : 0);
+  int cur = ga;
   Segment s;
 
   if (warp == 2 * NB) {
@@ -206,28 +209,40 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
       }
     }
   } else {
-    // factor planes, stencil weights and the two zero columns of every rank-ring row
+    // factor planes, stencil weights and the two zero columns of every rank-ring row; the global loads of a thread
+    // are all issued before the first value is used
     {
-      const int wt = tid;
       for (int cv = 0; cv < g.nconv; ++cv) {
         const StreamProb& p = cv ? p1 : p0;
         float* f1 = F1 + (size_t)cv * 2 * kRP * FP1;
-        for (int i = wt; i < kRP * p.Cin; i += kWorkers) {
-          const int c = i / kRP, r = i - c * kRP;     // r fastest: contiguous reads of Fin[c][:]
-          const float v = r < g.R ? __ldg(p.Fin + (size_t)c * g.Rs + g.r0 + r) : 0.f;
-          const float hi = tf32_round(v);
-          f1[r * FP1 + c] = hi;
-          f1[kRP * FP1 + r * FP1 + c] = tf32_round(v - hi);
-        }
         float* f2 = F2 + (size_t)cv * 2 * g.CoutPad * FP2;
-        for (int i = wt; i < g.CoutPad * kRP; i += kWorkers) {
-          const int t = i / kRP, r = i - t * kRP;
-          const float v = (r < g.R && t < p.Cout) ? __ldg(p.Fout + (size_t)t * g.Rs + g.r0 + r) : 0.f;
-          const float hi = tf32_round(v);
-          f2[t * FP2 + r] = hi;
-          f2[g.CoutPad * FP2 + t * FP2 + r] = tf32_round(v - hi);
+        const int n1 = kRP * p.Cin, n2 = g.CoutPad * kRP;
+        for (int i0 = 0; i0 < max(n1, n2); i0 += 4 * kWorkers) {
+          float v1[4], v2[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * kWorkers + tid;
+            const int c = i / kRP, r = i - c * kRP;     // r fastest: contiguous reads of Fin[c][:] and Fout[t][:]
+            v1[k] = (i < n1 && r < g.R) ? __ldg(p.Fin + (size_t)c * g.Rs + g.r0 + r) : 0.f;
+            v2[k] = (i < n2 && r < g.R && c < p.Cout) ? __ldg(p.Fout + (size_t)c * g.Rs + g.r0 + r) : 0.f;
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * kWorkers + tid;
+            const int c = i / kRP, r = i - c * kRP;
+            if (i < n1) {
+              const float hi = tf32_round(v1[k]);
+              f1[r * FP1 + c] = hi;
+              f1[kRP * FP1 + r * FP1 + c] = tf32_round(v1[k] - hi);
+            }
+            if (i < n2) {
+              const float hi = tf32_round(v2[k]);
+              f2[c * FP2 + r] = hi;
+              f2[g.CoutPad * FP2 + c * FP2 + r] = tf32_round(v2[k] - hi);
+            }
+          }
         }
-        for (int i = wt; i < 9 * kRP; i += kWorkers) {
+        for (int i = tid; i < 9 * kRP; i += kWorkers) {
           const int r = i % kRP, yx = i / kRP, y = yx / 3, x = yx - y * 3;
           const int yy = p.flip ? 2 - y : y, xx = p.flip ? 2 - x : x;
           // a free core [3][3][Rs] (three-factor CP conv) takes the place of the outer product KH x KW
@@ -237,7 +252,7 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
                        : __ldg(p.KH + (size_t)yy * g.Rs + g.r0 + r) * __ldg(p.KW + (size_t)xx * g.Rs + g.r0 + r);
         }
       }
-      for (int i = wt; i < PS * 2 * kRP; i += kWorkers) {
+      for (int i = tid; i < PS * 2 * kRP; i += kWorkers) {
         const int slot = i / (2 * kRP), q = i - slot * 2 * kRP;
         Pr[slot * PSLOT + (q < kRP ? q : (W + 1) * kRP + q - kRP)] = 0.f;
       }
@@ -501,6 +516,7 @@ const bool g_stream_off = [] {
   const char* e = getenv("B200CP_STREAM");
   return e && e[0] == '0';
 }();
+std::atomic<long long> g_stream_launches{0};   // launches of the row-stream kernel by this process (tests read it)
 std::atomic<int> g_stream_force{-1};   // test hook: 0 off, 1 on, -1 the environment's choice
 
 struct StreamPlan {
@@ -597,6 +613,7 @@ int cp4_stream_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* do
     p[i] = make_prob(c);
   }
   const long long rows = (long long)nconv * a.N * a.H;
+  if (rows >= 0x7fffffffLL) return B200CP_OK;
   const unsigned grid = (unsigned)std::min<long long>(di.sm_count, rows);
   static const bool debug = getenv("B200CP_DEBUG") != nullptr;
   if (debug)
@@ -614,9 +631,12 @@ int cp4_stream_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* do
     default: return B200CP_OK;
   }
   if (rc) return rc;
+  g_stream_launches.fetch_add(1, std::memory_order_relaxed);
   *done = true;
   return B200CP_OK;
 }
+
+long long stream_launches() { return g_stream_launches.load(std::memory_order_relaxed); }
 
 void stream_force(int on) { g_stream_force.store(on); }
 
@@ -632,3 +652,4 @@ int stream_device_status(int* out) {
 }  // namespace b200cp
 
 extern "C" void b200cp_test_set_stream(int on) { b200cp::stream_force(on); }
+extern "C" long long b200cp_test_stream_launches(void) { return b200cp::stream_launches(); }

@@ -42,8 +42,10 @@ def test_stream_forward_and_backward_data(case):
     import paralleltnnlayers_b200 as P
     X, K0, K1, KH, KW, dU = _inputs(case)
     t = dev(X, K0, K1, KH, KW, dU)
+    before = P._lib.lib.b200cp_test_stream_launches()
     U = P.cp4_conv2d_forward(*t[:5], 1)
     dX = P.cp4_conv2d_backward_data(t[5], *t[1:5], 1)
+    assert P._lib.lib.b200cp_test_stream_launches() == before + 2     # the kernel under test ran, not another path
     P.device_status()
     check(U, O.cp4_forward(X, K0, K1, KH, KW, 1), "forward (stream)")
     check(dX, O.cp4_backward_data(dU, K0, K1, KH, KW, 1), "backward-data (stream)")
@@ -59,7 +61,9 @@ def test_stream_step(case):
     import paralleltnnlayers_b200 as P
     X, K0, K1, KH, KW, dU = _inputs(case)
     t = dev(X, K0, K1, KH, KW, dU)
+    before = P._lib.lib.b200cp_test_stream_launches()
     U, gX, dK = P.cp4_conv2d_step(t[0], t[5], *t[1:5], 1)
+    assert P._lib.lib.b200cp_test_stream_launches() == before + 1     # both convolutions in one launch
     P.device_status()
     check(U, O.cp4_forward(X, K0, K1, KH, KW, 1), "step forward")
     check(gX, O.cp4_backward_data(dU, K0, K1, KH, KW, 1), "step backward-data")
