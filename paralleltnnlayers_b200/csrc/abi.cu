@@ -389,7 +389,7 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
   int dev = 0;
   B200CP_CUDA_OK(cudaGetDevice(&dev));
   StepFork* fk = nullptr;
-  const bool fork = dev >= 0 && dev < 64 && !g_step_no_fork;
+  const bool may_fork = dev >= 0 && dev < 64 && !g_step_no_fork;
   // the fork / join pairs of two host threads must not interleave on the shared side stream
   std::unique_lock<std::mutex> lk(g_step_mu, std::defer_lock);
   // Whatever way this call ends, the side stream is joined back into the caller's stream: an error return must not
@@ -407,14 +407,6 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
     }
     ~Rejoin() { join(); }
   } rejoin;
-  if (fork) {
-    lk.lock();
-    if (int rc = step_fork(dev, &fk)) return rc;
-    B200CP_CUDA_OK(cudaEventRecord(fk->fork, st));
-    B200CP_CUDA_OK(cudaStreamWaitEvent(fk->side, fk->fork, 0));
-    rejoin.fk = fk;
-    rejoin.st = st;
-  }
   // forward and backward-data: one launch of the band kernel carries both where the shape allows it; otherwise
   // two launches side by side
   bool both = false;
@@ -423,6 +415,17 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
     if (int rc = cp4_stream_launch(cv, 2, st, &both)) return rc;
     if (!both)
       if (int rc = cp4_band_launch(cv, 2, st, &both)) return rc;
+  }
+  // The fused path (both convolutions in one launch, then the gradient band kernel) is a plain chain of kernels on
+  // the caller's stream; everything else runs two branches side by side.
+  const bool fork = may_fork && !(both && s->Rank <= 16);
+  if (fork) {
+    lk.lock();
+    if (int rc = step_fork(dev, &fk)) return rc;
+    B200CP_CUDA_OK(cudaEventRecord(fk->fork, st));
+    B200CP_CUDA_OK(cudaStreamWaitEvent(fk->side, fk->fork, 0));
+    rejoin.fk = fk;
+    rejoin.st = st;
   }
   if (!both) {
     if (int rc = run_conv(s, X, K0, K1, KH, KW, U, st, flags, false, nullptr, P)) return rc;
@@ -439,7 +442,7 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
     a.R = (int)s->Rank;
     bool done = false;
     rejoin.join();   // nothing ran on the side stream
-    if (int rc = cp4_grad_band_launch(a, P, Q, st, &done)) return rc;
+    if (int rc = cp4_grad_band_launch(a, P, Q, st, &done, /*after_own_kernel=*/true)) return rc;
     if (done) return B200CP_OK;
   }
   if (fork && s->Rank <= 64) {

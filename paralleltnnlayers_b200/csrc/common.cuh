@@ -75,6 +75,36 @@ struct Cp4Args {
   const float* KC = nullptr;  // free [Y][X][Rs] spatial core (three-factor CP conv) instead of KH x KW; mma path only
   float* save = nullptr;      // [N][Rs][H][W]: the rank plane sum_ch Fin[ch][r] in[ch][px] is also written here (mma, 3x3)
 };
+// Programmatic dependent launch.  A kernel launched with `programmatic` may be scheduled while the previous kernel on
+// the stream drains: it executes grid_dependency_wait() before its first global read, which returns when that kernel
+// has completed and its writes are visible.  (Without the attribute the wait returns at once.)  B200CP_PDL=0 keeps
+// every launch a plain one.
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets a programmatically dependent kernel be scheduled once every CTA of this grid has got here (or has exited): its
+// CTAs take the SMs this grid leaves and wait in grid_dependency_wait() for the grid's completion.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool programmatic,
+                          Args&&... args) {
+  static const bool off = [] {
+    const char* e = getenv("B200CP_PDL");
+    return e && e[0] == '0';
+  }();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = (programmatic && !off) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
+
 int cp4_simt_launch(const Cp4Args& a, cudaStream_t st);
 // same arguments; channel contractions on the warp-level tensor path (mma.sync, three tf32 terms)
 int cp4_mma_launch(const Cp4Args& a, cudaStream_t st);
@@ -84,7 +114,7 @@ int cp4_mma_launch(const Cp4Args& a, cudaStream_t st);
 int cp4_band_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done);
 int band_device_status(int* out);
 // Row stream (one persistent CTA per SM; 3x3, pad 1, W a multiple of 8 that is 8 or 24 modulo 32, at most 16 ranks,
-// channels in multiples of 8 / 16): the same contract as cp4_band_launch.
+// input channels a multiple of 8, at most 256): the same contract as cp4_band_launch.
 int cp4_stream_launch(const Cp4Args* convs, int nconv, cudaStream_t st, bool* done);
 int stream_device_status(int* out);
 long long* band_trace_buffer();   // diagnostics buffer set by b200cp_test_set_band_trace (null: off)
@@ -111,12 +141,15 @@ size_t cp4_bwd_filter_saved_workspace(const b200cp_tensor_shape& s);
 int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, int part = 0);
 // dK[row*Rs + r0 + r] = sum over parts of partial[part][row*R + r], in a fixed order
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
-                               cudaStream_t st);
+                               cudaStream_t st, bool after_own_kernel = false);
 // the same gradients over full-width row bands (bulk / tensor-map loads, 3x3, W % 4 == 0, at most 16 ranks);
 // *done = false: not a shape this kernel takes
 bool cp4_grad_band_supported(const Cp4BwdFilterArgs& a);
 size_t cp4_grad_band_workspace(const b200cp_tensor_shape& s);
-int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, bool* done);
+// after_own_kernel: the previous launch on the stream is one of this library's kernels (the convolutions that wrote P
+// and Q); the launch then overlaps that kernel's completion (programmatic dependent launch)
+int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, bool* done,
+                         bool after_own_kernel = false);
 int grad_band_device_status(int* out);
 size_t cp4_bwd_filter_static_scratch_bytes();
 int cp4_bwd_filter_static_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);

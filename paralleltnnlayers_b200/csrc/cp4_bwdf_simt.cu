@@ -345,6 +345,7 @@ __global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* 
                                                                    int nparam, int R, int Rs, int r0,
                                                                    float* __restrict__ dK) {
   __shared__ float red[32][33];
+  grid_dependency_wait();   // the partials are the previous kernel's output
   const int j = blockIdx.x * 32 + threadIdx.x, sl = threadIdx.y;
   const int per = (nparts + 31) / 32;
   const int i0 = sl * per, i1 = min(nparts, i0 + per);
@@ -433,8 +434,9 @@ int dispatch_bwd_filter_rank(const Cp4BwdFilterArgs& a, const DeviceInfo& di, cu
 }  // namespace
 
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
-                               cudaStream_t st) {
-  cp4_reduce_partials_kernel<<<ceil_div(nparam, 32), dim3(32, 32), 0, st>>>(partial, nparts, nparam, R, Rs, r0, dK);
+                               cudaStream_t st, bool after_own_kernel) {
+  B200CP_CUDA_OK(launch_kernel(cp4_reduce_partials_kernel, dim3(ceil_div(nparam, 32)), dim3(32, 32), 0, st, after_own_kernel,
+                               partial, nparts, nparam, R, Rs, r0, dK));
   B200CP_LAUNCH_OK("cp4_reduce_partials_kernel");
   return B200CP_OK;
 }

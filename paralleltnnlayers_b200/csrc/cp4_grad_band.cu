@@ -149,6 +149,8 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
     tc::tma_prefetch_desc(kind ? &mapX : &mapU);
   }
   __syncthreads();
+  grid_launch_dependents();
+  grid_dependency_wait();   // the rank planes are the previous kernel's output
 
   float acc[NMB][3][2][4];   // [channel block][term][rank block][fragment]
   if (warp == kCons) {
@@ -586,7 +588,8 @@ size_t cp4_grad_band_workspace(const b200cp_tensor_shape& s) {
 }
 
 // Factor gradients from the saved rank planes; *done = false: not a shape this kernel takes.
-int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, bool* done) {
+int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, bool* done,
+                         bool after_own_kernel) {
   *done = false;
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
@@ -614,15 +617,17 @@ int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float*
     auto kern = cp4_grad_band_kernel<1>;
     static std::atomic<int> smem_set[64];
     B200CP_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_set, (int)smem));
-    kern<<<(unsigned)ctas, kNT, smem, st>>>(g, mU, mX, P, Q, a.KH, a.KW, (float*)a.ws);
+    B200CP_CUDA_OK(launch_kernel(kern, dim3((unsigned)ctas), dim3(kNT), smem, st, after_own_kernel, g, mU, mX, P, Q, a.KH, a.KW,
+                                 (float*)a.ws));
   } else {
     auto kern = cp4_grad_band_kernel<2>;
     static std::atomic<int> smem_set[64];
     B200CP_CUDA_OK(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_set, (int)smem));
-    kern<<<(unsigned)ctas, kNT, smem, st>>>(g, mU, mX, P, Q, a.KH, a.KW, (float*)a.ws);
+    B200CP_CUDA_OK(launch_kernel(kern, dim3((unsigned)ctas), dim3(kNT), smem, st, after_own_kernel, g, mU, mX, P, Q, a.KH, a.KW,
+                                 (float*)a.ws));
   }
   B200CP_LAUNCH_OK("cp4_grad_band_kernel");
-  if (int rc = cp4_reduce_partials_launch((const float*)a.ws, g.tiles, g.nparam, a.R, a.Rs, a.r0, a.dK, st)) return rc;
+  if (int rc = cp4_reduce_partials_launch((const float*)a.ws, g.tiles, g.nparam, a.R, a.Rs, a.r0, a.dK, st, true)) return rc;
   *done = true;
   return B200CP_OK;
 }

@@ -179,6 +179,7 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
     if (g.nconv > 1) tma_prefetch_desc(&map1);
   }
   __syncthreads();
+  grid_launch_dependents();
 
   // rows [ga, gb) of the list: the first (G mod grid) CTAs take one row more
   const int G = g.nconv * g.N * H;
@@ -372,7 +373,7 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
         const StreamProb& p = s.conv ? p1 : p0;
         const int kF2 = g.CoutPad * FP2;
         const float* f2 = F2 + (size_t)s.conv * 2 * kF2 + frow;
-        const int nmb = kRegs ? NMB2 : (p.Cout >> 4);
+        const int nmb = kRegs ? NMB2 : ((p.Cout + 15) >> 4);
         if (kRegs) {
 #pragma unroll
           for (int m = 0; m < (kRegs ? NMB2 : 1); ++m)
@@ -481,15 +482,23 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
               }
 #pragma unroll
               for (int m = 0; m < 4; ++m) {
-                if (mc + m < nmb) {   // uniform over the CTA; only the stores are guarded
-                  float* o0 = op + (size_t)(mc + m) * 16 * cstride;
-                  float* o1 = o0 + 8 * cstride;
-                  float2 u0 = make_float2(acc[m][0], acc[m][1]), u1 = make_float2(acc[m][2], acc[m][3]);
+                // only the stores are guarded: channels past Cout were computed on zero factor rows
+                const int t0 = (mc + m) * 16 + gq;
+                float* o0 = op + (size_t)(mc + m) * 16 * cstride;
+                float* o1 = o0 + 8 * cstride;
+                float2 u0 = make_float2(acc[m][0], acc[m][1]), u1 = make_float2(acc[m][2], acc[m][3]);
+                if (t0 < p.Cout) {
                   if (p.accumulate) {
-                    const float2 c0 = *reinterpret_cast<const float2*>(o0), c1 = *reinterpret_cast<const float2*>(o1);
-                    u0.x += c0.x; u0.y += c0.y; u1.x += c1.x; u1.y += c1.y;
+                    const float2 c0 = *reinterpret_cast<const float2*>(o0);
+                    u0.x += c0.x; u0.y += c0.y;
                   }
                   *reinterpret_cast<float2*>(o0) = u0;
+                }
+                if (t0 + 8 < p.Cout) {
+                  if (p.accumulate) {
+                    const float2 c1 = *reinterpret_cast<const float2*>(o1);
+                    u1.x += c1.x; u1.y += c1.y;
+                  }
                   *reinterpret_cast<float2*>(o1) = u1;
                 }
               }
@@ -528,7 +537,7 @@ bool stream_shape_ok(const Cp4Args& a) {
   if (a.Y != 3 || a.X != 3 || a.pad != 1) return false;
   if (a.W % 8 != 0 || a.W > 8 * kMaxNB || (a.W % 32 != 8 && a.W % 32 != 24)) return false;
   if (a.H < 1 || a.R < 1 || a.R > kRP) return false;
-  if (a.Cin % 8 != 0 || a.Cin > 256 || a.Cout % 16 != 0) return false;
+  if (a.Cin % 8 != 0 || a.Cin > 256 || a.Cout < 1) return false;   // the box of a row holds all input channels
   if (reinterpret_cast<uintptr_t>(a.in) & 15) return false;                    // tensor map
   if (reinterpret_cast<uintptr_t>(a.out) & 7) return false;                    // 8-byte stores
   if (a.save && (reinterpret_cast<uintptr_t>(a.save) & 7)) return false;

@@ -11,14 +11,15 @@ from tests.gpu_util import check, dev
 
 pytestmark = pytest.mark.gpu
 
-# (seed, N, C, T, H, W, R, factor std): W is 8, 24, 40 or 56; C a multiple of 8, T of 16
+# (seed, N, C, T, H, W, R, factor std): W is 8, 24, 40 or 56; C and T multiples of 8 (each is the input channel
+# count of one of the two convolutions)
 STREAM_SHAPES = [
     (170, 2, 64, 64, 56, 56, 16, 1.0 / 24),   # BASELINE config 2 at N = 2: 112 rows, fewer than CTAs
     (171, 9, 64, 64, 56, 56, 16, 1.0 / 24),   # 504 rows: ranges of 3-4 rows that cross image borders
     (172, 3, 16, 32, 5, 24, 7, 0.2),          # short images, rank padded to 16, half of an m-block group unused
     (173, 5, 24, 48, 3, 8, 16, 0.15),         # one pixel block per row
     (174, 2, 40, 16, 9, 40, 3, 0.1),
-    (175, 1, 8, 16, 1, 8, 1, 0.5),            # a single row
+    (175, 1, 8, 24, 1, 8, 1, 0.5),            # a single row; 8 output channels in one direction
     (176, 4, 16, 16, 100, 24, 8, 0.3),        # tall images
     (177, 2, 128, 80, 30, 56, 12, 0.03),      # 80 output channels: 5 m-blocks
 ]
