@@ -115,8 +115,10 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;
-  const int kind = (int)blockIdx.x >= g.tiles ? 1 : 0;
-  const int b = (int)blockIdx.x - kind * g.tiles;
+  // The longer-running kind comes first in the grid: the CTAs that do not fit the first round then follow the
+  // shorter ones.
+  const int kind = (int)blockIdx.x < g.tiles ? 1 : 0;
+  const int b = (int)blockIdx.x - (1 - kind) * g.tiles;
   const int band = b % g.bands, n = b / g.bands;
   const int h0 = band * g.TH;
   const int W = g.W, HW = g.H * g.W, PP = g.PP, ZP = g.ZP;

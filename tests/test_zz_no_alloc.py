@@ -54,7 +54,8 @@ def test_noalloc_refuses_shapes_beyond_the_built_in_array():
     import paralleltnnlayers_b200 as P
     s = P.tensor_shape(256, 128, 56, 56, 128, 3, 3, 64, 1)     # partial sums far beyond 8 MiB
     lib = P._lib.lib
-    assert lib.b200cp_cp4_bwd_filter_workspace_bytes(C.byref(s), 0) > (8 << 20)
+    # sized the way the call sizes it: the exact-fp32 kernels' partial sums
+    assert lib.b200cp_cp4_bwd_filter_workspace_bytes(C.byref(s), P.PATH_SIMT) > (8 << 20)
     one = torch.zeros(1, device="cuda")
     p = C.c_void_p(one.data_ptr())
     rc = lib.b200cp_cp4_bwd_filter_noalloc(C.byref(s), p, p, p, p, p, p, p, None)
