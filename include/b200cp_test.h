@@ -30,6 +30,10 @@ void b200cp_test_set_band_rows(int rows);
  * 0 = one 1-D bulk copy per channel (cp.async.bulk; the default).  Process-wide. */
 void b200cp_test_set_band_tensor_loads(int on);
 
+/* Largest rank the row-band kernel takes (1 .. 32; the default, 16, leaves ranks 17 .. 32 to the tile kernel, which
+ * measures faster there).  Process-wide. */
+void b200cp_test_set_band_max_rank(int rank);
+
 /* Output contraction of the row-band kernel: 1 = tcgen05.mma with the accumulators in tensor memory where the shape
  * allows it, 0 = mma.sync with the output staged in shared memory (the default: it measures faster).  Process-wide. */
 void b200cp_test_set_band_tcgen05(int on);

@@ -86,6 +86,7 @@ def _load():
         "b200cp_test_set_band_trace": (None, [vp]),
         "b200cp_test_set_band_tensor_loads": (None, [i]),
         "b200cp_test_set_band_tcgen05": (None, [i]),
+        "b200cp_test_set_band_max_rank": (None, [i]),
         "b200cp_test_set_stream": (None, [i]),
         "b200cp_test_stream_launches": (C.c_longlong, []),
         "b200cp_test_set_p2p_wait_cycles": (None, [C.c_longlong]),

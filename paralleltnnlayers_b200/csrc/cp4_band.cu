@@ -888,8 +888,17 @@ const bool g_band_off = [] {
   return e && e[0] == '0';
 }();
 
+// Ranks above 16 need two rank m-blocks per warp and one CTA per SM; at N=64, C=T=128, 28x28, R=32 that measures
+// 37.2 us per convolution against 32.8 us for the tile kernel, so the bands take them only on request
+// (B200CP_BAND_MAX_RANK=32, or the test hook).
+std::atomic<int> g_band_max_rank{[] {
+  const char* e = getenv("B200CP_BAND_MAX_RANK");
+  return e ? std::max(1, std::min(32, atoi(e))) : 16;
+}()};
+
 bool band_shape_ok(const Cp4Args& a) {
   if (g_band_off) return false;
+  if (a.R > g_band_max_rank.load(std::memory_order_relaxed)) return false;
   if (a.Y != 3 || a.X != 3 || a.pad != 1) return false;
   if (a.W % 4 != 0 || a.W > 256 || a.H < 1 || a.R > 32) return false;
   if ((reinterpret_cast<uintptr_t>(a.in) & 15) || (reinterpret_cast<uintptr_t>(a.out) & 15)) return false;   // bulk copies
@@ -967,6 +976,7 @@ int band_tensor_map(const float* ptr, int N, int C, int H, int W, int rows, int 
   return band_map(ptr, N, C, H, W, rows, cb, out);
 }
 
+void band_set_max_rank(int r) { g_band_max_rank.store(std::max(1, std::min(32, r))); }
 void band_force_rows(int rows) { g_band_th.store(rows > 0 ? rows : 0); }
 void band_force_tensor(int on) { g_band_tensor.store(on ? 1 : 0); }
 void band_force_tc3(int on) { g_band_tc3.store(on ? 1 : 0); }
@@ -985,6 +995,7 @@ int band_device_status(int* out) {
 }  // namespace b200cp
 
 extern "C" void b200cp_test_set_band_rows(int rows) { b200cp::band_force_rows(rows); }
+extern "C" void b200cp_test_set_band_max_rank(int rank) { b200cp::band_set_max_rank(rank); }
 extern "C" void b200cp_test_set_band_tensor_loads(int on) { b200cp::band_force_tensor(on); }
 extern "C" void b200cp_test_set_band_tcgen05(int on) { b200cp::band_force_tc3(on); }
 extern "C" void b200cp_test_set_band_trace(void* device_buffer) { b200cp::band_set_trace(static_cast<long long*>(device_buffer)); }

@@ -17,7 +17,9 @@ def _row_bands_only():
     """The row-stream kernel is tried first on the shapes it takes; these tests are about the row bands."""
     import paralleltnnlayers_b200 as P
     P.set_stream(0)
+    P._lib.lib.b200cp_test_set_band_max_rank(32)     # by default ranks above 16 go to the tile kernel
     yield
+    P._lib.lib.b200cp_test_set_band_max_rank(16)
     P.set_stream(-1)
 
 # (seed, N, C, T, H, W, R, factor std)
