@@ -251,6 +251,12 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the step times of the other configurations")
     ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"],
                     help="gradient allreduce of the multi-GPU step: the library's peer-memory kernel, or NCCL")
+    ap.add_argument("--exchange", default="overlap", choices=["pipelined", "fused", "inline", "overlap"],
+                    help="N > 1: the allreduce of the factor gradients as the tail of the step's gradient reduction "
+                         "kernel, completed by the next step's (pipelined: b200cp_cp4_step_allreduce_pipelined, the "
+                         "last one by b200cp_p2p_flush inside the timed region) or by the same kernel (fused: "
+                         "b200cp_cp4_step_allreduce) -- both need --allreduce p2p; as its own kernel on the step's "
+                         "stream (inline), or on a communication stream overlapped with the next step (overlap)")
     ap.add_argument("--separate", action="store_true",
                     help="step = the three entry points one after the other instead of b200cp_cp4_step")
     ap.add_argument("--watchdog", type=int, default=420, help="seconds after which a stuck run dumps its stacks and exits")
@@ -371,10 +377,28 @@ def main():
                 sys.stderr.write("[bench] peer-memory allreduce disagrees with NCCL on some rank; using NCCL\n")
                 p2p = None
 
+    fused_exchange = p2p is not None and shared and args.exchange in ("fused", "pipelined")
+    pipelined = fused_exchange and args.exchange == "pipelined"
+    if dist is not None and args.exchange in ("fused", "pipelined") and not fused_exchange:
+        args.exchange = "inline"                    # NCCL, or a path without the fused kernel chain
+    dk_scratch = torch.empty_like(dK) if pipelined else None
+
     def step(i, st):
         dk = dKs[i % len(dKs)]
         if dist is not None and ar_done[i % 2] is not None:
             torch.cuda.current_stream().wait_event(ar_done[i % 2])
+        if shared and pipelined:
+            # step i posts its gradients and completes step i-1's exchange into the other gradient buffer
+            x, du, u, dx = sets[i % NSETS]
+            P._lib.check(lib.b200cp_cp4_step_allreduce_pipelined(
+                p2p._ctx, C.byref(s), ptr(x), ptr(du), *fp, ptr(u), ptr(dx), ptr(dk_scratch), ptr(dKs[(i + 1) % len(dKs)]),
+                ptr(ws_step), wsb_step, st, flags))
+            return
+        if shared and fused_exchange:
+            x, du, u, dx = sets[i % NSETS]
+            P._lib.check(lib.b200cp_cp4_step_allreduce(p2p._ctx, C.byref(s), ptr(x), ptr(du), *fp, ptr(u), ptr(dx), ptr(dk),
+                                                       ptr(ws_step), wsb_step, st, flags))
+            return
         if shared:
             x, du, u, dx = sets[i % NSETS]
             P._lib.check(lib.b200cp_cp4_step(C.byref(s), ptr(x), ptr(du), *fp, ptr(u), ptr(dx), ptr(dk), ptr(ws_step),
@@ -384,7 +408,15 @@ def main():
             k_fwd(i, st)
             k_bwdd(i, st)
             P._lib.check(lib.b200cp_cp4_bwd_filter(C.byref(s), ptr(x), ptr(du), *fp, ptr(dk), ptr(ws), wsb, st, flags_f))
-        if dist is not None:
+        if dist is not None and args.exchange == "inline":
+            # The step's kernels are persistent (one CTA per SM, nearly all of its registers): an exchange kernel on
+            # another stream either waits for them to leave or takes the room of the next step's CTAs, and both
+            # measured slower than the exchange's own few microseconds on the step's stream.
+            if p2p is not None:
+                p2p(dk)
+            else:
+                dist.all_reduce(dk)
+        elif dist is not None:
             ready = torch.cuda.Event()
             ready.record()
             comm.wait_event(ready)
@@ -398,6 +430,8 @@ def main():
             ar_done[i % 2] = done
 
     def join_comm(*_):
+        if pipelined:                       # the last step's exchange, inside the timed region
+            P._lib.check(lib.b200cp_p2p_flush(p2p._ctx, ptr(dKs[0]), cur_stream()))
         for k in range(2):
             if ar_done[k] is not None:
                 torch.cuda.current_stream().wait_event(ar_done[k])
@@ -634,10 +668,15 @@ def main():
                               "events; median replay") if graphed else f"K eager steps, {REPLAYS} times; median",
                    "replay_ms": [round(x, 4) for x in replay_ms],
                    "l2": f"{NSETS} rotating buffer sets ({NSETS * 4 * n * HW * 64 * 4 / 1e6:.0f} MB) > 126 MB L2",
-                   "collective": ("allreduce of %d packed factor-gradient floats per step (%s), on a communication stream, "
-                                  "overlapped with the next step"
+                   "collective": ("allreduce of %d packed factor-gradient floats per step (%s), %s"
                                   % (nK, "b200cp_p2p_allreduce: one kernel over NVLink peer memory" if p2p is not None
-                                     else "NCCL")) if world > 1 else "none"},
+                                     else "NCCL",
+                                     "posted by the step's gradient reduction kernel and completed by the next step's "
+                                     "(b200cp_cp4_step_allreduce_pipelined; the last one by b200cp_p2p_flush, timed)"
+                                     if pipelined else
+                                     "as the tail of the step's gradient reduction kernel (b200cp_cp4_step_allreduce)"
+                                     if fused_exchange else "on the step's stream" if args.exchange == "inline" else
+                                     "on a communication stream, overlapped with the next step")) if world > 1 else "none"},
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ks,
                 "copy_gbs_per_rank": e2e_gbs, "copy_only_gbs_per_rank": copy_gbs,

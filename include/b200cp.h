@@ -240,6 +240,30 @@ int b200cp_p2p_allreduce(void* ctx, const float* src, float* dst, size_t n, void
 int b200cp_p2p_status(void* ctx);
 int b200cp_p2p_destroy(void* ctx);
 
+/* A data-parallel training step: b200cp_cp4_step on this rank's shard with dK_packed summed over the ranks of the
+ * exchange context (b200cp_p2p_init / _connect, made for at least (T+C+Y+X)*Rank floats).  Where the step runs as its
+ * fused kernel chain, the exchange is the tail of the kernel that adds the per-band partial gradients: every CTA of
+ * that kernel stores its 32 sums into every rank's region over NVLink, raises its flag, waits (bounded) for the
+ * peers' flags and adds the rows in rank order -- no separate collective launch.  Other shapes run the step and then
+ * b200cp_p2p_allreduce.  Every rank must make the same sequence of calls on its context.  The reference has no
+ * counterpart (it is single-GPU: Cuda_kernels/cp4Conv2d.cu:210,221). */
+int b200cp_cp4_step_allreduce(void* p2p_ctx, const b200cp_tensor_shape* s, const float* X, const float* dU,
+                              const float* K0, const float* K1, const float* KH, const float* KW, float* U, float* dX,
+                              float* dK_packed, void* workspace, size_t workspace_bytes, void* stream, int flags);
+
+/* The same step with the exchange pipelined over consecutive steps: the call only posts this step's gradient sums to
+ * the peers (the tail of its reduction kernel) and completes the exchange of the *previous* pipelined call, whose
+ * flags arrived a whole step ago, writing those summed gradients to dK_prev (ignored when nothing is pending).  The
+ * exchange latency then costs the step nothing and no second kernel runs beside the step's.  dK_scratch:
+ * (T+C+Y+X)*Rank floats the call may use.  b200cp_p2p_flush completes the last posted exchange into dK_last (a no-op
+ * when nothing is pending); until then no other exchange may use the context.  Consecutive pipelined calls must have
+ * the same shape.  Every rank makes the same sequence of calls.  No counterpart in the reference. */
+int b200cp_cp4_step_allreduce_pipelined(void* p2p_ctx, const b200cp_tensor_shape* s, const float* X, const float* dU,
+                                        const float* K0, const float* K1, const float* KH, const float* KW, float* U,
+                                        float* dX, float* dK_scratch, float* dK_prev, void* workspace,
+                                        size_t workspace_bytes, void* stream, int flags);
+int b200cp_p2p_flush(void* ctx, float* dK_last, void* stream);
+
 /* ---- misc --------------------------------------------------------------- */
 
 /* Synchronises the device and reports whether any tensor-path kernel gave up a bounded wait since

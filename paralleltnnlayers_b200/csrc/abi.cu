@@ -366,9 +366,13 @@ size_t b200cp_cp4_step_workspace_bytes(const b200cp_tensor_shape* s, int flags) 
   return 2 * plane + std::max(std::max(plain, cp4_bwd_filter_saved_workspace(*s)), cp4_grad_band_workspace(*s));
 }
 
-int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0, const float* K1,
-                    const float* KH, const float* KW, float* U, float* dX, float* dK_packed, void* workspace,
-                    size_t workspace_bytes, void* stream, int flags) {
+// The step.  `exchange` (may be null): the peer-memory exchange to run as the tail of the gradient reduction;
+// *exchanged tells the caller whether that happened (only the fused kernel chain can do it).
+static int cp4_step_impl(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0, const float* K1,
+                         const float* KH, const float* KW, float* U, float* dX, float* dK_packed, void* workspace,
+                         size_t workspace_bytes, void* stream, int flags, const ExchangeArgs* exchange,
+                         bool* exchanged) {
+  *exchanged = false;
   if (int rc = check_shape(s, "b200cp_cp4_step")) return rc;
   if (int rc = check_ptrs("b200cp_cp4_step", {X, dU, K0, K1, KH, KW, U, dX, dK_packed})) return rc;
   const size_t need = b200cp_cp4_step_workspace_bytes(s, flags);
@@ -442,8 +446,11 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
     a.R = (int)s->Rank;
     bool done = false;
     rejoin.join();   // nothing ran on the side stream
-    if (int rc = cp4_grad_band_launch(a, P, Q, st, &done, /*after_own_kernel=*/true)) return rc;
-    if (done) return B200CP_OK;
+    if (int rc = cp4_grad_band_launch(a, P, Q, st, &done, /*after_own_kernel=*/true, exchange)) return rc;
+    if (done) {
+      *exchanged = exchange != nullptr;
+      return B200CP_OK;
+    }
   }
   if (fork && s->Rank <= 64) {
     // the gradient kernel in two halves, also side by side: the dK0 half follows the forward on the caller's
@@ -463,6 +470,55 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
     a.R = std::min(64u, s->Rank - r0);
     if (int rc = cp4_bwd_filter_saved_launch(a, P, Q, st)) return rc;
   }
+  return B200CP_OK;
+}
+
+int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0, const float* K1,
+                    const float* KH, const float* KW, float* U, float* dX, float* dK_packed, void* workspace,
+                    size_t workspace_bytes, void* stream, int flags) {
+  bool exchanged = false;
+  return cp4_step_impl(s, X, dU, K0, K1, KH, KW, U, dX, dK_packed, workspace, workspace_bytes, stream, flags, nullptr,
+                       &exchanged);
+}
+
+int b200cp_cp4_step_allreduce(void* p2p_ctx, const b200cp_tensor_shape* s, const float* X, const float* dU,
+                              const float* K0, const float* K1, const float* KH, const float* KW, float* U, float* dX,
+                              float* dK_packed, void* workspace, size_t workspace_bytes, void* stream, int flags) {
+  if (!p2p_ctx) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_allreduce: null exchange context");
+  if (int rc = check_shape(s, "b200cp_cp4_step_allreduce")) return rc;
+  const size_t n = ((size_t)s->T + s->C + s->Y + s->X) * s->Rank;
+  ExchangeArgs ex{};
+  if (int rc = p2p_fused_args(p2p_ctx, n, 0, nullptr, &ex)) return rc;
+  bool exchanged = false;
+  if (int rc = cp4_step_impl(s, X, dU, K0, K1, KH, KW, U, dX, dK_packed, workspace, workspace_bytes, stream, flags, &ex,
+                             &exchanged))
+    return rc;
+  // a shape outside the fused kernel chain: the stand-alone exchange kernel on the finished gradients
+  return exchanged ? B200CP_OK : b200cp_p2p_allreduce(p2p_ctx, dK_packed, dK_packed, n, stream);
+}
+
+int b200cp_cp4_step_allreduce_pipelined(void* p2p_ctx, const b200cp_tensor_shape* s, const float* X, const float* dU,
+                                        const float* K0, const float* K1, const float* KH, const float* KW, float* U,
+                                        float* dX, float* dK_scratch, float* dK_prev, void* workspace,
+                                        size_t workspace_bytes, void* stream, int flags) {
+  if (!p2p_ctx) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_allreduce_pipelined: null exchange context");
+  if (int rc = check_shape(s, "b200cp_cp4_step_allreduce_pipelined")) return rc;
+  if (!dK_scratch) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_allreduce_pipelined: null scratch");
+  const size_t n = ((size_t)s->T + s->C + s->Y + s->X) * s->Rank;
+  ExchangeArgs ex{};
+  if (int rc = p2p_fused_args(p2p_ctx, n, 1, dK_prev, &ex)) return rc;
+  bool exchanged = false;
+  if (int rc = cp4_step_impl(s, X, dU, K0, K1, KH, KW, U, dX, dK_scratch, workspace, workspace_bytes, stream, flags, &ex,
+                             &exchanged))
+    return rc;
+  if (!exchanged) {
+    // a shape outside the fused kernel chain: this rank's gradients are in the scratch vector; the reduction kernel,
+    // run over that one "partial", posts them and completes the previous exchange
+    if (int rc = cp4_reduce_partials_launch(dK_scratch, 1, (int)n, (int)s->Rank, (int)s->Rank, 0, dK_scratch,
+                                            static_cast<cudaStream_t>(stream), true, &ex))
+      return rc;
+  }
+  p2p_fused_set_pending(p2p_ctx, n, (int)s->Rank, (int)s->Rank);
   return B200CP_OK;
 }
 

@@ -140,8 +140,27 @@ size_t cp4_bwd_filter_saved_workspace(const b200cp_tensor_shape& s);
 // 3: the sum of the partials only (after halves 1 and 2, which may run on different streams)
 int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, int part = 0);
 // dK[row*Rs + r0 + r] = sum over parts of partial[part][row*R + r], in a fixed order
+// The peer-memory exchange of a data-parallel step, as the tail of the kernel that sums the partial gradients: every
+// CTA of that kernel owns 32 gradient entries, stores its sums into every rank's exchange region (plain peer stores),
+// raises its flag there, waits (bounded) for the other ranks' flags of the same CTA and adds the rows in rank order.
+// Filled by p2p_fused_args() from a context of b200cp_p2p_init.
+struct ExchangeArgs {
+  float* const* data;      // [world] every rank's data region: [2 slots][world][row]
+  unsigned* const* flags;  // [world] every rank's flags: [2 slots][ctas][16]
+  unsigned* seqs;          // [ctas] sequence number of this rank's last exchange, per CTA
+  int* status;
+  int rank, world, ctas;
+  size_t row;
+  long long wait_cycles;
+  int mode;                // 0: post and complete in the same kernel; 1: post, and complete the previous exchange
+  float* prev_out;         // mode 1: where the previous exchange's sums go (null: nothing is pending)
+};
+// mode 1 keeps the posted exchange pending in the context until the next mode-1 call or p2p_fused_flush completes it
+int p2p_fused_args(void* ctx, size_t n, int mode, float* prev_out, ExchangeArgs* out);
+void p2p_fused_set_pending(void* ctx, size_t n, int R, int Rs);
+int exchange_finish_launch(const ExchangeArgs& ex, int nparam, int R, int Rs, int r0, float* dK, cudaStream_t st);
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
-                               cudaStream_t st, bool after_own_kernel = false);
+                               cudaStream_t st, bool after_own_kernel = false, const ExchangeArgs* exchange = nullptr);
 // the same gradients over full-width row bands (bulk / tensor-map loads, 3x3, W % 4 == 0, at most 16 ranks);
 // *done = false: not a shape this kernel takes
 bool cp4_grad_band_supported(const Cp4BwdFilterArgs& a);
@@ -149,7 +168,7 @@ size_t cp4_grad_band_workspace(const b200cp_tensor_shape& s);
 // after_own_kernel: the previous launch on the stream is one of this library's kernels (the convolutions that wrote P
 // and Q); the launch then overlaps that kernel's completion (programmatic dependent launch)
 int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, bool* done,
-                         bool after_own_kernel = false);
+                         bool after_own_kernel = false, const ExchangeArgs* exchange = nullptr);
 int grad_band_device_status(int* out);
 size_t cp4_bwd_filter_static_scratch_bytes();
 int cp4_bwd_filter_static_launch(const Cp4BwdFilterArgs& a, cudaStream_t st);

@@ -339,11 +339,65 @@ __global__ void __launch_bounds__(256) cp4_bwd_filter_kernel(const GeomF gf, con
   TRACE(5);
 }
 
+__device__ __forceinline__ void ex_st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ex_ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The three parts of one CTA's exchange (a warp; `seq` is the exchange's sequence number, its parity the slot).
+__device__ __forceinline__ void exchange_post(const ExchangeArgs& ex, int cta, int lane, bool live, int j, float v, unsigned seq) {
+  const int slot = (int)(seq & 1u);
+  if (live)
+    for (int p = 0; p < ex.world; ++p) ex.data[p][((size_t)slot * ex.world + ex.rank) * ex.row + j] = v;
+  __syncwarp();   // orders the lanes' stores before the flag lanes, whose fence and release store are cumulative over them
+  if (lane < ex.world) {
+    __threadfence_system();
+    ex_st_release_sys(ex.flags[lane] + ((size_t)slot * ex.ctas + cta) * 16 + ex.rank, seq);
+  }
+}
+__device__ __forceinline__ bool exchange_wait(const ExchangeArgs& ex, int cta, int lane, unsigned seq) {
+  const int slot = (int)(seq & 1u);
+  bool missed = false;
+  if (lane < ex.world) {
+    const unsigned* f = ex.flags[ex.rank] + ((size_t)slot * ex.ctas + cta) * 16 + lane;
+    const long long t0 = clock64();
+    while ((int)(ex_ld_acquire_sys(f) - seq) < 0) {
+      if (clock64() - t0 > ex.wait_cycles) {   // give up, never hang
+        missed = true;
+        atomicExch(ex.status, 1 + ex.rank);
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  missed = __any_sync(0xffffffffu, missed);
+  __syncwarp();   // the acquire loads of the flag lanes are ordered before every lane's loads that follow
+  return missed;
+}
+__device__ __forceinline__ float exchange_sum(const ExchangeArgs& ex, int j, unsigned seq) {
+  const int slot = (int)(seq & 1u);
+  const float* own = ex.data[ex.rank] + (size_t)slot * ex.world * ex.row + j;
+  float t = 0.f;
+  for (int p = 0; p < ex.world; ++p) t += __ldcg(own + (size_t)p * ex.row);   // rank order: the same bits on every rank
+  return t;
+}
+
 // out[j] = sum over CTAs of partial[cta][j].  32 parameters x 32 slices per block: slice s adds the
 // partials of its contiguous CTA range in order, then the slices are added in order (reproducible).
+// EXCHANGE: the sums then go through the peer-memory exchange of a data-parallel step in the same kernel -- the first
+// warp of every CTA stores its 32 sums into every rank's region, raises the CTA's flag there (one system-scope fence
+// and a release store by the lanes that write flags), waits for the peers' flags of the same CTA (bounded; a wait
+// that runs out gives NaN and a status word) and adds the rows in rank order, so every rank gets the same bits.
+// In pipelined mode (ex.mode == 1) the kernel only posts its sums and completes the *previous* step's exchange, whose
+// flags have long arrived: the exchange latency then costs the step nothing.
+template <bool EXCHANGE>
 __global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* __restrict__ partial, int nparts,
                                                                    int nparam, int R, int Rs, int r0,
-                                                                   float* __restrict__ dK) {
+                                                                   float* __restrict__ dK, const ExchangeArgs ex) {
   __shared__ float red[32][33];
   grid_dependency_wait();   // the partials are the previous kernel's output
   const int j = blockIdx.x * 32 + threadIdx.x, sl = threadIdx.y;
@@ -362,13 +416,45 @@ __global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* 
   }
   red[sl][threadIdx.x] = s0;
   __syncthreads();
-  if (sl == 0 && j < nparam) {
-    float s = 0.f;
+  if (sl != 0) return;
+  float s = 0.f;
 #pragma unroll
-    for (int k = 0; k < 32; ++k) s += red[k][threadIdx.x];
-    // the packed output has the same T, C, F, F row sections, with rows of length Rs
+  for (int k = 0; k < 32; ++k) s += red[k][threadIdx.x];
+  // the packed output has the same T, C, F, F row sections, with rows of length Rs
+  const int row = j / R, r = j - row * R;
+  float* out = dK + (size_t)row * Rs + r0 + r;
+  if (!EXCHANGE) {
+    if (j < nparam) *out = s;
+    return;
+  }
+  // ---- exchange (one warp; lane = entry of the CTA's 32, and lanes below `world` also own a peer's flag) -----------
+  const int lane = threadIdx.x, cta = blockIdx.x;
+  const unsigned last = ex.seqs[cta];
+  if (ex.mode == 1 && ex.prev_out != nullptr) {
+    // pipelined: the previous step's exchange is completed here, a whole step after it was posted
+    const bool missed = exchange_wait(ex, cta, lane, last);
+    if (j < nparam) ex.prev_out[(size_t)row * Rs + r0 + r] = missed ? __int_as_float(0x7fc00000) : exchange_sum(ex, j, last);
+  }
+  const unsigned seq = last + 1;
+  exchange_post(ex, cta, lane, j < nparam, j, s, seq);
+  if (ex.mode == 0) {
+    const bool missed = exchange_wait(ex, cta, lane, seq);
+    if (j < nparam) *out = missed ? __int_as_float(0x7fc00000) : exchange_sum(ex, j, seq);
+  }
+  __syncwarp();
+  if (lane == 0) ex.seqs[cta] = seq;   // the sequence advances either way: the next exchange lines up with the peers' again
+}
+
+// Completes the last posted exchange of a pipelined sequence: one warp per 32 entries.
+__global__ void __launch_bounds__(32) exchange_finish_kernel(const ExchangeArgs ex, int nparam, int R, int Rs, int r0,
+                                                             float* __restrict__ dK) {
+  grid_dependency_wait();
+  const int lane = threadIdx.x, cta = blockIdx.x, j = cta * 32 + lane;
+  const unsigned last = ex.seqs[cta];
+  const bool missed = exchange_wait(ex, cta, lane, last);
+  if (j < nparam) {
     const int row = j / R, r = j - row * R;
-    dK[(size_t)row * Rs + r0 + r] = s;
+    dK[(size_t)row * Rs + r0 + r] = missed ? __int_as_float(0x7fc00000) : exchange_sum(ex, j, last);
   }
 }
 
@@ -401,8 +487,9 @@ int launch_bwd_filter(const Cp4BwdFilterArgs& a, const TileChoice& t, const Devi
   B200CP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<(unsigned)ctas, t.NT, smem, st>>>(gf, a.X, a.dU, a.K0, a.K1, a.KH, a.KW, (float*)a.ws);
   B200CP_LAUNCH_OK("cp4_bwd_filter_kernel");
-  cp4_reduce_partials_kernel<<<ceil_div(gf.nparam, 32), dim3(32, 32), 0, st>>>((const float*)a.ws, (int)ctas, gf.nparam,
-                                                                            a.R, a.Rs, a.r0, a.dK);
+  cp4_reduce_partials_kernel<false><<<ceil_div(gf.nparam, 32), dim3(32, 32), 0, st>>>((const float*)a.ws, (int)ctas,
+                                                                                   gf.nparam, a.R, a.Rs, a.r0, a.dK,
+                                                                                   ExchangeArgs{});
   B200CP_LAUNCH_OK("cp4_reduce_partials_kernel");
   return B200CP_OK;
 }
@@ -434,10 +521,24 @@ int dispatch_bwd_filter_rank(const Cp4BwdFilterArgs& a, const DeviceInfo& di, cu
 }  // namespace
 
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
-                               cudaStream_t st, bool after_own_kernel) {
-  B200CP_CUDA_OK(launch_kernel(cp4_reduce_partials_kernel, dim3(ceil_div(nparam, 32)), dim3(32, 32), 0, st, after_own_kernel,
-                               partial, nparts, nparam, R, Rs, r0, dK));
+                               cudaStream_t st, bool after_own_kernel, const ExchangeArgs* exchange) {
+  if (exchange != nullptr) {
+    if (ceil_div(nparam, 32) > exchange->ctas)
+      return fail(B200CP_ERR_INVALID_ARG, "fused exchange: %d gradient entries, the context has flags for %d", nparam,
+                  exchange->ctas * 32);
+    B200CP_CUDA_OK(launch_kernel(cp4_reduce_partials_kernel<true>, dim3(ceil_div(nparam, 32)), dim3(32, 32), 0, st,
+                                 after_own_kernel, partial, nparts, nparam, R, Rs, r0, dK, *exchange));
+  } else {
+    B200CP_CUDA_OK(launch_kernel(cp4_reduce_partials_kernel<false>, dim3(ceil_div(nparam, 32)), dim3(32, 32), 0, st,
+                                 after_own_kernel, partial, nparts, nparam, R, Rs, r0, dK, ExchangeArgs{}));
+  }
   B200CP_LAUNCH_OK("cp4_reduce_partials_kernel");
+  return B200CP_OK;
+}
+
+int exchange_finish_launch(const ExchangeArgs& ex, int nparam, int R, int Rs, int r0, float* dK, cudaStream_t st) {
+  B200CP_CUDA_OK(launch_kernel(exchange_finish_kernel, dim3(ceil_div(nparam, 32)), dim3(32), 0, st, true, ex, nparam, R, Rs, r0, dK));
+  B200CP_LAUNCH_OK("exchange_finish_kernel");
   return B200CP_OK;
 }
 

@@ -591,7 +591,7 @@ size_t cp4_grad_band_workspace(const b200cp_tensor_shape& s) {
 
 // Factor gradients from the saved rank planes; *done = false: not a shape this kernel takes.
 int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, bool* done,
-                         bool after_own_kernel) {
+                         bool after_own_kernel, const ExchangeArgs* exchange) {
   *done = false;
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
@@ -629,7 +629,8 @@ int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float*
                                  (float*)a.ws));
   }
   B200CP_LAUNCH_OK("cp4_grad_band_kernel");
-  if (int rc = cp4_reduce_partials_launch((const float*)a.ws, g.tiles, g.nparam, a.R, a.Rs, a.r0, a.dK, st, true)) return rc;
+  if (int rc = cp4_reduce_partials_launch((const float*)a.ws, g.tiles, g.nparam, a.R, a.Rs, a.r0, a.dK, st, true, exchange))
+    return rc;
   *done = true;
   return B200CP_OK;
 }

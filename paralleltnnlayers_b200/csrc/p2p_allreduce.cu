@@ -25,7 +25,9 @@ namespace b200cp {
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr int kP2PThreads = 256;
+// 128 threads of at most 32 registers: 4096 registers, which is what a 480-thread row-stream CTA (or two gradient band
+// CTAs) leaves free on an SM -- the exchange has to become resident next to the next step's kernels to overlap them.
+constexpr int kP2PThreads = 128;
 constexpr int kP2PCtas = 4;   // CTAs of one exchange; each moves a quarter of the vector and has its own flags
 constexpr long long kDefaultWaitCycles = 1000000000ll;   // about half a second
 std::atomic<long long> g_wait_cycles{kDefaultWaitCycles};
@@ -51,11 +53,20 @@ struct P2PCtx {
   unsigned* d_seq;            // [kP2PCtas] next sequence number per CTA
   int* d_status;
   size_t bytes;
+  // the exchange fused into the gradient reduction (cp4_reduce_partials_kernel<true>) has its own data rows, flags
+  // and sequence numbers behind the stand-alone kernel's, so the two kinds of exchange can be mixed on one context
+  int fctas;                  // CTAs of 32 entries
+  size_t off_data2, off_flags2;
+  float** d_data2;            // [world]
+  unsigned** d_flags2;        // [world]
+  unsigned* d_seq2;           // [fctas]
+  size_t pending_n;           // floats of a posted, not yet completed pipelined exchange (0: none)
+  int pending_R, pending_Rs;
 };
 
 __host__ __device__ inline size_t flags_offset(size_t row, int world) { return 2 * (size_t)world * row * sizeof(float); }
 
-__global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(float* const* __restrict__ data,
+__global__ void __maxnreg__(32) p2p_allreduce_kernel(float* const* __restrict__ data,
                                                                     unsigned* const* __restrict__ flags, unsigned* seqs,
                                                                     int* status, int rank, int world, size_t row,
                                                                     const float* src, float* dst, size_t n,
@@ -64,6 +75,7 @@ __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(float* const
   const int cta = blockIdx.x, tid = threadIdx.x;
   __shared__ unsigned s_seq;
   __shared__ int s_missed;
+  grid_dependency_wait();   // launched as a programmatic dependent: src is the previous kernel's output
   if (tid == 0) {
     s_seq = seqs[cta] + 1;
     s_missed = 0;
@@ -79,10 +91,10 @@ __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(float* const
     float* d = data[p] + ((size_t)slot * world + rank) * row;
     for (size_t i = lo + tid; i < hi; i += kP2PThreads) d[i] = src[i];
   }
-  __threadfence_system();
   __syncthreads();
-  // 2. flag (slot, cta, rank) of every region: the CTA's stores were fenced above by the threads that made them;
-  //    the flag-writing thread fences again after the barrier and stores with release semantics
+  // 2. flag (slot, cta, rank) of every region.  The barrier orders the CTA's stores before the flag-writing thread,
+  //    whose system-scope fence and release store are cumulative over them: one fence on the critical path, not one
+  //    per thread.
   if (tid < world) {
     __threadfence_system();
     st_release_sys(flags[tid] + ((size_t)slot * kP2PCtas + cta) * kMaxWorld + rank, seq);
@@ -97,11 +109,10 @@ __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(float* const
         atomicExch(status, 1 + rank);
         break;
       }
-      __nanosleep(64);
+      __nanosleep(32);
     }
   }
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();   // the acquire loads above and this barrier order the peers' data before every thread's loads below
   // 4. the rows of the own region, in rank order; NaN where a peer's part never arrived
   const bool missed = s_missed != 0;
   const float* own = data[rank] + (size_t)slot * world * row;
@@ -114,6 +125,57 @@ __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(float* const
 }
 
 }  // namespace
+
+namespace {
+// device-side pointer tables of both kinds of exchange from the mapped peer allocations
+int upload_tables(P2PCtx* c) {
+  float* data[kMaxWorld] = {};
+  unsigned* flags[kMaxWorld] = {};
+  float* data2[kMaxWorld] = {};
+  unsigned* flags2[kMaxWorld] = {};
+  for (int p = 0; p < c->world; ++p) {
+    char* b = static_cast<char*>(c->peer[p]);
+    data[p] = reinterpret_cast<float*>(b);
+    flags[p] = reinterpret_cast<unsigned*>(b + flags_offset(c->row, c->world));
+    data2[p] = reinterpret_cast<float*>(b + c->off_data2);
+    flags2[p] = reinterpret_cast<unsigned*>(b + c->off_flags2);
+  }
+  B200CP_CUDA_OK(cudaMemcpy(c->d_data, data, sizeof(data), cudaMemcpyHostToDevice));
+  B200CP_CUDA_OK(cudaMemcpy(c->d_flags, flags, sizeof(flags), cudaMemcpyHostToDevice));
+  B200CP_CUDA_OK(cudaMemcpy(c->d_data2, data2, sizeof(data2), cudaMemcpyHostToDevice));
+  B200CP_CUDA_OK(cudaMemcpy(c->d_flags2, flags2, sizeof(flags2), cudaMemcpyHostToDevice));
+  return B200CP_OK;
+}
+}  // namespace
+
+// The arguments of the exchange fused into the gradient reduction, for a vector of n floats.
+int p2p_fused_args(void* ctx, size_t n, int mode, float* prev_out, ExchangeArgs* out) {
+  P2PCtx* c = static_cast<P2PCtx*>(ctx);
+  if (!c || !out) return fail(B200CP_ERR_INVALID_ARG, "fused exchange: null context");
+  if (n > c->max_floats) return fail(B200CP_ERR_INVALID_ARG, "fused exchange: %zu floats, room for %zu", n, c->max_floats);
+  if (c->pending_n != 0) {
+    if (mode != 1) return fail(B200CP_ERR_INVALID_ARG, "fused exchange: a pipelined exchange is pending; complete it with b200cp_p2p_flush");
+    if (!prev_out) return fail(B200CP_ERR_INVALID_ARG, "pipelined exchange: the previous step's gradients need a destination");
+    if (c->pending_n != n) return fail(B200CP_ERR_INVALID_ARG, "pipelined exchange: %zu floats after %zu", n, c->pending_n);
+  }
+  out->data = c->d_data2;
+  out->flags = c->d_flags2;
+  out->seqs = c->d_seq2;
+  out->status = c->d_status;
+  out->rank = c->rank;
+  out->world = c->world;
+  out->ctas = c->fctas;
+  out->row = c->row;
+  out->wait_cycles = g_wait_cycles.load();
+  out->mode = mode;
+  out->prev_out = c->pending_n != 0 ? prev_out : nullptr;
+  return B200CP_OK;
+}
+
+void p2p_fused_set_pending(void* ctx, size_t n, int R, int Rs) {
+  P2PCtx* c = static_cast<P2PCtx*>(ctx);
+  c->pending_n = n; c->pending_R = R; c->pending_Rs = Rs;
+}
 
 }  // namespace b200cp
 
@@ -134,6 +196,12 @@ int b200cp_p2p_init(int rank, int world, size_t max_floats, unsigned char* handl
   c->base = nullptr; c->d_data = nullptr; c->d_flags = nullptr; c->d_seq = nullptr; c->d_status = nullptr;
   for (int p = 0; p < kMaxWorld; ++p) { c->peer[p] = nullptr; c->opened[p] = false; }
   c->bytes = flags_offset(c->row, world) + 2 * (size_t)kP2PCtas * kMaxWorld * sizeof(unsigned);
+  c->fctas = (int)((c->row + 31) / 32);
+  c->off_data2 = (c->bytes + 255) / 256 * 256;
+  c->off_flags2 = c->off_data2 + flags_offset(c->row, world);
+  c->bytes = c->off_flags2 + 2 * (size_t)c->fctas * kMaxWorld * sizeof(unsigned);
+  c->d_data2 = nullptr; c->d_flags2 = nullptr; c->d_seq2 = nullptr;
+  c->pending_n = 0; c->pending_R = c->pending_Rs = 0;
   cudaIpcMemHandle_t h;
   memset(&h, 0, sizeof(h));
   static_assert(sizeof(cudaIpcMemHandle_t) == B200CP_P2P_HANDLE_BYTES, "IPC handle size");
@@ -145,6 +213,10 @@ int b200cp_p2p_init(int rank, int world, size_t max_floats, unsigned char* handl
   if (e == cudaSuccess) e = cudaMalloc(&c->d_flags, sizeof(unsigned*) * kMaxWorld);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_seq, sizeof(unsigned) * kP2PCtas);
   if (e == cudaSuccess) e = cudaMemset(c->d_seq, 0, sizeof(unsigned) * kP2PCtas);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_data2, sizeof(float*) * kMaxWorld);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_flags2, sizeof(unsigned*) * kMaxWorld);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_seq2, sizeof(unsigned) * c->fctas);
+  if (e == cudaSuccess) e = cudaMemset(c->d_seq2, 0, sizeof(unsigned) * c->fctas);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, sizeof(int));
   if (e == cudaSuccess && world > 1) e = cudaIpcGetMemHandle(&h, c->base);
@@ -169,25 +241,31 @@ int b200cp_p2p_connect(void* ctx, const unsigned char* handles) {
     B200CP_CUDA_OK(cudaIpcOpenMemHandle(&c->peer[p], h, cudaIpcMemLazyEnablePeerAccess));
     c->opened[p] = true;
   }
-  float* data[kMaxWorld] = {};
-  unsigned* flags[kMaxWorld] = {};
-  for (int p = 0; p < c->world; ++p) {
-    data[p] = static_cast<float*>(c->peer[p]);
-    flags[p] = reinterpret_cast<unsigned*>(static_cast<char*>(c->peer[p]) + flags_offset(c->row, c->world));
-  }
-  B200CP_CUDA_OK(cudaMemcpy(c->d_data, data, sizeof(data), cudaMemcpyHostToDevice));
-  B200CP_CUDA_OK(cudaMemcpy(c->d_flags, flags, sizeof(flags), cudaMemcpyHostToDevice));
-  return B200CP_OK;
+  return upload_tables(c);
 }
 
 int b200cp_p2p_allreduce(void* ctx, const float* src, float* dst, size_t n, void* stream) {
   P2PCtx* c = static_cast<P2PCtx*>(ctx);
   if (!c || !src || !dst) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_allreduce: null argument");
   if (n > c->max_floats) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_allreduce: %zu floats, room for %zu", n, c->max_floats);
-  p2p_allreduce_kernel<<<kP2PCtas, kP2PThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      c->d_data, c->d_flags, c->d_seq, c->d_status, c->rank, c->world, c->row, src, dst, n, g_wait_cycles.load());
+  B200CP_CUDA_OK(launch_kernel(p2p_allreduce_kernel, dim3(kP2PCtas), dim3(kP2PThreads), 0, static_cast<cudaStream_t>(stream),
+                               /*programmatic=*/true, c->d_data, c->d_flags, c->d_seq, c->d_status, c->rank, c->world, c->row,
+                               src, dst, n, g_wait_cycles.load()));
   B200CP_LAUNCH_OK("p2p_allreduce_kernel");
   return B200CP_OK;
+}
+
+int b200cp_p2p_flush(void* ctx, float* dK_last, void* stream) {
+  P2PCtx* c = static_cast<P2PCtx*>(ctx);
+  if (!c) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_flush: null context");
+  if (c->pending_n == 0) return B200CP_OK;
+  if (!dK_last) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_flush: the pending gradients need a destination");
+  ExchangeArgs ex{};
+  ex.data = c->d_data2; ex.flags = c->d_flags2; ex.seqs = c->d_seq2; ex.status = c->d_status;
+  ex.rank = c->rank; ex.world = c->world; ex.ctas = c->fctas; ex.row = c->row; ex.wait_cycles = g_wait_cycles.load();
+  const int n = (int)c->pending_n, R = c->pending_R, Rs = c->pending_Rs;
+  c->pending_n = 0;
+  return exchange_finish_launch(ex, n, R, Rs, 0, dK_last, static_cast<cudaStream_t>(stream));
 }
 
 void b200cp_test_set_p2p_wait_cycles(long long cycles) { g_wait_cycles.store(cycles > 0 ? cycles : kDefaultWaitCycles); }
@@ -197,19 +275,13 @@ void b200cp_test_set_p2p_wait_cycles(long long cycles) { g_wait_cycles.store(cyc
 int b200cp_test_p2p_connect_local(void* ctx, void* const* all_ctx) {
   P2PCtx* c = static_cast<P2PCtx*>(ctx);
   if (!c || !all_ctx) return fail(B200CP_ERR_INVALID_ARG, "b200cp_test_p2p_connect_local: null argument");
-  float* data[kMaxWorld] = {};
-  unsigned* flags[kMaxWorld] = {};
   for (int p = 0; p < c->world; ++p) {
     P2PCtx* o = static_cast<P2PCtx*>(all_ctx[p]);
     if (!o || o->world != c->world || o->row != c->row || o->rank != p)
       return fail(B200CP_ERR_INVALID_ARG, "b200cp_test_p2p_connect_local: context %d does not belong to this world", p);
     c->peer[p] = o->base;
-    data[p] = static_cast<float*>(o->base);
-    flags[p] = reinterpret_cast<unsigned*>(static_cast<char*>(o->base) + flags_offset(c->row, c->world));
   }
-  B200CP_CUDA_OK(cudaMemcpy(c->d_data, data, sizeof(data), cudaMemcpyHostToDevice));
-  B200CP_CUDA_OK(cudaMemcpy(c->d_flags, flags, sizeof(flags), cudaMemcpyHostToDevice));
-  return B200CP_OK;
+  return upload_tables(c);
 }
 
 // 0 when no wait has run out; synchronises the device
@@ -236,6 +308,9 @@ int b200cp_p2p_destroy(void* ctx) {
   cudaFree(c->d_data);
   cudaFree(c->d_flags);
   cudaFree(c->d_seq);
+  cudaFree(c->d_data2);
+  cudaFree(c->d_flags2);
+  cudaFree(c->d_seq2);
   cudaFree(c->d_status);
   delete c;
   return B200CP_OK;

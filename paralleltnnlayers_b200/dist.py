@@ -87,6 +87,53 @@ class P2PAllreduce:
         self._lib.check(self._lib.lib.b200cp_p2p_allreduce(self._ctx, t.data_ptr(), out.data_ptr(), t.numel(), st))
         return out
 
+    def cp4_step(self, X, dU, K0, K1, KH, KW, pad=1, flags=0):
+        """``b200cp_cp4_step_allreduce``: forward, backward-data and the factor gradients of this rank's shard with the
+        packed gradients summed over the ranks; where the step runs as its fused kernel chain the exchange is the tail
+        of the kernel that adds the partial gradients.  Returns (U, dX, dK_packed)."""
+        C = self._C
+        lib = self._lib.lib
+        N, Cc, H, W = X.shape
+        T, R = K0.shape
+        s = self._lib.TensorShape(N=N, H=H, W=W, pad=pad, T=T, C=Cc, Y=KH.shape[0], X=KW.shape[0], Rank=R)
+        U = torch.empty(N, T, H, W, device=X.device, dtype=torch.float32)
+        dX = torch.empty_like(X)
+        dK = torch.empty((T + Cc + KH.shape[0] + KW.shape[0]) * R, device=X.device, dtype=torch.float32)
+        nb = lib.b200cp_cp4_step_workspace_bytes(C.byref(s), flags)
+        ws = torch.empty(max(nb, 4) // 4, device=X.device, dtype=torch.float32)
+        st = torch.cuda.current_stream().cuda_stream
+        self._lib.check(lib.b200cp_cp4_step_allreduce(self._ctx, C.byref(s), X.data_ptr(), dU.data_ptr(), K0.data_ptr(),
+                                                      K1.data_ptr(), KH.data_ptr(), KW.data_ptr(), U.data_ptr(),
+                                                      dX.data_ptr(), dK.data_ptr(), ws.data_ptr(), nb, st, flags))
+        return U, dX, dK
+
+    def cp4_step_pipelined(self, X, dU, K0, K1, KH, KW, dK_prev, pad=1, flags=0):
+        """``b200cp_cp4_step_allreduce_pipelined``: posts this step's gradients to the peers and completes the previous
+        pipelined step's exchange into ``dK_prev`` (a float32 CUDA tensor of (T+C+Y+X)*R entries; untouched by the
+        first call).  Returns (U, dX).  ``flush(dK_last)`` completes the last step's exchange."""
+        C = self._C
+        lib = self._lib.lib
+        N, Cc, H, W = X.shape
+        T, R = K0.shape
+        s = self._lib.TensorShape(N=N, H=H, W=W, pad=pad, T=T, C=Cc, Y=KH.shape[0], X=KW.shape[0], Rank=R)
+        U = torch.empty(N, T, H, W, device=X.device, dtype=torch.float32)
+        dX = torch.empty_like(X)
+        scratch = torch.empty((T + Cc + KH.shape[0] + KW.shape[0]) * R, device=X.device, dtype=torch.float32)
+        assert dK_prev.is_cuda and dK_prev.dtype == torch.float32 and dK_prev.numel() == scratch.numel()
+        nb = lib.b200cp_cp4_step_workspace_bytes(C.byref(s), flags)
+        ws = torch.empty(max(nb, 4) // 4, device=X.device, dtype=torch.float32)
+        st = torch.cuda.current_stream().cuda_stream
+        self._lib.check(lib.b200cp_cp4_step_allreduce_pipelined(
+            self._ctx, C.byref(s), X.data_ptr(), dU.data_ptr(), K0.data_ptr(), K1.data_ptr(), KH.data_ptr(), KW.data_ptr(),
+            U.data_ptr(), dX.data_ptr(), scratch.data_ptr(), dK_prev.data_ptr(), ws.data_ptr(), nb, st, flags))
+        return U, dX
+
+    def flush(self, dK_last):
+        """Completes the last posted pipelined exchange into ``dK_last`` (nothing happens when none is pending)."""
+        st = torch.cuda.current_stream().cuda_stream
+        self._lib.check(self._lib.lib.b200cp_p2p_flush(self._ctx, dK_last.data_ptr(), st))
+        return dK_last
+
     def status(self):
         """Synchronises the device; raises if a wait for a peer's flag ran out."""
         self._lib.check(self._lib.lib.b200cp_p2p_status(self._ctx))

@@ -43,6 +43,42 @@ def test_single_rank_exchange_and_graph_replay():
     ar.close()
 
 
+def test_single_rank_step_with_the_exchange_fused_into_the_gradient_reduction():
+    """``b200cp_cp4_step_allreduce`` with one rank: the reduction kernel's exchange tail runs against itself (stores,
+    flags, wait, sum, sequence numbers over repeated calls and graph replays) and must give the plain step's bits;
+    a shape outside the fused kernel chain takes the stand-alone exchange kernel after the step."""
+    import paralleltnnlayers_b200 as P
+    from oracle import cp_oracle as O
+    from paralleltnnlayers_b200.dist import P2PAllreduce
+    from tests.gpu_util import dev
+    for shape in ((3, 64, 64, 56, 56, 16), (2, 16, 24, 9, 24, 5), (2, 12, 20, 7, 10, 3)):    # the last: not a fused shape
+        N, Cc, T, H, W, R = shape
+        X, K0, K1, KH, KW, dU = O.make_cp4_inputs(900 + H, N, Cc, T, H, W, 3, 3, R, factor_std=0.1)
+        t = dev(X, K0, K1, KH, KW, dU)
+        ar = P2PAllreduce((T + Cc + 6) * R)
+        ref = P.cp4_conv2d_step(t[0], t[5], *t[1:5], 1)
+        for _ in range(3):
+            got = ar.cp4_step(t[0], t[5], *t[1:5], 1)
+            for a, b in zip(got, ref):
+                assert torch.equal(a, b)
+        # pipelined: the gradients of a call arrive with the next call, the last ones with flush()
+        ref2 = P.cp4_conv2d_step(t[0], 2 * t[5], *t[1:5], 1)
+        prev = [torch.full_like(ref[2], 7.0) for _ in range(3)]
+        U0, dX0 = ar.cp4_step_pipelined(t[0], t[5], *t[1:5], prev[0], 1)
+        U1, dX1 = ar.cp4_step_pipelined(t[0], 2 * t[5], *t[1:5], prev[1], 1)
+        with pytest.raises(Exception):
+            ar.cp4_step(t[0], t[5], *t[1:5], 1)            # an exchange is pending: the unpipelined call is refused
+        ar.flush(prev[2])
+        ar.flush(prev[2])                                   # nothing pending: a no-op
+        assert torch.equal(U0, ref[0]) and torch.equal(dX0, ref[1]) and torch.equal(dX1, ref2[1])
+        assert torch.all(prev[0] == 7.0)                    # the first call had nothing to complete
+        assert torch.equal(prev[1], ref[2]) and torch.equal(prev[2], ref2[2])
+        got = ar.cp4_step(t[0], t[5], *t[1:5], 1)          # and the context is free again
+        assert torch.equal(got[2], ref[2])
+        ar.status()
+        ar.close()
+
+
 def test_a_wait_that_runs_out_is_reported_and_the_exchange_recovers():
     """Two ranks of one process on one GPU, driven one after the other with a wait limit of about a millisecond.
     The rank launched first stores its vector and raises its flags, finds its peer's flag missing, gives up within
@@ -151,10 +187,38 @@ def _worker(rank, world, port, q):
         every = [torch.empty_like(got) for _ in range(world)]
         dist.all_gather(every, got)
         ok = ok and all(torch.equal(e, every[0]) for e in every)     # bitwise the same on every rank
+    # the exchange fused into the gradient reduction of a training step against the plain step + NCCL
+    import paralleltnnlayers_b200 as P
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    X = torch.rand(4, 64, 56, 56, device="cuda", generator=g) * 2 - 1
+    dU = torch.randn(4, 64, 56, 56, device="cuda", generator=g)
+    f = torch.Generator(device="cuda").manual_seed(5)                  # the factors are the same on every rank
+    K0, K1 = torch.randn(64, 16, device="cuda", generator=f) / 24, torch.randn(64, 16, device="cuda", generator=f) / 24
+    KH, KW = torch.randn(3, 16, device="cuda", generator=f) / 3, torch.randn(3, 16, device="cuda", generator=f) / 3
+    ar2 = P2PAllreduce((64 + 64 + 6) * 16)
+    for _ in range(5):
+        U, dX, dK = ar2.cp4_step(X, dU, K0, K1, KH, KW, 1)
+        U1, dX1, dK1 = P.cp4_conv2d_step(X, dU, K0, K1, KH, KW, 1)
+        dist.all_reduce(dK1)
+        ok = ok and torch.equal(U, U1) and torch.equal(dX, dX1)
+        ok = ok and torch.allclose(dK, dK1, rtol=1e-5, atol=1e-6 * float(dK1.abs().max()))
+        every = [torch.empty_like(dK) for _ in range(world)]
+        dist.all_gather(every, dK)
+        ok = ok and all(torch.equal(e, every[0]) for e in every)
+    prev = [torch.zeros_like(dK1) for _ in range(4)]
+    for k in range(3):
+        ar2.cp4_step_pipelined(X, (k + 1) * dU, K0, K1, KH, KW, prev[k], 1)
+    ar2.flush(prev[3])
+    for k in range(3):
+        want = P.cp4_conv2d_step(X, (k + 1) * dU, K0, K1, KH, KW, 1)[2]
+        dist.all_reduce(want)
+        ok = ok and torch.allclose(prev[k + 1], want, rtol=1e-5, atol=1e-6 * float(want.abs().max()))
+    ar2.status()
     ar.status()
     q.put((rank, bool(ok)))
     torch.cuda.synchronize()
     dist.barrier()
+    ar2.close()
     ar.close()
     dist.destroy_process_group()
 
