@@ -251,7 +251,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the step times of the other configurations")
     ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"],
                     help="gradient allreduce of the multi-GPU step: the library's peer-memory kernel, or NCCL")
-    ap.add_argument("--exchange", default="overlap", choices=["pipelined", "fused", "inline", "overlap"],
+    ap.add_argument("--exchange", default="fused", choices=["pipelined", "fused", "inline", "overlap"],
                     help="N > 1: the allreduce of the factor gradients as the tail of the step's gradient reduction "
                          "kernel, completed by the next step's (pipelined: b200cp_cp4_step_allreduce_pipelined, the "
                          "last one by b200cp_p2p_flush inside the timed region) or by the same kernel (fused: "

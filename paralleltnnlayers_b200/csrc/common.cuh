@@ -141,12 +141,13 @@ size_t cp4_bwd_filter_saved_workspace(const b200cp_tensor_shape& s);
 int cp4_bwd_filter_saved_launch(const Cp4BwdFilterArgs& a, const float* P, const float* Q, cudaStream_t st, int part = 0);
 // dK[row*Rs + r0 + r] = sum over parts of partial[part][row*R + r], in a fixed order
 // The peer-memory exchange of a data-parallel step, as the tail of the kernel that sums the partial gradients: every
-// CTA of that kernel owns 32 gradient entries, stores its sums into every rank's exchange region (plain peer stores),
-// raises its flag there, waits (bounded) for the other ranks' flags of the same CTA and adds the rows in rank order.
-// Filled by p2p_fused_args() from a context of b200cp_p2p_init.
+// CTA of that kernel owns 32 gradient entries, stores each of its sums together with the exchange's sequence number
+// as one 8-byte word into every rank's exchange region (plain peer stores), then reads the words of all ranks from
+// its own region, spinning (bounded) on a word until it carries the sequence number, and adds them in rank order.
+// An aligned 8-byte store is one transaction, so the value and its "arrived" mark cannot be seen apart: no fence and
+// no separate flag.  Filled by p2p_fused_args() from a context of b200cp_p2p_init.
 struct ExchangeArgs {
-  float* const* data;      // [world] every rank's data region: [2 slots][world][row]
-  unsigned* const* flags;  // [world] every rank's flags: [2 slots][ctas][16]
+  unsigned long long* const* data;   // [world] every rank's region: [2 slots][world][row] words {value, sequence}
   unsigned* seqs;          // [ctas] sequence number of this rank's last exchange, per CTA
   int* status;
   int rank, world, ctas;
@@ -155,6 +156,16 @@ struct ExchangeArgs {
   int mode;                // 0: post and complete in the same kernel; 1: post, and complete the previous exchange
   float* prev_out;         // mode 1: where the previous exchange's sums go (null: nothing is pending)
 };
+// one word of an exchange region
+__device__ __forceinline__ void exchange_store(unsigned long long* p, float v, unsigned seq) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+__device__ __forceinline__ bool exchange_load(const unsigned long long* p, unsigned seq, float* v) {
+  unsigned a, b;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "l"(p) : "memory");
+  *v = __uint_as_float(a);
+  return b == seq;
+}
 // mode 1 keeps the posted exchange pending in the context until the next mode-1 call or p2p_fused_flush completes it
 int p2p_fused_args(void* ctx, size_t n, int mode, float* prev_out, ExchangeArgs* out);
 void p2p_fused_set_pending(void* ctx, size_t n, int R, int Rs);

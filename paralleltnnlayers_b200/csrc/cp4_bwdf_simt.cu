@@ -339,59 +339,45 @@ __global__ void __launch_bounds__(256) cp4_bwd_filter_kernel(const GeomF gf, con
   TRACE(5);
 }
 
-__device__ __forceinline__ void ex_st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ex_ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// The three parts of one CTA's exchange (a warp; `seq` is the exchange's sequence number, its parity the slot).
-__device__ __forceinline__ void exchange_post(const ExchangeArgs& ex, int cta, int lane, bool live, int j, float v, unsigned seq) {
+// The two parts of one warp's exchange (`seq` is the exchange's sequence number, its parity the slot).
+__device__ __forceinline__ void exchange_post(const ExchangeArgs& ex, bool live, int j, float v, unsigned seq) {
   const int slot = (int)(seq & 1u);
   if (live)
-    for (int p = 0; p < ex.world; ++p) ex.data[p][((size_t)slot * ex.world + ex.rank) * ex.row + j] = v;
-  __syncwarp();   // orders the lanes' stores before the flag lanes, whose fence and release store are cumulative over them
-  if (lane < ex.world) {
-    __threadfence_system();
-    ex_st_release_sys(ex.flags[lane] + ((size_t)slot * ex.ctas + cta) * 16 + ex.rank, seq);
-  }
+    for (int p = 0; p < ex.world; ++p) exchange_store(ex.data[p] + ((size_t)slot * ex.world + ex.rank) * ex.row + j, v, seq);
 }
-__device__ __forceinline__ bool exchange_wait(const ExchangeArgs& ex, int cta, int lane, unsigned seq) {
+// the sum over the ranks of entry j, in rank order (the same bits on every rank); NaN for the whole warp when a
+// rank's word did not arrive within the limit
+__device__ __forceinline__ float exchange_gather(const ExchangeArgs& ex, bool live, int j, unsigned seq) {
   const int slot = (int)(seq & 1u);
   bool missed = false;
-  if (lane < ex.world) {
-    const unsigned* f = ex.flags[ex.rank] + ((size_t)slot * ex.ctas + cta) * 16 + lane;
+  float t = 0.f;
+  if (live) {
+    const unsigned long long* own = ex.data[ex.rank] + (size_t)slot * ex.world * ex.row + j;
     const long long t0 = clock64();
-    while ((int)(ex_ld_acquire_sys(f) - seq) < 0) {
-      if (clock64() - t0 > ex.wait_cycles) {   // give up, never hang
-        missed = true;
-        atomicExch(ex.status, 1 + ex.rank);
-        break;
+    for (int p = 0; p < ex.world && !missed; ++p) {
+      float v;
+      while (!exchange_load(own + (size_t)p * ex.row, seq, &v)) {
+        if (clock64() - t0 > ex.wait_cycles) {   // give up, never hang
+          missed = true;
+          atomicExch(ex.status, 1 + ex.rank);
+          break;
+        }
+        __nanosleep(20);
       }
-      __nanosleep(32);
+      t += v;
     }
   }
   missed = __any_sync(0xffffffffu, missed);
-  __syncwarp();   // the acquire loads of the flag lanes are ordered before every lane's loads that follow
-  return missed;
-}
-__device__ __forceinline__ float exchange_sum(const ExchangeArgs& ex, int j, unsigned seq) {
-  const int slot = (int)(seq & 1u);
-  const float* own = ex.data[ex.rank] + (size_t)slot * ex.world * ex.row + j;
-  float t = 0.f;
-  for (int p = 0; p < ex.world; ++p) t += __ldcg(own + (size_t)p * ex.row);   // rank order: the same bits on every rank
-  return t;
+  return missed ? __int_as_float(0x7fc00000) : t;
 }
 
 // out[j] = sum over CTAs of partial[cta][j].  32 parameters x 32 slices per block: slice s adds the
 // partials of its contiguous CTA range in order, then the slices are added in order (reproducible).
 // EXCHANGE: the sums then go through the peer-memory exchange of a data-parallel step in the same kernel -- the first
-// warp of every CTA stores its 32 sums into every rank's region, raises the CTA's flag there (one system-scope fence
-// and a release store by the lanes that write flags), waits for the peers' flags of the same CTA (bounded; a wait
-// that runs out gives NaN and a status word) and adds the rows in rank order, so every rank gets the same bits.
+// warp of every CTA stores its 32 sums, each with the sequence number in one 8-byte word, into every rank's region,
+// reads all ranks' words of the same entries from its own region (spinning, bounded, until they carry the sequence
+// number; a wait that runs out gives NaN and a status word) and adds them in rank order, so every rank gets the
+// same bits.
 // In pipelined mode (ex.mode == 1) the kernel only posts its sums and completes the *previous* step's exchange, whose
 // flags have long arrived: the exchange latency then costs the step nothing.
 template <bool EXCHANGE>
@@ -427,19 +413,20 @@ __global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* 
     if (j < nparam) *out = s;
     return;
   }
-  // ---- exchange (one warp; lane = entry of the CTA's 32, and lanes below `world` also own a peer's flag) -----------
+  // ---- exchange (one warp; lane = entry of the CTA's 32) -----------------------------------------------------------
   const int lane = threadIdx.x, cta = blockIdx.x;
+  const bool live = j < nparam;
   const unsigned last = ex.seqs[cta];
   if (ex.mode == 1 && ex.prev_out != nullptr) {
     // pipelined: the previous step's exchange is completed here, a whole step after it was posted
-    const bool missed = exchange_wait(ex, cta, lane, last);
-    if (j < nparam) ex.prev_out[(size_t)row * Rs + r0 + r] = missed ? __int_as_float(0x7fc00000) : exchange_sum(ex, j, last);
+    const float t = exchange_gather(ex, live, j, last);
+    if (live) ex.prev_out[(size_t)row * Rs + r0 + r] = t;
   }
   const unsigned seq = last + 1;
-  exchange_post(ex, cta, lane, j < nparam, j, s, seq);
+  exchange_post(ex, live, j, s, seq);
   if (ex.mode == 0) {
-    const bool missed = exchange_wait(ex, cta, lane, seq);
-    if (j < nparam) *out = missed ? __int_as_float(0x7fc00000) : exchange_sum(ex, j, seq);
+    const float t = exchange_gather(ex, live, j, seq);
+    if (live) *out = t;
   }
   __syncwarp();
   if (lane == 0) ex.seqs[cta] = seq;   // the sequence advances either way: the next exchange lines up with the peers' again
@@ -450,11 +437,10 @@ __global__ void __launch_bounds__(32) exchange_finish_kernel(const ExchangeArgs 
                                                              float* __restrict__ dK) {
   grid_dependency_wait();
   const int lane = threadIdx.x, cta = blockIdx.x, j = cta * 32 + lane;
-  const unsigned last = ex.seqs[cta];
-  const bool missed = exchange_wait(ex, cta, lane, last);
+  const float t = exchange_gather(ex, j < nparam, j, ex.seqs[cta]);
   if (j < nparam) {
     const int row = j / R, r = j - row * R;
-    dK[(size_t)row * Rs + r0 + r] = missed ? __int_as_float(0x7fc00000) : exchange_sum(ex, j, last);
+    dK[(size_t)row * Rs + r0 + r] = t;
   }
 }
 

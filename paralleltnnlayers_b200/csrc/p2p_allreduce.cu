@@ -1,19 +1,24 @@
 // One-shot allreduce of the packed factor gradients over peer memory (NVLink / NVSwitch), one process per GPU.
 //
 // The buffer is a few KB ((T + C + FH + FW) * R floats), so the collective is pure latency.  Every rank owns an
-// exchange region [2 slots][world][max floats] plus flags [2 slots][world] in its own memory, exported to the peers
-// through CUDA IPC.  One launch per step:
-//   1. the rank stores its vector into slot s, row `rank`, of EVERY rank's region (plain peer stores),
-//   2. fences and raises flag (s, rank) in every region to the step's sequence number,
-//   3. waits until all `world` flags of slot s in its OWN region carry that number (a bounded wait: about half a
-//      second, then a status word is set, the result is filled with NaN -- a missed exchange cannot pass for a sum --
-//      and the kernel leaves; b200cp_p2p_status reports it),
-//   4. adds the `world` rows of its own region in rank order, so every rank gets bitwise the same sums.
-// Flags are written with st.release.sys after a system-scope fence and polled with ld.acquire.sys.
+// exchange region [2 slots][world][max floats] of 8-byte words in its own memory, exported to the peers through CUDA
+// IPC.  A word holds a value and the sequence number of the exchange it belongs to; it is written with one aligned
+// 8-byte store, which is one transaction, so a reader sees either the old word or the new one, never a new value
+// without its number.  One launch per step:
+//   1. the rank stores its vector, every value with the step's sequence number, into slot s, row `rank`, of EVERY
+//      rank's region (plain peer stores; no fence, no flag),
+//   2. reads the `world` rows of its OWN region, spinning on a word until it carries the number (a bounded wait: about
+//      half a second, then a status word is set, the result is filled with NaN -- a missed exchange cannot pass for
+//      a sum -- and the kernel leaves; b200cp_p2p_status reports it), and adds them in rank order, so every rank
+//      gets bitwise the same sums.
+// (An earlier form wrote the data, then a system-scope fence and a release store of a flag; on one GPU exchanging
+// with itself the fence alone cost 9 us per step.)
 // Two slots alternate.  A rank that writes slot s for step q has finished step q - 1, for which it needed every
-// peer's flag of step q - 1; a peer raises that flag in its launch q - 1, which runs after its launch q - 2 has read
-// slot s.  So a slot is never overwritten while a peer still reads it.  The sequence number lives in device memory and is advanced by the kernel, so a captured CUDA graph can
-// be replayed.  No NCCL kernel, no multicast, no peer loads: a CTA of 256 threads that fits next to the compute kernels.
+// peer's words of step q - 1; a peer writes those in its launch q - 1, which runs after its launch q - 2 has read
+// slot s.  So a slot is never overwritten while a peer still reads it.  The sequence number lives in device memory
+// and is advanced by the kernel, so a captured CUDA graph can be replayed.  No NCCL kernel, no multicast, no peer
+// loads.  The same exchange also exists as the tail of the kernel that adds the partial factor gradients of a
+// training step (cp4_reduce_partials_kernel<true>), with a region and sequence numbers of its own.
 #include <atomic>
 #include <cstring>
 
@@ -28,18 +33,9 @@ constexpr int kMaxWorld = 16;
 // 128 threads of at most 32 registers: 4096 registers, which is what a 480-thread row-stream CTA (or two gradient band
 // CTAs) leaves free on an SM -- the exchange has to become resident next to the next step's kernels to overlap them.
 constexpr int kP2PThreads = 128;
-constexpr int kP2PCtas = 4;   // CTAs of one exchange; each moves a quarter of the vector and has its own flags
+constexpr int kP2PCtas = 4;   // CTAs of one exchange; each moves a quarter of the vector
 constexpr long long kDefaultWaitCycles = 1000000000ll;   // about half a second
 std::atomic<long long> g_wait_cycles{kDefaultWaitCycles};
-
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 struct P2PCtx {
   int rank, world, device;
@@ -48,30 +44,30 @@ struct P2PCtx {
   void* peer[kMaxWorld];      // mapped allocations (peer[rank] == base)
   bool opened[kMaxWorld];
   // device-side table
-  float** d_data;             // [world] data pointers
-  unsigned** d_flags;         // [world] flag pointers
+  unsigned long long** d_data;   // [world] region pointers of the stand-alone exchange kernel
   unsigned* d_seq;            // [kP2PCtas] next sequence number per CTA
   int* d_status;
   size_t bytes;
-  // the exchange fused into the gradient reduction (cp4_reduce_partials_kernel<true>) has its own data rows, flags
-  // and sequence numbers behind the stand-alone kernel's, so the two kinds of exchange can be mixed on one context
+  // the exchange fused into the gradient reduction (cp4_reduce_partials_kernel<true>) has its own region and
+  // sequence numbers behind the stand-alone kernel's, so the two kinds of exchange can be mixed on one context
   int fctas;                  // CTAs of 32 entries
-  size_t off_data2, off_flags2;
-  float** d_data2;            // [world]
-  unsigned** d_flags2;        // [world]
+  size_t off_data2;
+  unsigned long long** d_data2;   // [world]
   unsigned* d_seq2;           // [fctas]
   size_t pending_n;           // floats of a posted, not yet completed pipelined exchange (0: none)
   int pending_R, pending_Rs;
 };
 
-__host__ __device__ inline size_t flags_offset(size_t row, int world) { return 2 * (size_t)world * row * sizeof(float); }
+// bytes of one exchange region: [2 slots][world][row] words of 8 bytes {value, sequence number}
+inline size_t region_bytes(size_t row, int world) { return 2 * (size_t)world * row * sizeof(unsigned long long); }
 
-__global__ void __maxnreg__(32) p2p_allreduce_kernel(float* const* __restrict__ data,
-                                                                    unsigned* const* __restrict__ flags, unsigned* seqs,
-                                                                    int* status, int rank, int world, size_t row,
-                                                                    const float* src, float* dst, size_t n,
-                                                                    long long wait_cycles) {
-  // (src and dst may be the same buffer: a CTA reads and writes only its own part of the vector)
+// Every value travels with the exchange's sequence number in one aligned 8-byte word (one transaction: the value and
+// its "arrived" mark cannot be seen apart), so the exchange needs no fence and no separate flag: a rank stores its
+// words into every rank's region and spins, bounded, on the words of its own region until they carry the number.
+__global__ void __maxnreg__(32) p2p_allreduce_kernel(unsigned long long* const* __restrict__ data, unsigned* seqs,
+                                                     int* status, int rank, int world, size_t row, const float* src,
+                                                     float* dst, size_t n, long long wait_cycles) {
+  // (src and dst may be the same buffer: a thread reads the entries it later writes)
   const int cta = blockIdx.x, tid = threadIdx.x;
   __shared__ unsigned s_seq;
   __shared__ int s_missed;
@@ -87,40 +83,34 @@ __global__ void __maxnreg__(32) p2p_allreduce_kernel(float* const* __restrict__ 
   const size_t per = (n + kP2PCtas - 1) / kP2PCtas;
   const size_t lo = min(n, (size_t)cta * per), hi = min(n, lo + per);
   // 1. the own part into every rank's region
-  for (int p = 0; p < world; ++p) {
-    float* d = data[p] + ((size_t)slot * world + rank) * row;
-    for (size_t i = lo + tid; i < hi; i += kP2PThreads) d[i] = src[i];
+  for (size_t i = lo + tid; i < hi; i += kP2PThreads) {
+    const float v = src[i];
+    for (int p = 0; p < world; ++p) exchange_store(data[p] + ((size_t)slot * world + rank) * row + i, v, seq);
   }
-  __syncthreads();
-  // 2. flag (slot, cta, rank) of every region.  The barrier orders the CTA's stores before the flag-writing thread,
-  //    whose system-scope fence and release store are cumulative over them: one fence on the critical path, not one
-  //    per thread.
-  if (tid < world) {
-    __threadfence_system();
-    st_release_sys(flags[tid] + ((size_t)slot * kP2PCtas + cta) * kMaxWorld + rank, seq);
-  }
-  // 3. all flags of the own region
-  if (tid < world) {
-    const unsigned* f = flags[rank] + ((size_t)slot * kP2PCtas + cta) * kMaxWorld + tid;
-    const long long t0 = clock64();
-    while ((int)(ld_acquire_sys(f) - seq) < 0) {
-      if (clock64() - t0 > wait_cycles) {   // give up, never hang
-        s_missed = 1;
-        atomicExch(status, 1 + rank);
-        break;
-      }
-      __nanosleep(32);
-    }
-  }
-  __syncthreads();   // the acquire loads above and this barrier order the peers' data before every thread's loads below
-  // 4. the rows of the own region, in rank order; NaN where a peer's part never arrived
-  const bool missed = s_missed != 0;
-  const float* own = data[rank] + (size_t)slot * world * row;
+  // 2. the words of the own region, added in rank order
+  const unsigned long long* own = data[rank] + (size_t)slot * world * row;
+  const long long t0 = clock64();
+  volatile int* missed = &s_missed;
   for (size_t i = lo + tid; i < hi; i += kP2PThreads) {
     float s = 0.f;
-    for (int p = 0; p < world; ++p) s += __ldcg(own + (size_t)p * row + i);
-    dst[i] = missed ? __int_as_float(0x7fc00000) : s;
+    for (int p = 0; p < world; ++p) {
+      float v = 0.f;
+      while (!*missed && !exchange_load(own + (size_t)p * row + i, seq, &v)) {
+        if (clock64() - t0 > wait_cycles) {   // give up, never hang
+          *missed = 1;
+          atomicExch(status, 1 + rank);
+          break;
+        }
+        __nanosleep(20);
+      }
+      s += v;
+    }
+    dst[i] = s;
   }
+  __syncthreads();
+  // a missed exchange cannot pass for a sum: NaN for the CTA's whole part
+  if (s_missed)
+    for (size_t i = lo + tid; i < hi; i += kP2PThreads) dst[i] = __int_as_float(0x7fc00000);
   if (tid == 0) seqs[cta] = seq;   // the sequence advances either way: the next exchange lines up with the peers' again
 }
 
@@ -129,21 +119,15 @@ __global__ void __maxnreg__(32) p2p_allreduce_kernel(float* const* __restrict__ 
 namespace {
 // device-side pointer tables of both kinds of exchange from the mapped peer allocations
 int upload_tables(P2PCtx* c) {
-  float* data[kMaxWorld] = {};
-  unsigned* flags[kMaxWorld] = {};
-  float* data2[kMaxWorld] = {};
-  unsigned* flags2[kMaxWorld] = {};
+  unsigned long long* data[kMaxWorld] = {};
+  unsigned long long* data2[kMaxWorld] = {};
   for (int p = 0; p < c->world; ++p) {
     char* b = static_cast<char*>(c->peer[p]);
-    data[p] = reinterpret_cast<float*>(b);
-    flags[p] = reinterpret_cast<unsigned*>(b + flags_offset(c->row, c->world));
-    data2[p] = reinterpret_cast<float*>(b + c->off_data2);
-    flags2[p] = reinterpret_cast<unsigned*>(b + c->off_flags2);
+    data[p] = reinterpret_cast<unsigned long long*>(b);
+    data2[p] = reinterpret_cast<unsigned long long*>(b + c->off_data2);
   }
   B200CP_CUDA_OK(cudaMemcpy(c->d_data, data, sizeof(data), cudaMemcpyHostToDevice));
-  B200CP_CUDA_OK(cudaMemcpy(c->d_flags, flags, sizeof(flags), cudaMemcpyHostToDevice));
   B200CP_CUDA_OK(cudaMemcpy(c->d_data2, data2, sizeof(data2), cudaMemcpyHostToDevice));
-  B200CP_CUDA_OK(cudaMemcpy(c->d_flags2, flags2, sizeof(flags2), cudaMemcpyHostToDevice));
   return B200CP_OK;
 }
 }  // namespace
@@ -159,7 +143,6 @@ int p2p_fused_args(void* ctx, size_t n, int mode, float* prev_out, ExchangeArgs*
     if (c->pending_n != n) return fail(B200CP_ERR_INVALID_ARG, "pipelined exchange: %zu floats after %zu", n, c->pending_n);
   }
   out->data = c->d_data2;
-  out->flags = c->d_flags2;
   out->seqs = c->d_seq2;
   out->status = c->d_status;
   out->rank = c->rank;
@@ -193,14 +176,12 @@ int b200cp_p2p_init(int rank, int world, size_t max_floats, unsigned char* handl
   P2PCtx* c = new P2PCtx();
   c->rank = rank; c->world = world; c->max_floats = max_floats;
   c->row = (max_floats + 3) / 4 * 4;
-  c->base = nullptr; c->d_data = nullptr; c->d_flags = nullptr; c->d_seq = nullptr; c->d_status = nullptr;
+  c->base = nullptr; c->d_data = nullptr; c->d_seq = nullptr; c->d_status = nullptr;
   for (int p = 0; p < kMaxWorld; ++p) { c->peer[p] = nullptr; c->opened[p] = false; }
-  c->bytes = flags_offset(c->row, world) + 2 * (size_t)kP2PCtas * kMaxWorld * sizeof(unsigned);
   c->fctas = (int)((c->row + 31) / 32);
-  c->off_data2 = (c->bytes + 255) / 256 * 256;
-  c->off_flags2 = c->off_data2 + flags_offset(c->row, world);
-  c->bytes = c->off_flags2 + 2 * (size_t)c->fctas * kMaxWorld * sizeof(unsigned);
-  c->d_data2 = nullptr; c->d_flags2 = nullptr; c->d_seq2 = nullptr;
+  c->off_data2 = (region_bytes(c->row, world) + 255) / 256 * 256;
+  c->bytes = c->off_data2 + region_bytes(c->row, world);
+  c->d_data2 = nullptr; c->d_seq2 = nullptr;
   c->pending_n = 0; c->pending_R = c->pending_Rs = 0;
   cudaIpcMemHandle_t h;
   memset(&h, 0, sizeof(h));
@@ -209,12 +190,10 @@ int b200cp_p2p_init(int rank, int world, size_t max_floats, unsigned char* handl
   cudaError_t e = cudaGetDevice(&c->device);
   if (e == cudaSuccess) e = cudaMalloc(&c->base, c->bytes);
   if (e == cudaSuccess) e = cudaMemset(c->base, 0, c->bytes);
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_data, sizeof(float*) * kMaxWorld);
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_flags, sizeof(unsigned*) * kMaxWorld);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_data, sizeof(unsigned long long*) * kMaxWorld);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_seq, sizeof(unsigned) * kP2PCtas);
   if (e == cudaSuccess) e = cudaMemset(c->d_seq, 0, sizeof(unsigned) * kP2PCtas);
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_data2, sizeof(float*) * kMaxWorld);
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_flags2, sizeof(unsigned*) * kMaxWorld);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_data2, sizeof(unsigned long long*) * kMaxWorld);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_seq2, sizeof(unsigned) * c->fctas);
   if (e == cudaSuccess) e = cudaMemset(c->d_seq2, 0, sizeof(unsigned) * c->fctas);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_status, sizeof(int));
@@ -249,8 +228,8 @@ int b200cp_p2p_allreduce(void* ctx, const float* src, float* dst, size_t n, void
   if (!c || !src || !dst) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_allreduce: null argument");
   if (n > c->max_floats) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_allreduce: %zu floats, room for %zu", n, c->max_floats);
   B200CP_CUDA_OK(launch_kernel(p2p_allreduce_kernel, dim3(kP2PCtas), dim3(kP2PThreads), 0, static_cast<cudaStream_t>(stream),
-                               /*programmatic=*/true, c->d_data, c->d_flags, c->d_seq, c->d_status, c->rank, c->world, c->row,
-                               src, dst, n, g_wait_cycles.load()));
+                               /*programmatic=*/true, c->d_data, c->d_seq, c->d_status, c->rank, c->world, c->row, src, dst, n,
+                               g_wait_cycles.load()));
   B200CP_LAUNCH_OK("p2p_allreduce_kernel");
   return B200CP_OK;
 }
@@ -261,7 +240,7 @@ int b200cp_p2p_flush(void* ctx, float* dK_last, void* stream) {
   if (c->pending_n == 0) return B200CP_OK;
   if (!dK_last) return fail(B200CP_ERR_INVALID_ARG, "b200cp_p2p_flush: the pending gradients need a destination");
   ExchangeArgs ex{};
-  ex.data = c->d_data2; ex.flags = c->d_flags2; ex.seqs = c->d_seq2; ex.status = c->d_status;
+  ex.data = c->d_data2; ex.seqs = c->d_seq2; ex.status = c->d_status;
   ex.rank = c->rank; ex.world = c->world; ex.ctas = c->fctas; ex.row = c->row; ex.wait_cycles = g_wait_cycles.load();
   const int n = (int)c->pending_n, R = c->pending_R, Rs = c->pending_Rs;
   c->pending_n = 0;
@@ -306,10 +285,8 @@ int b200cp_p2p_destroy(void* ctx) {
     if (c->opened[p]) cudaIpcCloseMemHandle(c->peer[p]);
   cudaFree(c->base);
   cudaFree(c->d_data);
-  cudaFree(c->d_flags);
   cudaFree(c->d_seq);
   cudaFree(c->d_data2);
-  cudaFree(c->d_flags2);
   cudaFree(c->d_seq2);
   cudaFree(c->d_status);
   delete c;
