@@ -179,10 +179,23 @@ int b200cp_cp4_bwd_data(const b200cp_tensor_shape* s, const float* dU, const flo
   return run_conv(s, dU, K0, K1, KH, KW, dX, static_cast<cudaStream_t>(stream), flags, true);
 }
 
+// 3x3 / pad 1 / at most 16 ranks: the stand-alone backward-filter can write the two rank planes with plane-only
+// convolutions and form the gradients from them with the step's band kernel; that needs room for the planes
+static size_t bwd_filter_plane_bytes(const b200cp_tensor_shape* s) {
+  return align_up((size_t)s->N * s->Rank * s->H * s->W * sizeof(float), 256);
+}
+static bool bwd_filter_by_planes(const b200cp_tensor_shape* s, int flags) {
+  const int path = path_of(flags);
+  return s->Y == 3 && s->X == 3 && s->pad == 1 && s->Rank <= 16 &&
+         (path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma));
+}
+
 size_t b200cp_cp4_bwd_filter_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
   if (check_shape(s, "b200cp_cp4_bwd_filter_workspace_bytes")) return 0;
   if (path_of(flags) == B200CP_PATH_SIMT) return cp4_bwd_filter_simt_workspace(*s);
-  return std::max(cp4_bwd_filter_simt_workspace(*s), cp4_bwd_filter_mma_workspace(*s));
+  size_t need = std::max(cp4_bwd_filter_simt_workspace(*s), cp4_bwd_filter_mma_workspace(*s));
+  if (bwd_filter_by_planes(s, flags)) need = std::max(need, 2 * bwd_filter_plane_bytes(s) + cp4_grad_band_workspace(*s));
+  return need;
 }
 
 int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
@@ -202,6 +215,31 @@ int b200cp_cp4_bwd_filter(const b200cp_tensor_shape* s, const float* X, const fl
   a.Rs = s->Rank;
   a.X = X; a.dU = dU; a.K0 = K0; a.K1 = K1; a.KH = KH; a.KW = KW; a.dK = dK_packed;
   a.ws = workspace; a.ws_bytes = workspace_bytes;
+  if (bwd_filter_by_planes(s, flags)) {
+    // rank planes by two plane-only convolutions in one launch (they read X and dU once), then the gradient band
+    // kernel of the training step; taken where the workspace has room for the planes and both kernels take the shape
+    const size_t plane = bwd_filter_plane_bytes(s);
+    const size_t gws = cp4_grad_band_workspace(*s);
+    a.r0 = 0;
+    a.R = (int)s->Rank;
+    if (gws > 0 && workspace_bytes >= 2 * plane + gws && cp4_grad_band_supported(a)) {
+      float* P = static_cast<float*>(workspace);
+      float* Q = reinterpret_cast<float*>(static_cast<char*>(workspace) + plane);
+      cudaStream_t st = static_cast<cudaStream_t>(stream);
+      Cp4Args cv[2] = {conv_args(s, X, K0, K1, KH, KW, nullptr, false, nullptr, P),
+                       conv_args(s, dU, K0, K1, KH, KW, nullptr, true, nullptr, Q)};
+      bool both = false;
+      if (int rc = cp4_stream_launch(cv, 2, st, &both)) return rc;
+      if (both) {
+        Cp4BwdFilterArgs b = a;
+        b.ws = static_cast<char*>(workspace) + 2 * plane;
+        b.ws_bytes = workspace_bytes - 2 * plane;
+        bool done = false;
+        if (int rc = cp4_grad_band_launch(b, P, Q, st, &done, /*after_own_kernel=*/true)) return rc;
+        if (done) return B200CP_OK;
+      }
+    }
+  }
   for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
     a.r0 = r0;
     a.R = std::min(64u, s->Rank - r0);

@@ -16,7 +16,9 @@
 //                    contiguous bytes of one channel row.
 //
 // Every product is hi*hi + lo*hi + hi*lo (fp32-grade).  Forward: Fin = K1, Fout = K0; backward-data swaps them and
-// flips the taps (Cuda_kernels/cp4Conv2dForward.cu:84-133, cp4Conv2dBackwardData.cu:57-108).  One launch can carry
+// flips the taps (Cuda_kernels/cp4Conv2dForward.cu:84-133, cp4Conv2dBackwardData.cu:57-108).  A convolution given no
+// output only writes its rank plane P (what the stand-alone backward-filter needs of it): the producer then loads
+// its own rows only and the output warps skip it.  One launch can carry
 // two convolutions (the forward and the backward-data of a training step): their rows form one list that is cut into
 // equal ranges.  A range that starts inside an image recomputes the rank rows of its two neighbours (one row above,
 // one below).  The warps meet only through mbarriers; every wait is bounded, and a wait that runs out sets a status
@@ -199,7 +201,9 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
         const StreamProb& p = s.conv ? p1 : p0;
         const CUtensorMap* map = s.conv ? &map1 : &map0;
         const uint32_t bytes = (uint32_t)p.Cin * (uint32_t)W * 4u;
-        const int ya = max(s.y0 - 1, 0), yb = min(s.y0 + s.len + 1, H);
+        // a convolution without an output only writes its rank plane: its own rows, no neighbours
+        const bool po = p.out == nullptr;
+        const int ya = po ? s.y0 : max(s.y0 - 1, 0), yb = po ? s.y0 + s.len : min(s.y0 + s.len + 1, H);
         for (int y = ya; y < yb; ++y) {
           if (issued >= XS && !wait_or_abort(&empty[x.slot], x.par, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&full[x.slot], bytes);
@@ -225,7 +229,7 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
             const int i = i0 + k * kWorkers + tid;
             const int c = i / kRP, r = i - c * kRP;     // r fastest: contiguous reads of Fin[c][:] and Fout[t][:]
             v1[k] = (i < n1 && r < g.R) ? __ldg(p.Fin + (size_t)c * g.Rs + g.r0 + r) : 0.f;
-            v2[k] = (i < n2 && r < g.R && c < p.Cout) ? __ldg(p.Fout + (size_t)c * g.Rs + g.r0 + r) : 0.f;
+            v2[k] = (i < n2 && r < g.R && c < p.Cout && p.out != nullptr) ? __ldg(p.Fout + (size_t)c * g.Rs + g.r0 + r) : 0.f;
           }
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -286,7 +290,8 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
         float* sv = p.save == nullptr ? nullptr
                     : p.save + (((size_t)s.n * g.Rs + g.r0 + gq) * H + s.y0) * W + w * 8 + 2 * tq;
         const bool sv0 = gq < g.R, sv1 = gq + 8 < g.R;
-        for (int j = 0; j <= s.len + 1 && ok; ++j) {
+        const bool po = p.out == nullptr;   // plane only: no rank ring, no output warps
+        for (int j = po ? 1 : 0; j <= (po ? s.len : s.len + 1) && ok; ++j) {
           const int y = s.y0 - 1 + j;
           float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
           if (y >= 0 && y < H) {     // uniform over the CTA: rows outside the image are zero and were never loaded
@@ -337,6 +342,12 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
           }
           const float v0 = a0[0] + (a1[0] + a2[0]), v1 = a0[1] + (a1[1] + a2[1]);
           const float v2 = a0[2] + (a1[2] + a2[2]), v3 = a0[3] + (a1[3] + a2[3]);
+          if (sv != nullptr && j >= 1 && j <= s.len) {   // the rows this range owns
+            if (sv0) *reinterpret_cast<float2*>(sv) = make_float2(v0, v1);
+            if (sv1) *reinterpret_cast<float2*>(sv + (size_t)8 * H * W) = make_float2(v2, v3);
+            sv += W;
+          }
+          if (po) continue;
           if (written >= PS) {
             ok = wait_or_abort(&pempty[pr.slot], pr.par, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
@@ -347,11 +358,6 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
           pd[kRP] = v1;
           pd[2] = v2;          // rank gq + 8 sits two places after rank gq
           pd[kRP + 2] = v3;
-          if (sv != nullptr && j >= 1 && j <= s.len) {   // the rows this range owns
-            if (sv0) *reinterpret_cast<float2*>(sv) = make_float2(v0, v1);
-            if (sv1) *reinterpret_cast<float2*>(sv + (size_t)8 * H * W) = make_float2(v2, v3);
-            sv += W;
-          }
           __syncwarp();
           if (lane == 0) mbar_arrive(&pfull[pr.slot]);
           pr.next(PS);
@@ -371,6 +377,7 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
       uint32_t fh[kRegs ? NMB2 : 1][2][4], fl[kRegs ? NMB2 : 1][2][4];
       while (ok && next_segment(cur, gb, g, s)) {
         const StreamProb& p = s.conv ? p1 : p0;
+        if (p.out == nullptr) continue;   // plane only: nothing for the output warps, and no rank rows in the ring
         const int kF2 = g.CoutPad * FP2;
         const float* f2 = F2 + (size_t)s.conv * 2 * kF2 + frow;
         const int nmb = kRegs ? NMB2 : ((p.Cout + 15) >> 4);
@@ -540,6 +547,7 @@ bool stream_shape_ok(const Cp4Args& a) {
   if (a.Cin % 8 != 0 || a.Cin > 256 || a.Cout < 1) return false;   // the box of a row holds all input channels
   if (reinterpret_cast<uintptr_t>(a.in) & 15) return false;                    // tensor map
   if (reinterpret_cast<uintptr_t>(a.out) & 7) return false;                    // 8-byte stores
+  if (a.out == nullptr && (a.save == nullptr || a.accumulate)) return false;   // no output: the rank plane is the result
   if (a.save && (reinterpret_cast<uintptr_t>(a.save) & 7)) return false;
   return true;
 }
