@@ -56,7 +56,6 @@ struct GradGeom {
   int nparam;                             // floats of a band's partial vector: (T + C + 6) * R
   int oP, oQ, oZ, oW, oRed, oBar;         // byte offsets: Q plane first (ring space from the start), then P; Z; weights
   long long* trace;                       // diagnostics: 32 cycle stamps per CTA for the first 1024 CTAs (null: off)
-  int stagger, sm_count;                  // cycles by which the second CTA of every SM starts late
 };
 
 __device__ __forceinline__ bool try_wait(uint32_t bar, uint32_t parity) {
@@ -137,13 +136,6 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
     return;
   }
 
-  if (g.stagger > 0 && (int)blockIdx.x >= g.sm_count && (int)blockIdx.x < 2 * g.sm_count) {
-    // Two CTAs that start together on an SM set up, stream and sum up in lockstep, and only the streaming part uses
-    // the memory system: the second one starts late, so that one streams while the other is in its other phases;
-    // the CTAs of the second round follow the first round's and keep the shift.
-    const long long t0 = clock64();
-    while (clock64() - t0 < g.stagger) {}
-  }
   long long* tr = (g.trace != nullptr && blockIdx.x < 1024 && tid == 0) ? g.trace + (size_t)blockIdx.x * 32 : nullptr;
   auto stamp = [&](int k) { if (tr) tr[k] = clock64(); };
   stamp(0);
@@ -611,16 +603,6 @@ int cp4_grad_band_launch(const Cp4BwdFilterArgs& a, const float* P, const float*
   g.N = a.N; g.H = a.H; g.W = a.W; g.C = a.C; g.T = a.T; g.R = a.R; g.Rs = a.Rs; g.r0 = a.r0;
   g.nparam = (a.T + a.C + 6) * a.R;
   g.trace = band_trace_buffer();
-  static const int stagger = [] {
-    const char* e = getenv("B200CP_GRAD_STAGGER");
-    return e ? atoi(e) : 0;
-  }();
-  g.stagger = stagger;
-  {
-    DeviceInfo di;
-    if (int rc = device_info(&di)) return rc;
-    g.sm_count = di.sm_count;
-  }
   const size_t need = (size_t)g.tiles * g.nparam * sizeof(float);
   if (a.ws_bytes < need)
     return fail(B200CP_ERR_WORKSPACE, "cp4 bwd-filter (bands): workspace of %zu bytes needed, %zu given", need, a.ws_bytes);
