@@ -527,12 +527,14 @@ def main():
     value = world * n * K / (ms * 1e-3)
 
     # ---- end to end: host buffers through the C ABI's host entry point ------------------------
-    Ks = max(4, min(K, 20))
+    Ks = max(8, min(K, 60))                     # steps of the end-to-end loop: its fill and drain cost one step's copies
     hX, hdU = torch.from_numpy(X).pin_memory(), torch.from_numpy(dU).pin_memory()
     hf = [torch.from_numpy(a).pin_memory() for a in (K0, K1, KH, KW)]
-    # two sets of pinned result buffers: step i+1 is queued while step i drains (two slots of the host entry point)
+    # NSLOT sets of pinned result buffers: steps i+1 .. i+NSLOT-1 are queued while step i drains (the slots of the host
+    # entry point), so that the copy-in runs ahead of the copy-out by more than a kernel time
+    NSLOT = 4
     houts = [(torch.empty((n, c["T"], c["H"], c["W"])).pin_memory(), torch.empty((n, c["C"], c["H"], c["W"])).pin_memory(),
-              torch.empty(nK).pin_memory()) for _ in range(2)]
+              torch.empty(nK).pin_memory()) for _ in range(NSLOT)]
 
     def finish(slot):
         P.cp4_conv2d_step_host_wait(slot)
@@ -545,12 +547,13 @@ def main():
 
     def run_e2e(steps):
         for i in range(steps):
-            P.cp4_conv2d_step_host_submit(hX, hdU, *hf, houts[i % 2], pad=c["pad"], flags=flags, slot=i % 2)
-            if i >= 1:
-                finish((i - 1) % 2)
-        finish((steps - 1) % 2)
+            P.cp4_conv2d_step_host_submit(hX, hdU, *hf, houts[i % NSLOT], pad=c["pad"], flags=flags, slot=i % NSLOT)
+            if i >= NSLOT - 1:
+                finish((i - (NSLOT - 1)) % NSLOT)
+        for i in range(max(0, steps - (NSLOT - 1)), steps):
+            finish(i % NSLOT)
 
-    run_e2e(3)
+    run_e2e(NSLOT + 1)
     barrier()
     t0 = time.perf_counter()
     run_e2e(Ks)

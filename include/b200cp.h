@@ -171,8 +171,9 @@ int b200cp_cp4_step_host(const b200cp_tensor_shape* s, const float* X, const flo
 
 /* The same step, queued: `submit` returns once the copies and kernels of one step are on the library's
  * copy-in, compute and copy-out streams; `wait` blocks until that slot's results are in U / dX / dK_packed.
- * Two slots (0 and 1) with their own device buffers let a caller submit step i+1 while step i drains, so the
- * host-to-device copy of one step, the kernels of another and the device-to-host copy of a third overlap.
+ * Four slots (0 .. 3) with their own device buffers let a caller submit the next steps while step i drains, so the
+ * host-to-device copy of one step, the kernels of another and the device-to-host copy of a third overlap; with three
+ * or four steps in flight neither direction of the host link waits for a kernel.
  * Host buffers should be pinned and must stay untouched until `wait` returns.  Submitting to a slot that is
  * still pending waits for it first.  No counterpart in the reference (its launchers synchronise the device). */
 int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,

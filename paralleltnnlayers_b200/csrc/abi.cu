@@ -130,14 +130,21 @@ int run_conv(const b200cp_tensor_shape* s, const float* in, const float* K0, con
 }
 
 // ---- cached device buffers of the *_host helpers --------------------------
+// Slots of the host-buffer step.  With two, the copy-out of a step waits for its kernels while the copy-in of the next
+// step but one waits for that copy-out (it reuses the buffers): each direction of the host link idles for a kernel
+// time per step.  A third and fourth slot let the copy-in run ahead.
+constexpr int kHostSlots = 4;
 struct HostCtx {
   std::vector<void*> bufs;
   std::vector<size_t> sizes;
   // copy-in, compute and copy-out streams: the two copy directions and the kernels overlap
   cudaStream_t s_in = nullptr, s_cmp = nullptr, s_out = nullptr;
   // per slot: X and factors in, dU in, forward / backward-data / backward-filter done, results out
-  cudaEvent_t ev[2][6] = {};
-  bool pending[2] = {false, false};
+  cudaEvent_t ev[kHostSlots][6] = {};
+  bool pending[kHostSlots] = {};
+  // pinned staging of the four factor matrices of a slot: they go to the device as one copy
+  float* stage[kHostSlots] = {};
+  size_t stage_bytes[kHostSlots] = {};
 };
 std::mutex g_host_mu;
 HostCtx g_host_ctx[64];
@@ -619,7 +626,7 @@ static int host_ctx_ready(HostCtx& c) {
   B200CP_CUDA_OK(cudaStreamCreateWithFlags(&c.s_in, cudaStreamNonBlocking));
   B200CP_CUDA_OK(cudaStreamCreateWithFlags(&c.s_cmp, cudaStreamNonBlocking));
   B200CP_CUDA_OK(cudaStreamCreateWithFlags(&c.s_out, cudaStreamNonBlocking));
-  for (int sl = 0; sl < 2; ++sl)
+  for (int sl = 0; sl < kHostSlots; ++sl)
     for (int e = 0; e < 6; ++e) B200CP_CUDA_OK(cudaEventCreateWithFlags(&c.ev[sl][e], cudaEventDisableTiming));
   return B200CP_OK;
 }
@@ -629,7 +636,8 @@ int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, co
                                 float* dK_packed, int flags, int slot) {
   if (int rc = check_shape(s, "b200cp_cp4_step_host_submit")) return rc;
   if (int rc = check_ptrs("b200cp_cp4_step_host_submit", {X, K0, K1, KH, KW})) return rc;
-  if (slot < 0 || slot > 1) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_submit: slot must be 0 or 1");
+  if (slot < 0 || slot >= kHostSlots)
+    return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_submit: slot must be 0 .. %d", kHostSlots - 1);
   const bool bwd = dU != nullptr;
   if (!U && !bwd) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_submit: nothing to compute");
   if (bwd && (!dX || !dK_packed))
@@ -649,17 +657,19 @@ int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, co
   const size_t nK0 = s->T * R, nK1 = s->C * R, nKH = s->Y * R, nKW = s->X * R, nK = nK0 + nK1 + nKH + nKW;
   float *dXin, *dUout, *dF, *ddU = nullptr, *ddX = nullptr, *ddK = nullptr, *ws = nullptr;
   const size_t b0 = (size_t)slot * 8;
+  constexpr int kWsIndex = 8 * kHostSlots;
   size_t wsb = 0;
   if (bwd) wsb = b200cp_cp4_step_workspace_bytes(s, flags);
   // a (re)allocation frees a buffer the other slot's queued work may still use: drain first
   {
     const size_t want[7] = {nX * 4, nU * 4, nK * 4, bwd ? nU * 4 : 0, bwd ? nX * 4 : 0, bwd ? nK * 4 : 0, 0};
-    bool grow = c.bufs.size() <= 16 || c.sizes[16] < wsb;
+    bool grow = c.bufs.size() <= (size_t)kWsIndex || c.sizes[kWsIndex] < wsb;
     for (int k = 0; k < 7 && !grow; ++k) grow = c.sizes[b0 + k] < want[k];
-    if (grow && c.pending[slot ^ 1]) {
-      B200CP_CUDA_OK(cudaEventSynchronize(c.ev[slot ^ 1][5]));
-      c.pending[slot ^ 1] = false;
-    }
+    for (int o = 0; o < kHostSlots && grow; ++o)
+      if (o != slot && c.pending[o]) {
+        B200CP_CUDA_OK(cudaEventSynchronize(c.ev[o][5]));
+        c.pending[o] = false;
+      }
   }
   if (int rc = host_buffer(c, b0 + 0, nX * 4, &dXin)) return rc;
   if (int rc = host_buffer(c, b0 + 1, nU * 4, &dUout)) return rc;
@@ -668,15 +678,24 @@ int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, co
     if (int rc = host_buffer(c, b0 + 3, nU * 4, &ddU)) return rc;
     if (int rc = host_buffer(c, b0 + 4, nX * 4, &ddX)) return rc;
     if (int rc = host_buffer(c, b0 + 5, nK * 4, &ddK)) return rc;
-    if (int rc = host_buffer(c, 16, wsb, &ws)) return rc;  // one workspace: the compute stream is serial
+    if (int rc = host_buffer(c, kWsIndex, wsb, &ws)) return rc;  // one workspace: the compute stream is serial
   }
   cudaEvent_t* ev = c.ev[slot];
   float *dK0 = dF, *dK1 = dK0 + nK0, *dKH = dK1 + nK1, *dKW = dKH + nKH;
+  if (c.stage_bytes[slot] < nK * 4) {
+    if (c.stage[slot]) B200CP_CUDA_OK(cudaFreeHost(c.stage[slot]));
+    c.stage[slot] = nullptr;
+    c.stage_bytes[slot] = 0;
+    B200CP_CUDA_OK(cudaHostAlloc(reinterpret_cast<void**>(&c.stage[slot]), nK * 4, cudaHostAllocDefault));
+    c.stage_bytes[slot] = nK * 4;
+  }
+  // (the slot's previous copy out of the staging buffer is complete: its step was waited for above)
+  memcpy(c.stage[slot], K0, nK0 * 4);
+  memcpy(c.stage[slot] + nK0, K1, nK1 * 4);
+  memcpy(c.stage[slot] + nK0 + nK1, KH, nKH * 4);
+  memcpy(c.stage[slot] + nK0 + nK1 + nKH, KW, nKW * 4);
+  B200CP_CUDA_OK(cudaMemcpyAsync(dF, c.stage[slot], nK * 4, cudaMemcpyHostToDevice, c.s_in));
   B200CP_CUDA_OK(cudaMemcpyAsync(dXin, X, nX * 4, cudaMemcpyHostToDevice, c.s_in));
-  B200CP_CUDA_OK(cudaMemcpyAsync(dK0, K0, nK0 * 4, cudaMemcpyHostToDevice, c.s_in));
-  B200CP_CUDA_OK(cudaMemcpyAsync(dK1, K1, nK1 * 4, cudaMemcpyHostToDevice, c.s_in));
-  B200CP_CUDA_OK(cudaMemcpyAsync(dKH, KH, nKH * 4, cudaMemcpyHostToDevice, c.s_in));
-  B200CP_CUDA_OK(cudaMemcpyAsync(dKW, KW, nKW * 4, cudaMemcpyHostToDevice, c.s_in));
   B200CP_CUDA_OK(cudaEventRecord(ev[0], c.s_in));
   if (bwd) {
     B200CP_CUDA_OK(cudaMemcpyAsync(ddU, dU, nU * 4, cudaMemcpyHostToDevice, c.s_in));
@@ -705,7 +724,8 @@ int b200cp_cp4_step_host_submit(const b200cp_tensor_shape* s, const float* X, co
 }
 
 int b200cp_cp4_step_host_wait(int slot) {
-  if (slot < 0 || slot > 1) return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_wait: slot must be 0 or 1");
+  if (slot < 0 || slot >= kHostSlots)
+    return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_step_host_wait: slot must be 0 .. %d", kHostSlots - 1);
   int dev = 0;
   B200CP_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(B200CP_ERR_NO_DEVICE, "device ordinal %d out of range", dev);

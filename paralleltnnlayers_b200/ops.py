@@ -214,7 +214,7 @@ def cp4_conv2d_step_host(X, dU, FT, FC, FY, FX, pad=1, flags=0, out=None):
 
 
 def cp4_conv2d_step_host_submit(X, dU, FT, FC, FY, FX, out, pad=1, flags=0, slot=0):
-    """Queue one step on ``slot`` (0 or 1) through ``b200cp_cp4_step_host_submit``; ``out`` holds the pinned
+    """Queue one step on ``slot`` (0 .. 3) through ``b200cp_cp4_step_host_submit``; ``out`` holds the pinned
     ``(U, dX, dK_packed)`` that ``cp4_conv2d_step_host_wait(slot)`` fills.  Inputs and outputs must stay
     alive and untouched until that wait returns."""
     ts = [X, dU, FT, FC, FY, FX] + list(out)

@@ -146,6 +146,30 @@ def test_host_entry_point_two_slots_in_flight():
         check(dK, ref, "queued dK", atol=1e-4)
 
 
+def test_host_entry_point_four_slots_in_flight():
+    """Six steps over the four slots, three or four in flight at a time; a slot outside 0 .. 3 is refused."""
+    import paralleltnnlayers_b200 as P
+    cases = [_inputs((80 + k, 2, 8, 16, 9, 24, 3, 5, 1, 0.3)) for k in range(6)]
+    pins, outs = [], []
+    for (X, K0, K1, KH, KW, dU), pad in cases:
+        pins.append([torch.from_numpy(a).pin_memory() for a in (X, dU, K0, K1, KH, KW)])
+        outs.append((torch.empty(X.shape[0], K0.shape[0], X.shape[2], X.shape[3]).pin_memory(),
+                     torch.empty(X.shape).pin_memory(), torch.empty((K0.shape[0] + K1.shape[0] + 6) * K0.shape[1]).pin_memory()))
+    for k in range(6):
+        P.cp4_conv2d_step_host_submit(*pins[k], outs[k], pad=1, slot=k % 4)
+        if k >= 3:
+            P.cp4_conv2d_step_host_wait((k - 3) % 4)
+    for k in range(3, 6):
+        P.cp4_conv2d_step_host_wait(k % 4)
+    for ((X, K0, K1, KH, KW, dU), pad), (U, dX, dK) in zip(cases, outs):
+        check(U, O.cp4_forward(X, K0, K1, KH, KW, pad), "queued fwd")
+        check(dX, O.cp4_backward_data(dU, K0, K1, KH, KW, pad), "queued bwd-data")
+        ref = np.concatenate([a.ravel() for a in O.cp4_backward_filter(X, dU, K0, K1, KH, KW, pad)])
+        check(dK, ref, "queued dK", atol=1e-4)
+    with pytest.raises(P.B200CPError):
+        P.cp4_conv2d_step_host_submit(*pins[0], outs[0], pad=1, slot=4)
+
+
 def test_errors_are_status_codes():
     import paralleltnnlayers_b200 as P
     x = torch.zeros(1, 4, 8, 8, device="cuda")
