@@ -170,8 +170,10 @@ __device__ __forceinline__ bool exchange_load(const unsigned long long* p, unsig
 int p2p_fused_args(void* ctx, size_t n, int mode, float* prev_out, ExchangeArgs* out);
 void p2p_fused_set_pending(void* ctx, size_t n, int R, int Rs);
 int exchange_finish_launch(const ExchangeArgs& ex, int nparam, int R, int Rs, int r0, float* dK, cudaStream_t st);
+// split > 0: entries below `split` are summed over the first nparts_low partial vectors, the others over nparts
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
-                               cudaStream_t st, bool after_own_kernel = false, const ExchangeArgs* exchange = nullptr);
+                               cudaStream_t st, bool after_own_kernel = false, const ExchangeArgs* exchange = nullptr,
+                               int split = 0, int nparts_low = 0);
 // the same gradients over full-width row bands (bulk / tensor-map loads, 3x3, W % 4 == 0, at most 16 ranks);
 // *done = false: not a shape this kernel takes
 bool cp4_grad_band_supported(const Cp4BwdFilterArgs& a);

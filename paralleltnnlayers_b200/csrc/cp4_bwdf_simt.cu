@@ -381,12 +381,14 @@ __device__ __forceinline__ float exchange_gather(const ExchangeArgs& ex, bool li
 // In pipelined mode (ex.mode == 1) the kernel only posts its sums and completes the *previous* step's exchange, whose
 // flags have long arrived: the exchange latency then costs the step nothing.
 template <bool EXCHANGE>
-__global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* __restrict__ partial, int nparts,
+__global__ void __launch_bounds__(1024) cp4_reduce_partials_kernel(const float* __restrict__ partial, int nparts_high,
                                                                    int nparam, int R, int Rs, int r0,
-                                                                   float* __restrict__ dK, const ExchangeArgs ex) {
+                                                                   float* __restrict__ dK, const ExchangeArgs ex,
+                                                                   int split, int nparts_low) {
   __shared__ float red[32][33];
   grid_dependency_wait();   // the partials are the previous kernel's output
   const int j = blockIdx.x * 32 + threadIdx.x, sl = threadIdx.y;
+  const int nparts = j < split ? nparts_low : nparts_high;   // entries below `split` come from fewer CTAs
   const int per = (nparts + 31) / 32;
   const int i0 = sl * per, i1 = min(nparts, i0 + per);
   float s0 = 0.f;
@@ -475,7 +477,7 @@ int launch_bwd_filter(const Cp4BwdFilterArgs& a, const TileChoice& t, const Devi
   B200CP_LAUNCH_OK("cp4_bwd_filter_kernel");
   cp4_reduce_partials_kernel<false><<<ceil_div(gf.nparam, 32), dim3(32, 32), 0, st>>>((const float*)a.ws, (int)ctas,
                                                                                    gf.nparam, a.R, a.Rs, a.r0, a.dK,
-                                                                                   ExchangeArgs{});
+                                                                                   ExchangeArgs{}, 0, 0);
   B200CP_LAUNCH_OK("cp4_reduce_partials_kernel");
   return B200CP_OK;
 }
@@ -507,16 +509,17 @@ int dispatch_bwd_filter_rank(const Cp4BwdFilterArgs& a, const DeviceInfo& di, cu
 }  // namespace
 
 int cp4_reduce_partials_launch(const float* partial, int nparts, int nparam, int R, int Rs, int r0, float* dK,
-                               cudaStream_t st, bool after_own_kernel, const ExchangeArgs* exchange) {
+                               cudaStream_t st, bool after_own_kernel, const ExchangeArgs* exchange, int split,
+                               int nparts_low) {
   if (exchange != nullptr) {
     if (ceil_div(nparam, 32) > exchange->ctas)
       return fail(B200CP_ERR_INVALID_ARG, "fused exchange: %d gradient entries, the context has flags for %d", nparam,
                   exchange->ctas * 32);
     B200CP_CUDA_OK(launch_kernel(cp4_reduce_partials_kernel<true>, dim3(ceil_div(nparam, 32)), dim3(32, 32), 0, st,
-                                 after_own_kernel, partial, nparts, nparam, R, Rs, r0, dK, *exchange));
+                                 after_own_kernel, partial, nparts, nparam, R, Rs, r0, dK, *exchange, split, nparts_low));
   } else {
     B200CP_CUDA_OK(launch_kernel(cp4_reduce_partials_kernel<false>, dim3(ceil_div(nparam, 32)), dim3(32, 32), 0, st,
-                                 after_own_kernel, partial, nparts, nparam, R, Rs, r0, dK, ExchangeArgs{}));
+                                 after_own_kernel, partial, nparts, nparam, R, Rs, r0, dK, ExchangeArgs{}, split, nparts_low));
   }
   B200CP_LAUNCH_OK("cp4_reduce_partials_kernel");
   return B200CP_OK;
