@@ -276,6 +276,9 @@ def main():
     import paralleltnnlayers_b200 as P   # raises if libb200cp.so is missing: there is no fallback
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(local)
+    # one process per GPU: keep this rank's host threads and the pinned buffers it allocates on the GPU's NUMA node
+    from paralleltnnlayers_b200.dist import bind_host_to_gpu
+    numa_node = bind_host_to_gpu(local) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -682,7 +685,7 @@ def main():
                                      "on a communication stream, overlapped with the next step")) if world > 1 else "none"},
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": Ks,
-                "copy_gbs_per_rank": e2e_gbs, "copy_only_gbs_per_rank": copy_gbs,
+                "copy_gbs_per_rank": e2e_gbs, "copy_only_gbs_per_rank": copy_gbs, "numa_node_rank0": numa_node,
                 "note": "host buffers through b200cp_cp4_step_host_submit / _wait (b200cp_cp4_step inside); the copies "
                         "alone, both directions at once, reach copy_only_gbs_per_rank on this host"},
         "extra": extra,

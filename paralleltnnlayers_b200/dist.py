@@ -29,6 +29,32 @@ def allreduce_factor_grads(packed, group=None):
     return packed
 
 
+def bind_host_to_gpu(device=None):
+    """Best effort: restrict this process to the CPUs of the NUMA node its GPU hangs off, so that the pinned host
+    buffers it allocates afterwards (first touch) and the threads that fill them are local to the GPU's PCIe root.
+    With one process per GPU on a two-socket host this keeps the host-to-device traffic of half the ranks off the
+    socket interconnect.  Returns the node number, or None when it cannot be found (no sysfs, one node, no rights)."""
+    import os
+    try:
+        dev = torch.cuda.current_device() if device is None else int(device)
+        pr = torch.cuda.get_device_properties(dev)
+        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/numa_node" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        node = int(open(path).read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            a, _, b = part.partition("-")
+            cpus.update(range(int(a), int(b or a) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 class P2PAllreduce:
     """The gradient allreduce as one small kernel over NVLink peer memory (``b200cp_p2p_*``), one process per GPU.
 
