@@ -294,6 +294,7 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
         for (int j = po ? 1 : 0; j <= (po ? s.len : s.len + 1) && ok; ++j) {
           const int y = s.y0 - 1 + j;
           float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
+          float b0[4] = {0.f, 0.f, 0.f, 0.f}, b1[4] = {0.f, 0.f, 0.f, 0.f}, b2[4] = {0.f, 0.f, 0.f, 0.f};
           if (y >= 0 && y < H) {     // uniform over the CTA: rows outside the image are zero and were never loaded
             ok = wait_or_abort(&full[x.slot], x.par, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
@@ -313,10 +314,20 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
                 uint32_t bh[2], bl[2];
                 split_tf32(xv[ks][0], bh[0], bl[0]);
                 split_tf32(xv[ks][1], bh[1], bl[1]);
-                mma_tf32_ordered(a0, fh[ks], bh);
-                mma_tf32_ordered(a1, fl[ks], bh);
-                mma_tf32_ordered(a2, fh[ks], bl);
+                // six accumulator chains (three terms x even / odd k-step): consecutive mma on one accumulator are six
+                // instructions apart
+                if (ks & 1) {
+                  mma_tf32_ordered(b0, fh[ks], bh);
+                  mma_tf32_ordered(b1, fl[ks], bh);
+                  mma_tf32_ordered(b2, fh[ks], bl);
+                } else {
+                  mma_tf32_ordered(a0, fh[ks], bh);
+                  mma_tf32_ordered(a1, fl[ks], bh);
+                  mma_tf32_ordered(a2, fh[ks], bl);
+                }
               }
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { a0[e] += b0[e]; a1[e] += b1[e]; a2[e] += b2[e]; }
             } else {
               const float* fk = f1;
               float x0 = xs[0], x1 = xs[4 * W];
