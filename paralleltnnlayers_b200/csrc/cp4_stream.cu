@@ -575,7 +575,10 @@ bool plan_stream(const Cp4Args* convs, int nconv, const DeviceInfo& di, StreamPl
   g.FP1 = cin + 4;
   g.FP2 = kRP + 4;
   g.CoutPad = (cout + 63) / 64 * 64;
-  g.PS = 6;
+  // rank rows in the ring: three are read per output row and one is being written; deeper rings measured slower
+  // (step at N=32, C=T=64, 56x56, R=16: 60.6 us with 4, 61.1 with 6, 61.4 with 8)
+  g.PS = 4;
+  static_assert(4 <= kMaxRing, "the rank ring has a barrier pair per row");
   const size_t pring = (size_t)g.PS * g.pslot_floats * 4;
   const size_t f1 = (size_t)nconv * 2 * kRP * g.FP1 * 4;
   const size_t f2 = (size_t)nconv * 2 * g.CoutPad * g.FP2 * 4;
