@@ -587,7 +587,10 @@ bool plan_stream(const Cp4Args* convs, int nconv, const DeviceInfo& di, StreamPl
   const size_t fixed = pring + f1 + f2 + ws + bars + 512;
   const size_t stage = (size_t)g.xstage_floats * 4;
   if (fixed + 3 * stage > (size_t)di.smem_optin) return false;
-  g.XS = (int)std::min<size_t>(kMaxRing, ((size_t)di.smem_optin - fixed) / stage);
+  // input rows in flight: four measured best (step at N=32, C=T=64, 56x56, R=16: 59.1 us with 3, 58.8 with 4, 59.0 with
+  // 5, 59.6 with 6, 60.6 with 8 -- every CTA asks for its rows at the same time, and deeper rings only lengthen the
+  // queue in front of the memory system)
+  g.XS = (int)std::min<size_t>(4, ((size_t)di.smem_optin - fixed) / stage);
   size_t o = align_up((size_t)g.XS * stage, 128);
   g.oP = (int)o; o += pring;
   g.oF1 = (int)o; o += f1;
