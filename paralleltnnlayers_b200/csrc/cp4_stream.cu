@@ -217,7 +217,10 @@ cp4_stream_kernel(const StreamGeom g, const __grid_constant__ CUtensorMap map0, 
     // factor planes, stencil weights and the two zero columns of every rank-ring row; the global loads of a thread
     // are all issued before the first value is used
     {
-      for (int cv = 0; cv < g.nconv; ++cv) {
+      // only the convolutions this CTA's rows belong to (one, except for the CTA whose range crosses from the first
+      // convolution's rows into the second's)
+      const int cv_first = ga >= g.N * H ? 1 : 0, cv_last = gb - 1 >= g.N * H ? 1 : 0;
+      for (int cv = cv_first; cv <= cv_last; ++cv) {
         const StreamProb& p = cv ? p1 : p0;
         float* f1 = F1 + (size_t)cv * 2 * kRP * FP1;
         float* f2 = F2 + (size_t)cv * 2 * g.CoutPad * FP2;
