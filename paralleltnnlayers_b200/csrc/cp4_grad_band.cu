@@ -106,7 +106,7 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
   float* Ps = reinterpret_cast<float*>(sm + g.oP);    // [RP][PP] halo band of P
   float* Zs = reinterpret_cast<float*>(sm + g.oZ);    // [RP][ZP] Z (kind 0) or Qt (kind 1) on the band's own pixels
   float* Ws = reinterpret_cast<float*>(sm + g.oW);    // [9][RP] stencil weights, then [3][RP] KH, [3][RP] KW
-  float* red = reinterpret_cast<float*>(sm + g.oRed); // [threads][6] spatial sums, later the warps' channel sums
+  float* red = reinterpret_cast<float*>(sm + g.oRed); // [threads][9] spatial correlations, later the warps' channel sums
   uint64_t* full = reinterpret_cast<uint64_t*>(sm + g.oBar);
   uint64_t* empty = full + kMaxStages;
   uint64_t* planes_full = empty + kMaxStages;
@@ -231,17 +231,15 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
     ok = ok && !*abort_flag;
 
     // ---- stencil: strips of 8 pixels, one rank per thread ------------------------------------------------------------
-    float sp[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // this thread's share of dKH[0..2], dKW[0..2] of its rank
+    float sp[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // this thread's share of the nine Q x P correlations of its rank
     if (ok) {
       static_assert(NTC % RP == 0, "a thread keeps one rank");
       const int spr = (W + 7) >> 3;
       const int nitems = own_rows * spr;
       const int r = tid % RP;
-      float w[9], kh[3], kw[3];
+      float w[9];
 #pragma unroll
       for (int t = 0; t < 9; ++t) w[t] = Ws[t * RP + r];
-#pragma unroll
-      for (int t = 0; t < 3; ++t) { kh[t] = Ws[(9 + t) * RP + r]; kw[t] = Ws[(12 + t) * RP + r]; }
       const float* src = kind ? Qs : Ps;
       constexpr int STEP = NTC / RP;
       int oy = (tid / RP) / spr, sx = (tid / RP) % spr;
@@ -274,16 +272,13 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
         *reinterpret_cast<float4*>(zd) = make_float4(z[0], z[1], z[2], z[3]);
         if (hi_ok) *reinterpret_cast<float4*>(zd + 4) = make_float4(z[4], z[5], z[6], z[7]);
         if (kind) {
-          // spatial factors: Q at the strip's own pixels against the row / column sums of P around them
+          // spatial factors: the nine correlations S[dy][dx] = sum_px Q[px] P[px + (dy-1, dx-1)] of the strip; the
+          // factor gradients are their contractions with the other factor (dKH[i] = sum_j KW[j] S[i][j], dKW[j] =
+          // sum_i KH[i] S[i][j]), formed once per CTA
           const float* qc = Qs + r * PP + (oy + 1) * W + x0;
           const float4 qa = *reinterpret_cast<const float4*>(qc);
           const float4 qb = hi_ok ? *reinterpret_cast<const float4*>(qc + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
           const float q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-          float cs[3][8];   // column sums: sum_dy KH[dy] P[dy][j + dx]
-#pragma unroll
-          for (int dx = 0; dx < 3; ++dx)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) cs[dx][j] = 0.f;
           const float* pp = Ps + r * PP + oy * W + x0;
 #pragma unroll
           for (int dy = 0; dy < 3; ++dy) {
@@ -295,22 +290,13 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
             v[1] = a.x; v[2] = a.y; v[3] = a.z; v[4] = a.w;
             v[5] = c.x; v[6] = c.y; v[7] = c.z; v[8] = c.w;
             pp += W;
-            float rs = 0.f;   // sum_j q[j] * sum_dx KW[dx] P[dy][j + dx]
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float t = fmaf(kw[2], v[j + 2], fmaf(kw[1], v[j + 1], kw[0] * v[j]));
-              rs = fmaf(q[j], t, rs);
+            for (int dx = 0; dx < 3; ++dx) {
+              float t = 0.f;
 #pragma unroll
-              for (int dx = 0; dx < 3; ++dx) cs[dx][j] = fmaf(kh[dy], v[j + dx], cs[dx][j]);
+              for (int j = 0; j < 8; ++j) t = fmaf(q[j], v[j + dx], t);
+              sp[dy * 3 + dx] += t;
             }
-            sp[dy] += rs;
-          }
-#pragma unroll
-          for (int dx = 0; dx < 3; ++dx) {
-            float t = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) t = fmaf(q[j], cs[dx][j], t);
-            sp[3 + dx] += t;
           }
         }
         oy += dy_step;
@@ -320,7 +306,7 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
     }
     if (kind) {
 #pragma unroll
-      for (int k = 0; k < 6; ++k) red[tid * 6 + k] = sp[k];
+      for (int k = 0; k < 9; ++k) red[tid * 9 + k] = sp[k];
     }
     tc::fence_proxy_async();   // this thread's writes into the planes' space are ordered before the bulk copies that reuse it
     __syncwarp();
@@ -328,10 +314,17 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
     consumers_sync();                          // Z is complete; the spatial sums are in place
     stamp(3);
     if (kind && ok && tid < 6 * RP) {
-      // spatial sums of rank r over the threads that worked on it, in thread order
+      // the correlations of rank r summed over the threads that worked on it, in thread order, then contracted with
+      // the other spatial factor: k < 3 is dKH[k], k >= 3 is dKW[k - 3]
       const int r = tid % RP, k = tid / RP;
       float s = 0.f;
-      for (int t = r; t < NTC; t += RP) s += red[t * 6 + k];
+#pragma unroll
+      for (int o = 0; o < 3; ++o) {
+        const int idx = k < 3 ? k * 3 + o : o * 3 + (k - 3);            // S[k][o] or S[o][k - 3]
+        float c = 0.f;
+        for (int t = r; t < NTC; t += RP) c += red[t * 9 + idx];
+        s = fmaf(Ws[((k < 3 ? 12 : 9) + o) * RP + r], c, s);            // KW[o] for dKH, KH[o] for dKW
+      }
       if (r < g.R) part[(size_t)(g.T + g.C + k) * g.R + r] = s;
     }
 
@@ -547,7 +540,7 @@ bool plan_grad_search(const Cp4BwdFilterArgs& a, const DeviceInfo& di, GradGeom*
     g.oZ = (int)o; o += (size_t)16 * g.ZP * 4;
     g.oW = (int)o; o += (size_t)15 * 16 * 4;
     o = align_up(o, 16);
-    g.oRed = (int)o; o += std::max((size_t)kCons * 32 * 6 * 4, (size_t)kMma * NMB * 256 * 4);
+    g.oRed = (int)o; o += std::max((size_t)kCons * 32 * 9 * 4, (size_t)kMma * NMB * 256 * 4);
     o = align_up(o, 16);
     g.oBar = (int)o; o += 256;
     if ((int)o > di.smem_optin || (o + 1024) * 2 > (size_t)228 * 1024) continue;   // two CTAs per SM
