@@ -74,3 +74,35 @@ def test_stream_step(case):
         off += r.size
     U2, gX2, dK2 = P.cp4_conv2d_step(t[0], t[5], *t[1:5], 1)
     assert torch.equal(U, U2) and torch.equal(gX, gX2) and torch.equal(dK, dK2)
+
+
+def test_stream_random_shapes_against_the_exact_kernels():
+    """Forty seeded random shapes the row stream takes (any batch and height, W in {8, 24, 40, 56}, channels in
+    multiples of 8 up to 136, ranks 1..16): forward, backward-data and the stand-alone backward-filter (plane-only
+    convolutions + gradient bands) against the exact-fp32 CUDA-core kernels of the same library."""
+    import paralleltnnlayers_b200 as P
+    rng = np.random.default_rng(4242)
+    lib = P._lib.lib
+    for k in range(40):
+        N = int(rng.integers(1, 7)); H = int(rng.integers(1, 40)); W = int(rng.choice([8, 24, 40, 56]))
+        C = 8 * int(rng.integers(1, 18)); T = 8 * int(rng.integers(1, 18)); R = int(rng.integers(1, 17))
+        g = torch.Generator(device="cuda").manual_seed(1000 + k)
+        X = torch.rand(N, C, H, W, device="cuda", generator=g) * 2 - 1
+        dU = torch.randn(N, T, H, W, device="cuda", generator=g)
+        K0 = torch.randn(T, R, device="cuda", generator=g) * 0.2
+        K1 = torch.randn(C, R, device="cuda", generator=g) * 0.2
+        KH = torch.randn(3, R, device="cuda", generator=g) * 0.5
+        KW = torch.randn(3, R, device="cuda", generator=g) * 0.5
+        what = f"case {k}: N={N} C={C} T={T} H={H} W={W} R={R}"
+        before = lib.b200cp_test_stream_launches()
+        U = P.cp4_conv2d_forward(X, K0, K1, KH, KW, 1)
+        dX = P.cp4_conv2d_backward_data(dU, K0, K1, KH, KW, 1)
+        assert lib.b200cp_test_stream_launches() == before + 2, what
+        dK = P.cp4_conv2d_backward_filter(dU, X, K0, K1, KH, KW, 1)
+        Ue = P.cp4_conv2d_forward(X, K0, K1, KH, KW, 1, flags=P.PATH_SIMT)
+        dXe = P.cp4_conv2d_backward_data(dU, K0, K1, KH, KW, 1, flags=P.PATH_SIMT)
+        dKe = P.cp4_conv2d_backward_filter(dU, X, K0, K1, KH, KW, 1, flags=P.PATH_SIMT)
+        for a, b, nm in [(U, Ue, "forward"), (dX, dXe, "backward-data")] + [(x, y, "dK%d" % i) for i, (x, y) in enumerate(zip(dK, dKe))]:
+            scale = float(b.abs().max()) + 1e-30
+            assert float((a - b).abs().max()) <= 2e-5 * scale, f"{what}: {nm}"
+    P.device_status()
