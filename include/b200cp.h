@@ -201,6 +201,36 @@ int b200cp_rcp_bwd(int N, int H, int W, int order, const int* cdims, const int* 
                    const float* X, const float* dV, const float* const* A, const float* S, float* dX,
                    float* const* dA, float* dS, void* workspace, size_t workspace_bytes, void* stream, int flags);
 
+/* ---- the reference's "rebuild" variants ------------------------------------
+ * Its benchmarks time, beside each fused layer, the undecomposed layer run with the recomposed weight
+ * (test/benchmark_conv2d_cp4.py:35-42: cp4recom + conv2d; test/benchmark_dense_cp.py:43-49: einsum of the factors +
+ * matmul).  These entry points give that line without cuDNN / cuBLAS. */
+
+/* U[n,t,h,w] = sum_{c,y,x} K[t,c,y,x] X[n,c,h+y-pad,w+x-pad], zero outside the image, H x W output; K is
+ * [T,C,Y,X] as b200cp_cp4_recompose / b200cp_rcp_recompose write it.  s->Rank is not used. */
+int b200cp_conv2d_dense_fwd(const b200cp_tensor_shape* s, const float* X, const float* K, float* U, void* stream);
+
+/* b200cp_cp4_recompose into the workspace (T*C*Y*X floats), then b200cp_conv2d_dense_fwd. */
+size_t b200cp_cp4_rebuild_fwd_workspace_bytes(const b200cp_tensor_shape* s);
+int b200cp_cp4_rebuild_fwd(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,
+                           const float* KH, const float* KW, float* U, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/* K[t,c,y,x] = sum_r S[y,x,r] prod_k A_k[c_k,t_k,r], c and t flattened first-mode-slowest: the filter of the
+ * reshaped-CP conv (einsum of test/test_conv2d_rcp.py:41-42 in [T,C,FH,FW] order). */
+int b200cp_rcp_recompose(int order, const int* cdims, const int* tdims, int R, int FH, int FW, const float* const* A,
+                         const float* S, float* K, void* stream);
+
+/* M[i,o] = sum_r prod_k F_k[i_k,o_k,r], i and o flattened first-mode-slowest (test/benchmark_dense_cp.py:43-44). */
+int b200cp_dense_recompose(int order, const int* idims, const int* odims, int R, const float* const* F, float* M,
+                           void* stream);
+
+/* Y[b,o] = sum_i X[b,i] M[i,o] (test/benchmark_dense_cp.py:45-48) with fp32-grade results: tcgen05 with three tf32
+ * terms where B, I, O fill its tiles, CUDA cores otherwise. */
+size_t b200cp_dense_matmul_workspace_bytes(int B, int I, int O);
+int b200cp_dense_matmul(int B, int I, int O, const float* X, const float* M, float* Y, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
 /* ---- CP dense layer, order m (1..4) ------------------------------------ */
 
 /* Y[b,o] = sum_r sum_i X[b,i] prod_k F_k[i_k,o_k,r]; F[k] is [i_k, o_k, R]: the

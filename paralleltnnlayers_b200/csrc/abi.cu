@@ -808,6 +808,65 @@ int b200cp_rcp_bwd(int N, int H, int W, int order, const int* cdims, const int* 
 }
 
 // ---- dense-CP -----------------------------------------------------------------
+// ---- the reference's "rebuild" variants: the undecomposed layer with the recomposed weight ------------------------
+int b200cp_conv2d_dense_fwd(const b200cp_tensor_shape* s, const float* X, const float* K, float* U, void* stream) {
+  if (!s) return fail(B200CP_ERR_INVALID_ARG, "b200cp_conv2d_dense_fwd: shape is null");
+  b200cp_tensor_shape q = *s;
+  q.Rank = 1;  // not used by the dense convolution
+  if (int rc = check_shape(&q, "b200cp_conv2d_dense_fwd")) return rc;
+  if (int rc = check_ptrs("b200cp_conv2d_dense_fwd", {X, K, U})) return rc;
+  return conv_dense_launch(q, X, K, U, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200cp_cp4_rebuild_fwd_workspace_bytes(const b200cp_tensor_shape* s) {
+  if (!s) return 0;
+  return (size_t)s->T * s->C * s->Y * s->X * sizeof(float);
+}
+
+int b200cp_cp4_rebuild_fwd(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,
+                           const float* KH, const float* KW, float* U, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  if (int rc = check_shape(s, "b200cp_cp4_rebuild_fwd")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_rebuild_fwd", {X, K0, K1, KH, KW, U})) return rc;
+  if (!workspace || workspace_bytes < b200cp_cp4_rebuild_fwd_workspace_bytes(s))
+    return fail(B200CP_ERR_WORKSPACE, "b200cp_cp4_rebuild_fwd: workspace of %zu bytes needed, %zu given",
+                b200cp_cp4_rebuild_fwd_workspace_bytes(s), workspace ? workspace_bytes : (size_t)0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* K = static_cast<float*>(workspace);
+  if (int rc = cp4_recompose_launch(*s, K0, K1, KH, KW, K, st)) return rc;
+  return conv_dense_launch(*s, X, K, U, st);
+}
+
+int b200cp_rcp_recompose(int order, const int* cdims, const int* tdims, int R, int FH, int FW, const float* const* A,
+                         const float* S, float* K, void* stream) {
+  if (int rc = check_modes("b200cp_rcp_recompose", order, cdims, tdims, A)) return rc;
+  if (int rc = check_ptrs("b200cp_rcp_recompose", {S, K})) return rc;
+  if (FH < 1 || FW < 1) return fail(B200CP_ERR_INVALID_ARG, "b200cp_rcp_recompose: filter %d x %d", FH, FW);
+  return kron_recompose_launch(order, cdims, tdims, R, A, S, FH * FW, K, static_cast<cudaStream_t>(stream));
+}
+
+int b200cp_dense_recompose(int order, const int* idims, const int* odims, int R, const float* const* F, float* M,
+                           void* stream) {
+  if (int rc = check_modes("b200cp_dense_recompose", order, idims, odims, F)) return rc;
+  if (int rc = check_ptrs("b200cp_dense_recompose", {M})) return rc;
+  return kron_recompose_launch(order, idims, odims, R, F, nullptr, 1, M, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200cp_dense_matmul_workspace_bytes(int B, int I, int O) {
+  if (B < 1 || I < 1 || O < 1) return 0;
+  return dense_matmul_scratch_floats(B, I, O) * sizeof(float);
+}
+
+int b200cp_dense_matmul(int B, int I, int O, const float* X, const float* M, float* Y, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  if (B < 1 || I < 1 || O < 1) return fail(B200CP_ERR_INVALID_ARG, "b200cp_dense_matmul: B=%d I=%d O=%d", B, I, O);
+  if (int rc = check_ptrs("b200cp_dense_matmul", {X, M, Y})) return rc;
+  const size_t need = b200cp_dense_matmul_workspace_bytes(B, I, O);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(B200CP_ERR_WORKSPACE, "b200cp_dense_matmul: a 256-byte aligned workspace of %zu bytes is needed", need);
+  return dense_matmul_launch(B, I, O, X, M, Y, static_cast<float*>(workspace), static_cast<cudaStream_t>(stream));
+}
+
 int b200cp_dense_fwd(int B, int order, const int* idims, const int* odims, int R, const float* X,
                      const float* const* F, float* Y, void* stream, int flags) {
   (void)flags;

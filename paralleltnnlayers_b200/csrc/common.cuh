@@ -229,6 +229,14 @@ bool conv_gemm_tc_supported(int N, int T, int C, int H, int W, int FH, int FW);
 size_t conv_gemm_tc_scratch_floats(int N, int T, int C, int H, int W, int FH, int FW);
 int conv_gemm_tc_launch(int N, int T, int C, int H, int W, int FH, int FW, const float* dV, const float* X, float* G,
                         float* scratch, cudaStream_t st);
+// the reference's "rebuild" variants: dense conv2d forward with an undecomposed filter K [T][C][FH][FW]; recomposed
+// weights of the dense ([I][O]) and reshaped-CP ([T][C][FH][FW], S != nullptr) layers; Y = X M for the dense layer
+bool conv_dense_supported(const b200cp_tensor_shape& s);
+int conv_dense_launch(const b200cp_tensor_shape& s, const float* X, const float* K, float* U, cudaStream_t st);
+int kron_recompose_launch(int order, const int* a, const int* b, int R, const float* const* F, const float* S, int taps,
+                          float* Wout, cudaStream_t st);
+size_t dense_matmul_scratch_floats(int B, int I, int O);
+int dense_matmul_launch(int B, int I, int O, const float* X, const float* M, float* Y, float* scratch, cudaStream_t st);
 // G[e] = sum over splits of P[split][e], in split order
 void sum_splits_launch(const float* P, float* G, size_t n, int splits, cudaStream_t st);
 size_t contract_scratch_floats(int order, const int* cdims, const int* tdims, int R, int taps, bool has_s);

@@ -457,6 +457,98 @@ def dense_cp_backward(U, dV, *kernels, flags=0, need_dx=True, need_dw=True):
     return dU, dF
 
 
+# ---- the reference's "rebuild" variants: the undecomposed layer with the recomposed weight --------------------
+
+def conv2d_dense_forward(Input, K, pad=1):
+    """Ordinary conv2d with a dense filter ``K [T,C,Y,X]``, H x W output: the ``tf.nn.conv2d(U, K, ..., 'SAME')`` of
+    test/benchmark_conv2d_cp4.py:41."""
+    Input, K = _dev(Input, "Input"), _dev(K, "K")
+    if K.dim() != 4 or K.shape[1] != Input.shape[1]:
+        raise ValueError("K must be [T, C, Y, X] with C the input's channel count")
+    s = tensor_shape(Input.shape[0], Input.shape[1], Input.shape[2], Input.shape[3], K.shape[0], K.shape[2],
+                     K.shape[3], 1, pad)
+    U = torch.empty((s.N, s.T, s.H, s.W), device=Input.device, dtype=torch.float32)
+    with torch.cuda.device(Input.device):
+        check(lib.b200cp_conv2d_dense_fwd(C.byref(s), _p(Input), _p(K), _p(U), _stream()))
+    return U
+
+
+def cp4_conv2d_rebuild_forward(Input, FT, FC, FY, FX, pad=1):
+    """The CP4 layer's "rebuild" line (test/benchmark_conv2d_cp4.py:35-42): ``cp4recom`` then an ordinary conv2d."""
+    Input = _dev(Input, "Input")
+    FT, FC, FY, FX = (_dev(t, n) for t, n in ((FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(Input, FT, FC, FY, FX, pad)
+    U = torch.empty((s.N, s.T, s.H, s.W), device=Input.device, dtype=torch.float32)
+    with torch.cuda.device(Input.device):
+        wsb = lib.b200cp_cp4_rebuild_fwd_workspace_bytes(C.byref(s))
+        ws = torch.empty(max(wsb, 4) // 4, device=Input.device, dtype=torch.float32)
+        check(lib.b200cp_cp4_rebuild_fwd(C.byref(s), _p(Input), _p(FT), _p(FC), _p(FY), _p(FX), _p(U), _p(ws),
+                                         ws.numel() * 4, _stream()))
+    return U
+
+
+def rcp_recompose(*kernels):
+    """Dense filter ``[T, C, FH, FW]`` of the reshaped-CP conv from ``(K0[S0,T0,R], ..., KC[FH,FW,R])``."""
+    *A, KC = kernels
+    A = [_dev(a, f"kernel{k}") for k, a in enumerate(A)]
+    KC = _dev(KC, "kernelc")
+    cd, td, R = _modes(A, "rcp_recompose")
+    if KC.dim() != 3 or KC.shape[2] != R:
+        raise ValueError("kernelc must be [FH, FW, rank]")
+    Cc, Tc = 1, 1
+    for c, t in zip(cd, td):
+        Cc *= c
+        Tc *= t
+    K = torch.empty((Tc, Cc, KC.shape[0], KC.shape[1]), device=KC.device, dtype=torch.float32)
+    with torch.cuda.device(KC.device):
+        check(lib.b200cp_rcp_recompose(len(A), int_array(cd), int_array(td), R, KC.shape[0], KC.shape[1],
+                                       ptr_array([a.data_ptr() for a in A]), _p(KC), _p(K), _stream()))
+    return K
+
+
+def conv2d_rcp_rebuild_nchw(U, *kernels):
+    """The reshaped-CP layer's "rebuild" line: recompose the filter, then an ordinary same-size conv2d."""
+    K = rcp_recompose(*kernels)
+    U = _dev(U, "input")
+    N, H, W = U.shape[0], U.shape[-2], U.shape[-1]
+    return conv2d_dense_forward(U.reshape(N, K.shape[1], H, W), K, pad=(K.shape[2] - 1) // 2)
+
+
+def dense_cp_recompose(*kernels):
+    """``M [I, O]`` of the CP dense layer (the einsum + reshape of test/benchmark_dense_cp.py:43-44)."""
+    Fk = [_dev(f, f"kernel{k}") for k, f in enumerate(kernels)]
+    idims, odims, R = _modes(Fk, "dense_cp_recompose")
+    I, O = 1, 1
+    for a, b in zip(idims, odims):
+        I *= a
+        O *= b
+    M = torch.empty((I, O), device=Fk[0].device, dtype=torch.float32)
+    with torch.cuda.device(M.device):
+        check(lib.b200cp_dense_recompose(len(Fk), int_array(idims), int_array(odims), R,
+                                         ptr_array([f.data_ptr() for f in Fk]), _p(M), _stream()))
+    return M
+
+
+def dense_matmul(U, M):
+    """``U [B, I] @ M [I, O]`` with fp32-grade results (test/benchmark_dense_cp.py:45-48)."""
+    U, M = _dev(U, "input"), _dev(M, "M")
+    B = U.shape[0]
+    I, O = M.shape
+    if U.numel() != B * I:
+        raise ValueError("input size does not match M")
+    Y = torch.empty((B, O), device=U.device, dtype=torch.float32)
+    with torch.cuda.device(U.device):
+        wsb = lib.b200cp_dense_matmul_workspace_bytes(B, I, O)
+        ws = torch.empty(max(wsb, 4) // 4, device=U.device, dtype=torch.float32)
+        check(lib.b200cp_dense_matmul(B, I, O, _p(U), _p(M), _p(Y), _p(ws), ws.numel() * 4, _stream()))
+    return Y
+
+
+def dense_cp_rebuild(U, *kernels):
+    """The CP dense layer's "rebuild" line: recompose ``M``, then one matmul."""
+    return dense_matmul(U, dense_cp_recompose(*kernels))
+
+
 # ---- autograd wrappers ----------------------------------------------------------
 class CP4Conv2dFunction(torch.autograd.Function):
     """y = CP4 conv2d(x; FT, FC, FY, FX) with the fused backward kernels."""
