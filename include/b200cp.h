@@ -207,10 +207,13 @@ int b200cp_rcp_bwd(int N, int H, int W, int order, const int* cdims, const int* 
  * matmul).  These entry points give that line without cuDNN / cuBLAS. */
 
 /* U[n,t,h,w] = sum_{c,y,x} K[t,c,y,x] X[n,c,h+y-pad,w+x-pad], zero outside the image, H x W output; K is
- * [T,C,Y,X] as b200cp_cp4_recompose / b200cp_rcp_recompose write it.  s->Rank is not used. */
-int b200cp_conv2d_dense_fwd(const b200cp_tensor_shape* s, const float* X, const float* K, float* U, void* stream);
+ * [T,C,Y,X] as b200cp_cp4_recompose / b200cp_rcp_recompose write it.  s->Rank is not used.  The 16-byte aligned
+ * workspace takes the filter re-laid as tf32 hi / lo planes. */
+size_t b200cp_conv2d_dense_fwd_workspace_bytes(const b200cp_tensor_shape* s);
+int b200cp_conv2d_dense_fwd(const b200cp_tensor_shape* s, const float* X, const float* K, float* U, void* workspace,
+                            size_t workspace_bytes, void* stream);
 
-/* b200cp_cp4_recompose into the workspace (T*C*Y*X floats), then b200cp_conv2d_dense_fwd. */
+/* b200cp_cp4_recompose into the workspace, then b200cp_conv2d_dense_fwd. */
 size_t b200cp_cp4_rebuild_fwd_workspace_bytes(const b200cp_tensor_shape* s);
 int b200cp_cp4_rebuild_fwd(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,
                            const float* KH, const float* KW, float* U, void* workspace, size_t workspace_bytes,

@@ -68,7 +68,8 @@ def _load():
         "b200cp_rcp_bwd_workspace_bytes": (sz, [i, i, i, i, ip, ip, i, i, i, i]),
         "b200cp_rcp_bwd": (i, [i, i, i, i, ip, ip, i, i, i, fp, fp, pp, fp, fp, pp, fp, vp, sz, vp, i]),
         "b200cp_dense_fwd": (i, [i, i, ip, ip, i, fp, pp, fp, vp, i]),
-        "b200cp_conv2d_dense_fwd": (i, [sp, fp, fp, fp, vp]),
+        "b200cp_conv2d_dense_fwd_workspace_bytes": (sz, [sp]),
+        "b200cp_conv2d_dense_fwd": (i, [sp, fp, fp, fp, vp, sz, vp]),
         "b200cp_cp4_rebuild_fwd_workspace_bytes": (sz, [sp]),
         "b200cp_cp4_rebuild_fwd": (i, [sp, fp, fp, fp, fp, fp, fp, vp, sz, vp]),
         "b200cp_rcp_recompose": (i, [i, ip, ip, i, i, i, pp, fp, fp, vp]),

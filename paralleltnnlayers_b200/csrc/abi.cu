@@ -809,18 +809,35 @@ int b200cp_rcp_bwd(int N, int H, int W, int order, const int* cdims, const int* 
 
 // ---- dense-CP -----------------------------------------------------------------
 // ---- the reference's "rebuild" variants: the undecomposed layer with the recomposed weight ------------------------
-int b200cp_conv2d_dense_fwd(const b200cp_tensor_shape* s, const float* X, const float* K, float* U, void* stream) {
-  if (!s) return fail(B200CP_ERR_INVALID_ARG, "b200cp_conv2d_dense_fwd: shape is null");
-  b200cp_tensor_shape q = *s;
-  q.Rank = 1;  // not used by the dense convolution
-  if (int rc = check_shape(&q, "b200cp_conv2d_dense_fwd")) return rc;
+static int dense_conv_shape(const b200cp_tensor_shape* s, const char* who, b200cp_tensor_shape* q) {
+  if (!s) return fail(B200CP_ERR_INVALID_ARG, "%s: shape is null", who);
+  *q = *s;
+  q->Rank = 1;  // not used by the dense convolution
+  return check_shape(q, who);
+}
+
+size_t b200cp_conv2d_dense_fwd_workspace_bytes(const b200cp_tensor_shape* s) {
+  b200cp_tensor_shape q;
+  if (!s || !s->T || !s->C || !s->Y || !s->X || !s->W) return 0;
+  q = *s;
+  return align_up(conv_dense_scratch_floats(q) * sizeof(float), 256);
+}
+
+int b200cp_conv2d_dense_fwd(const b200cp_tensor_shape* s, const float* X, const float* K, float* U, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  b200cp_tensor_shape q;
+  if (int rc = dense_conv_shape(s, "b200cp_conv2d_dense_fwd", &q)) return rc;
   if (int rc = check_ptrs("b200cp_conv2d_dense_fwd", {X, K, U})) return rc;
-  return conv_dense_launch(q, X, K, U, static_cast<cudaStream_t>(stream));
+  const size_t need = b200cp_conv2d_dense_fwd_workspace_bytes(&q);
+  if (!workspace || workspace_bytes < need)
+    return fail(B200CP_ERR_WORKSPACE, "b200cp_conv2d_dense_fwd: workspace of %zu bytes needed, %zu given", need,
+                workspace ? workspace_bytes : (size_t)0);
+  return conv_dense_launch(q, X, K, U, static_cast<float*>(workspace), static_cast<cudaStream_t>(stream));
 }
 
 size_t b200cp_cp4_rebuild_fwd_workspace_bytes(const b200cp_tensor_shape* s) {
   if (!s) return 0;
-  return (size_t)s->T * s->C * s->Y * s->X * sizeof(float);
+  return align_up((size_t)s->T * s->C * s->Y * s->X * sizeof(float), 256) + b200cp_conv2d_dense_fwd_workspace_bytes(s);
 }
 
 int b200cp_cp4_rebuild_fwd(const b200cp_tensor_shape* s, const float* X, const float* K0, const float* K1,
@@ -828,13 +845,15 @@ int b200cp_cp4_rebuild_fwd(const b200cp_tensor_shape* s, const float* X, const f
                            void* stream) {
   if (int rc = check_shape(s, "b200cp_cp4_rebuild_fwd")) return rc;
   if (int rc = check_ptrs("b200cp_cp4_rebuild_fwd", {X, K0, K1, KH, KW, U})) return rc;
-  if (!workspace || workspace_bytes < b200cp_cp4_rebuild_fwd_workspace_bytes(s))
-    return fail(B200CP_ERR_WORKSPACE, "b200cp_cp4_rebuild_fwd: workspace of %zu bytes needed, %zu given",
+  if (!workspace || workspace_bytes < b200cp_cp4_rebuild_fwd_workspace_bytes(s) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 15))
+    return fail(B200CP_ERR_WORKSPACE, "b200cp_cp4_rebuild_fwd: a 16-byte aligned workspace of %zu bytes is needed, %zu given",
                 b200cp_cp4_rebuild_fwd_workspace_bytes(s), workspace ? workspace_bytes : (size_t)0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* K = static_cast<float*>(workspace);
+  float* scratch = K + align_up((size_t)s->T * s->C * s->Y * s->X * sizeof(float), 256) / sizeof(float);
   if (int rc = cp4_recompose_launch(*s, K0, K1, KH, KW, K, st)) return rc;
-  return conv_dense_launch(*s, X, K, U, st);
+  return conv_dense_launch(*s, X, K, U, scratch, st);
 }
 
 int b200cp_rcp_recompose(int order, const int* cdims, const int* tdims, int R, int FH, int FW, const float* const* A,

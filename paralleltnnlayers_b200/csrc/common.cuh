@@ -232,7 +232,9 @@ int conv_gemm_tc_launch(int N, int T, int C, int H, int W, int FH, int FW, const
 // the reference's "rebuild" variants: dense conv2d forward with an undecomposed filter K [T][C][FH][FW]; recomposed
 // weights of the dense ([I][O]) and reshaped-CP ([T][C][FH][FW], S != nullptr) layers; Y = X M for the dense layer
 bool conv_dense_supported(const b200cp_tensor_shape& s);
-int conv_dense_launch(const b200cp_tensor_shape& s, const float* X, const float* K, float* U, cudaStream_t st);
+size_t conv_dense_scratch_floats(const b200cp_tensor_shape& s);
+int conv_dense_launch(const b200cp_tensor_shape& s, const float* X, const float* K, float* U, float* scratch,
+                      cudaStream_t st);
 int kron_recompose_launch(int order, const int* a, const int* b, int R, const float* const* F, const float* S, int taps,
                           float* Wout, cudaStream_t st);
 size_t dense_matmul_scratch_floats(int B, int I, int O);

@@ -8,10 +8,14 @@
 //
 //   U[n,t,h,w] = sum_{c,y,x} K[t,c,y,x] X[n,c,h+y-pad,w+x-pad]      (zero outside the image; H x W output)
 //
-// A CTA owns 64 output channels x 128 consecutive output pixels of one image.  Per chunk of 8 input channels it
-// stages the input rows those pixels touch (zero ring included) and, per filter row, the FW x 8 x 64 slice of the
-// filter split into hi / lo tf32 planes; a filter tap is then one k-step of 8 channels whose B operand is the staged
-// image shifted by (y, x).  Eight warps: 2 (halves of the 64 channels) x 4 (quarters of the 128 pixels).
+// A first pass rewrites the filter as hi / lo tf32 planes [chunk of 8 input channels][tap][T padded to 64][8], so that
+// a CTA's slice of a tap is 64 rows of 32 bytes and an A fragment is one ldmatrix.  A CTA owns 64 output channels x
+// 128 consecutive output pixels of one image.  Its work is a list of items (chunk of 8 input channels, group of at
+// most 9 filter taps); item i + 1 is
+// copied into the other half of a double buffer (cp.async: the image rows the pixels touch, zero ring included,
+// once per chunk; the filter slice per item) while item i is multiplied: a tap is one k-step of 8 channels whose B
+// operand is the staged image shifted by (y, x).  Eight warps: 2 (halves of the 64 channels) x 4 (quarters of the
+// 128 pixels).
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -21,20 +25,41 @@ namespace {
 constexpr int kTM = 64;    // output channels per CTA
 constexpr int kTP = 128;   // output pixels per CTA
 constexpr int kCK = 8;     // input channels per stage
-constexpr int kWS = 72;    // filter plane row: 64 output channels + 8 (bank shift of 8 per input channel)
+constexpr int kWS = 8;     // staged filter row: the 8 input channels of a chunk (one ldmatrix tile row per 16 bytes)
+constexpr int kTG = 9;     // filter taps per item
 constexpr int kThreads = 256;
+constexpr int kWBuf = kTG * kTM * kWS;   // floats of one hi (or lo) filter buffer
 
 struct DenseConvGeom {
   int N, C, H, W, T, FH, FW, pad, Wp, CS;  // Wp = staged row width, CS = staged floats per input channel
+  int TP, chunks, groups;                  // T padded to 64; chunks of 8 input channels; tap groups per chunk
+  size_t plane;                            // floats of one filter plane
 };
 
+// K [T][C][taps] -> hi / lo planes [chunk][tap][TP][8], zero where t >= T or c >= C
+__global__ void __launch_bounds__(256) dense_filter_split_kernel(const DenseConvGeom g, const float* __restrict__ K,
+                                                                 float* __restrict__ Wg) {
+  const int taps = g.FH * g.FW;
+  for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < g.plane; e += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(e % kCK);
+    size_t q = e / kCK;
+    const int t = (int)(q % g.TP);
+    q /= g.TP;
+    const int tap = (int)(q % taps), cc = (int)(q / taps) * kCK + c;
+    const float v = (t < g.T && cc < g.C) ? __ldg(K + ((size_t)t * g.C + cc) * taps + tap) : 0.f;
+    uint32_t hi, lo;
+    mma::split_tf32(v, hi, lo);
+    Wg[e] = __uint_as_float(hi);
+    Wg[g.plane + e] = __uint_as_float(lo);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 2)
-conv_dense_mma_kernel(const DenseConvGeom g, const float* __restrict__ X, const float* __restrict__ K,
+conv_dense_mma_kernel(const DenseConvGeom g, const float* __restrict__ X, const float* __restrict__ Wg,
                       float* __restrict__ U) {
   extern __shared__ __align__(16) float smem[];
-  float* Xs = smem;                          // [8][CS]: rows h_lo-pad .., columns -pad ..
-  float* Whi = Xs + kCK * g.CS;              // [FW][8][kWS]
-  float* Wlo = Whi + g.FW * kCK * kWS;
+  float* Xs = smem;                          // [2][8][CS]: rows h_lo-pad .., columns -pad ..
+  float* Ws = Xs + 2 * kCK * g.CS;           // [2][hi, lo][kTG][64][kWS]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
   const int wm = warp >> 2, wn = warp & 3;
   const int n = blockIdx.z, t0 = blockIdx.y * kTM, p0 = blockIdx.x * kTP;
@@ -42,7 +67,7 @@ conv_dense_mma_kernel(const DenseConvGeom g, const float* __restrict__ X, const 
   const int h_lo = p0 / g.W;
   const int h_hi = min(p0 + kTP - 1, HW - 1) / g.W;
   const int nrows = h_hi - h_lo + g.FH;
-  const int rowsz = nrows * g.Wp;
+  const int taps = g.FH * g.FW;
 
   int off[4];
 #pragma unroll
@@ -60,56 +85,91 @@ conv_dense_mma_kernel(const DenseConvGeom g, const float* __restrict__ X, const 
       for (int e = 0; e < 4; ++e) acc[mi][j][e] = 0.f;
 
   const float* Xn = X + (size_t)n * g.C * HW;
-  const int taps = g.FH * g.FW;
-  for (int c0 = 0; c0 < g.C; c0 += kCK) {
-    __syncthreads();   // the chunk before is consumed
-    for (int i = tid; i < kCK * rowsz; i += kThreads) {
-      const int c = i / rowsz, rem = i - c * rowsz;
-      const int r = rem / g.Wp, col = rem - r * g.Wp;
-      const int hi = h_lo - g.pad + r, wi = col - g.pad, cc = c0 + c;
-      float v = 0.f;
-      if (cc < g.C && hi >= 0 && hi < g.H && wi >= 0 && wi < g.W) v = __ldg(Xn + ((size_t)cc * g.H + hi) * g.W + wi);
-      Xs[c * g.CS + rem] = v;
-    }
-    for (int y = 0; y < g.FH; ++y) {
-      if (y) __syncthreads();   // the filter row before is consumed
-      for (int i = tid; i < kTM * kCK * g.FW; i += kThreads) {
-        const int x = i % g.FW, c = (i / g.FW) % kCK, t = i / (g.FW * kCK);
-        float v = 0.f;
-        if (t0 + t < g.T && c0 + c < g.C) v = __ldg(K + ((size_t)(t0 + t) * g.C + c0 + c) * taps + y * g.FW + x);
-        uint32_t hi, lo;
-        mma::split_tf32(v, hi, lo);
-        Whi[(x * kCK + c) * kWS + t] = __uint_as_float(hi);
-        Wlo[(x * kCK + c) * kWS + t] = __uint_as_float(lo);
-      }
-      __syncthreads();
-      for (int x = 0; x < g.FW; ++x) {
-        uint32_t ah[2][4], al[2][4];
-#pragma unroll
-        for (int mi = 0; mi < 2; ++mi) {
-          const int row = wm * 32 + mi * 16 + gq;
-          const float* h0 = Whi + (x * kCK + tq) * kWS + row;
-          const float* l0 = Wlo + (x * kCK + tq) * kWS + row;
-          ah[mi][0] = __float_as_uint(h0[0]);           ah[mi][1] = __float_as_uint(h0[8]);
-          ah[mi][2] = __float_as_uint(h0[4 * kWS]);     ah[mi][3] = __float_as_uint(h0[4 * kWS + 8]);
-          al[mi][0] = __float_as_uint(l0[0]);           al[mi][1] = __float_as_uint(l0[8]);
-          al[mi][2] = __float_as_uint(l0[4 * kWS]);     al[mi][3] = __float_as_uint(l0[4 * kWS + 8]);
+  const unsigned xs_s = (unsigned)__cvta_generic_to_shared(Xs), ws_s = (unsigned)__cvta_generic_to_shared(Ws);
+
+  auto load_item = [&](int item) {
+    const int chunk = item / g.groups, grp = item - chunk * g.groups;
+    if (grp == 0) {
+      const unsigned dst = xs_s + (unsigned)((chunk & 1) * kCK * g.CS) * 4u;
+      if (g.Wp < 40) {   // short rows: one element per thread and turn
+        const int rowsz = nrows * g.Wp;
+        for (int i = tid; i < kCK * rowsz; i += kThreads) {
+          const int c = i / rowsz, rem = i - c * rowsz;
+          const int r = rem / g.Wp, col = rem - r * g.Wp;
+          const int hi = h_lo - g.pad + r, wi = col - g.pad, cc = chunk * kCK + c;
+          const bool in = cc < g.C && hi >= 0 && hi < g.H && wi >= 0 && wi < g.W;
+          mma::cp_async4_s(dst + (unsigned)(c * g.CS + rem) * 4u, in ? Xn + ((size_t)cc * g.H + hi) * g.W + wi : Xn,
+                           in ? 4 : 0);
         }
-        const float* xb = Xs + tq * g.CS + y * g.Wp + x;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t bh[2], bl[2];
-          mma::split_tf32(xb[off[j]], bh[0], bl[0]);
-          mma::split_tf32(xb[off[j] + 4 * g.CS], bh[1], bl[1]);
-#pragma unroll
-          for (int mi = 0; mi < 2; ++mi) {
-            mma::mma_tf32(acc[mi][j], al[mi], bh);
-            mma::mma_tf32(acc[mi][j], ah[mi], bl);
-            mma::mma_tf32(acc[mi][j], ah[mi], bh);
-          }
+      } else
+      for (int row = warp; row < kCK * nrows; row += kThreads / 32) {   // long rows: a warp copies whole staged rows
+        const int c = row / nrows, r = row - c * nrows;
+        const int hi = h_lo - g.pad + r, cc = chunk * kCK + c;
+        const bool row_in = cc < g.C && hi >= 0 && hi < g.H;
+        const float* srow = Xn + ((size_t)cc * g.H + hi) * g.W - g.pad;
+        const unsigned drow = dst + (unsigned)(c * g.CS + r * g.Wp) * 4u;
+        for (int col = lane; col < g.Wp; col += 32) {
+          const bool in = row_in && col >= g.pad && col < g.W + g.pad;
+          mma::cp_async4_s(drow + (unsigned)col * 4u, in ? srow + col : Xn, in ? 4 : 0);
         }
       }
     }
+    const int tap0 = grp * kTG, nt = min(kTG, taps - tap0);
+    const float* src = Wg + ((size_t)(chunk * taps + tap0) * g.TP + t0) * kCK;
+    const unsigned dst = ws_s + (unsigned)((item & 1) * 2 * kWBuf) * 4u;
+    for (int i = tid; i < nt * kTM * 2; i += kThreads) {
+      const int tl = i / (kTM * 2), rem = i - tl * kTM * 2, t = rem >> 1, half = (rem & 1) * 4;
+      const float* sp = src + ((size_t)tl * g.TP + t) * kCK + half;
+      const unsigned d = dst + (unsigned)((tl * kTM + t) * kWS + half) * 4u;
+      mma::cp_async16_s(d, sp, 16);
+      mma::cp_async16_s(d + kWBuf * 4u, sp + g.plane, 16);
+    }
+  };
+
+  const int items = g.chunks * g.groups;
+  load_item(0);
+  mma::cp_async_commit();
+  for (int item = 0; item < items; ++item) {
+    if (item + 1 < items) load_item(item + 1);
+    mma::cp_async_commit();
+    mma::cp_async_wait<1>();
+    __syncthreads();
+    const int chunk = item / g.groups, grp = item - chunk * g.groups;
+    const float* Xc = Xs + (chunk & 1) * kCK * g.CS + tq * g.CS;
+    const float* Whi = Ws + (item & 1) * 2 * kWBuf;
+    const int tap0 = grp * kTG, nt = min(kTG, taps - tap0);
+    for (int tl = 0; tl < nt; ++tl) {
+      const int tap = tap0 + tl, y = tap / g.FW, x = tap - y * g.FW;
+      uint32_t ah[2][4], al[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) {
+        // tiles of one ldmatrix: (rows 0-7, k 0-3), (rows 8-15, k 0-3), (rows 0-7, k 4-7), (rows 8-15, k 4-7) = a0..a3
+        const float* h0 = Whi + (tl * kTM + wm * 32 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kWS + (lane >> 4) * 4;
+        mma::ldmatrix_x4(ah[mi], h0);
+        mma::ldmatrix_x4(al[mi], h0 + kWBuf);
+      }
+      const float* xb = Xc + y * g.Wp + x;
+      uint32_t bh[4][2], bl[4][2];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mma::split_tf32(xb[off[j]], bh[j][0], bl[j][0]);
+        mma::split_tf32(xb[off[j] + 4 * g.CS], bh[j][1], bl[j][1]);
+      }
+      // term-major: the three products of one accumulator are eight instructions apart
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) mma::mma_tf32_ordered(acc[mi][j], al[mi], bh[j]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) mma::mma_tf32_ordered(acc[mi][j], ah[mi], bl[j]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) mma::mma_tf32_ordered(acc[mi][j], ah[mi], bh[j]);
+    }
+    __syncthreads();   // the buffers of this item are free for item + 2
   }
 
   float* Un = U + (size_t)n * g.T * HW;
@@ -127,15 +187,19 @@ conv_dense_mma_kernel(const DenseConvGeom g, const float* __restrict__ X, const 
 }
 
 bool plan(const b200cp_tensor_shape& s, DenseConvGeom& g, size_t& smem) {
-  g = DenseConvGeom{(int)s.N, (int)s.C, (int)s.H, (int)s.W, (int)s.T, (int)s.Y, (int)s.X, (int)s.pad, 0, 0};
+  g = DenseConvGeom{(int)s.N, (int)s.C, (int)s.H, (int)s.W, (int)s.T, (int)s.Y, (int)s.X, (int)s.pad, 0, 0, 0, 0, 0, 0};
   g.Wp = g.W + g.FW - 1;
   const int span = std::min(g.H, (kTP - 2) / g.W + 2);      // image rows that 128 consecutive pixels can touch
   const long per = (long)(span + g.FH - 1) * g.Wp;
   long cs = per;
   while (cs % 32 != 8) ++cs;                                // 4 channels x 8 pixels of a B fragment: 32 banks
   g.CS = (int)cs;
-  smem = ((size_t)kCK * cs + 2 * (size_t)g.FW * kCK * kWS) * sizeof(float);
-  return smem <= 100 * 1024 && s.N <= 65535 && ceil_div(g.T, kTM) <= 65535;
+  g.TP = ceil_div(g.T, kTM) * kTM;
+  g.chunks = ceil_div(g.C, kCK);
+  g.groups = ceil_div(g.FH * g.FW, kTG);
+  g.plane = (size_t)g.chunks * g.FH * g.FW * kCK * g.TP;
+  smem = (2 * (size_t)kCK * cs + 4 * (size_t)kWBuf) * sizeof(float);
+  return smem <= 200 * 1024 && s.N <= 65535 && ceil_div(g.T, kTM) <= 65535;
 }
 
 // W[e] = sum_r prod_k F_k[i_k, o_k, r] (* S[tap, r]), modes flattened first-mode-slowest.  Dense layer: e = i * O + o
@@ -144,7 +208,7 @@ bool plan(const b200cp_tensor_shape& s, DenseConvGeom& g, size_t& smem) {
 struct ModeArgs {
   const float* F[4];
   int a[4], b[4];
-  int order, R, taps;
+  int order, R, taps, vec;   // vec: R % 4 == 0 and every factor on a 16-byte boundary
 };
 __global__ void __launch_bounds__(256) kron_recompose_kernel(const ModeArgs m, const float* __restrict__ S,
                                                              float* __restrict__ Wout, int I, int O) {
@@ -173,12 +237,28 @@ __global__ void __launch_bounds__(256) kron_recompose_kernel(const ModeArgs m, c
       }
     }
     float acc = 0.f;
-    for (int r = 0; r < m.R; ++r) {
-      float v = S ? S[tap * m.R + r] : 1.f;
+    if (m.vec) {   // every factor row starts on 16 bytes: four ranks per load
+      for (int r = 0; r < m.R; r += 4) {
+        float4 v = S ? __ldg(reinterpret_cast<const float4*>(S + tap * m.R + r)) : make_float4(1.f, 1.f, 1.f, 1.f);
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (k < m.order) v *= m.F[k][base[k] + r];
-      acc += v;
+        for (int k = 0; k < 4; ++k)
+          if (k < m.order) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(m.F[k] + base[k] + r));
+            v.x *= f.x; v.y *= f.y; v.z *= f.z; v.w *= f.w;
+          }
+        acc += v.x;   // rank order, as the scalar loop
+        acc += v.y;
+        acc += v.z;
+        acc += v.w;
+      }
+    } else {
+      for (int r = 0; r < m.R; ++r) {
+        float v = S ? S[tap * m.R + r] : 1.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (k < m.order) v *= m.F[k][base[k] + r];
+        acc += v;
+      }
     }
     Wout[e] = acc;
   }
@@ -230,6 +310,9 @@ int kron_recompose_launch(int order, const int* a, const int* b, int R, const fl
   if (R < 1 || taps < 1) return fail(B200CP_ERR_INVALID_ARG, "recompose: rank %d, taps %d", R, taps);
   if (I > 0x7fffffff || O > 0x7fffffff) return fail(B200CP_ERR_UNSUPPORTED, "recompose: more than 2^31 rows or columns");
   m.order = order; m.R = R; m.taps = S ? taps : 1;
+  uintptr_t bits = reinterpret_cast<uintptr_t>(S);
+  for (int k = 0; k < order; ++k) bits |= reinterpret_cast<uintptr_t>(F[k]);
+  m.vec = R % 4 == 0 && (bits & 15) == 0;
   const size_t total = I * O * (size_t)m.taps;
   const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 148 * 64);
   kron_recompose_kernel<<<blocks, 256, 0, st>>>(m, S, Wout, (int)I, (int)O);
@@ -243,16 +326,30 @@ bool conv_dense_supported(const b200cp_tensor_shape& s) {
   return plan(s, g, smem);
 }
 
-// U [N,T,H,W] = dense cross-correlation of X [N,C,H,W] with K [T,C,FH,FW], zero padding `pad` on the top / left
-int conv_dense_launch(const b200cp_tensor_shape& s, const float* X, const float* K, float* U, cudaStream_t st) {
+// floats of scratch: the hi / lo planes of the re-laid filter
+size_t conv_dense_scratch_floats(const b200cp_tensor_shape& s) {
+  DenseConvGeom g;
+  size_t smem;
+  plan(s, g, smem);
+  return 2 * g.plane;
+}
+
+// U [N,T,H,W] = dense cross-correlation of X [N,C,H,W] with K [T,C,FH,FW], zero padding `pad` on the top / left;
+// scratch: conv_dense_scratch_floats() floats, 16-byte aligned
+int conv_dense_launch(const b200cp_tensor_shape& s, const float* X, const float* K, float* U, float* scratch,
+                      cudaStream_t st) {
   DenseConvGeom g;
   size_t smem;
   if (!plan(s, g, smem))
     return fail(B200CP_ERR_UNSUPPORTED, "dense conv2d: staged rows need %zu bytes of shared memory (W=%u, filter %ux%u)",
                 smem, s.W, s.Y, s.X);
+  if (reinterpret_cast<uintptr_t>(scratch) & 15)
+    return fail(B200CP_ERR_INVALID_ARG, "dense conv2d: the workspace must be 16-byte aligned");
+  dense_filter_split_kernel<<<(unsigned)std::min<size_t>((g.plane + 255) / 256, 148 * 16), 256, 0, st>>>(g, K, scratch);
+  B200CP_LAUNCH_OK("dense_filter_split_kernel");
   B200CP_CUDA_OK(cudaFuncSetAttribute(conv_dense_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(ceil_div(g.H * g.W, kTP), ceil_div(g.T, kTM), g.N);
-  conv_dense_mma_kernel<<<grid, kThreads, smem, st>>>(g, X, K, U);
+  conv_dense_mma_kernel<<<grid, kThreads, smem, st>>>(g, X, scratch, U);
   B200CP_LAUNCH_OK("conv_dense_mma_kernel");
   return B200CP_OK;
 }

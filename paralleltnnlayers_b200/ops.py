@@ -469,7 +469,9 @@ def conv2d_dense_forward(Input, K, pad=1):
                      K.shape[3], 1, pad)
     U = torch.empty((s.N, s.T, s.H, s.W), device=Input.device, dtype=torch.float32)
     with torch.cuda.device(Input.device):
-        check(lib.b200cp_conv2d_dense_fwd(C.byref(s), _p(Input), _p(K), _p(U), _stream()))
+        wsb = lib.b200cp_conv2d_dense_fwd_workspace_bytes(C.byref(s))
+        ws = torch.empty(max(wsb, 4) // 4, device=Input.device, dtype=torch.float32)
+        check(lib.b200cp_conv2d_dense_fwd(C.byref(s), _p(Input), _p(K), _p(U), _p(ws), ws.numel() * 4, _stream()))
     return U
 
 

@@ -79,6 +79,10 @@ def sweep_cp4(P, reps, rows):
                 row["fwd_" + name] = timeit(lambda i: P.cp4_conv2d_forward(Xs[i % n], *K, 1, flags=fl), reps)
             except P.B200CPError:
                 row["fwd_" + name] = None      # the path does not take this shape
+        # the reference's comparison line: recomposed filter + ordinary conv2d (and the conv2d alone, filter kept)
+        row["fwd_rebuild"] = timeit(lambda i: P.cp4_conv2d_rebuild_forward(Xs[i % n], *K, 1), reps)
+        Kd = P.cp4recom(*K)
+        row["fwd_dense_conv"] = timeit(lambda i: P.conv2d_dense_forward(Xs[i % n], Kd, 1), reps)
         row["bwd_data"] = timeit(lambda i: P.cp4_conv2d_backward_data(dUs[i % n], *K, 1), reps)
         for name, fl in (("simt", P.PATH_SIMT), ("mma", P.PATH_MMA)):
             row["bwd_filter_" + name] = timeit(
@@ -103,6 +107,7 @@ def sweep_rcp(P, reps, rows):
     n = len(Xs)
     rows.append({"layer": "rcp", **{k: v for k, v in c.items()},
                  "fwd": timeit(lambda i: P.conv2d_rcp_fused_nchw(Xs[i % n], *A, S), reps),
+                 "fwd_rebuild": timeit(lambda i: P.conv2d_rcp_rebuild_nchw(Xs[i % n], *A, S), reps),
                  "bwd_data": timeit(lambda i: P.rcp_conv2d_backward(Xs[i % n], dVs[i % n], *A, S, need_dw=False), reps),
                  "bwd_factors": timeit(lambda i: P.rcp_conv2d_backward(Xs[i % n], dVs[i % n], *A, S, need_dx=False), reps),
                  "hbm_floor_us": 2 * X.numel() * 4 / 6.45e12 * 1e6})
@@ -120,6 +125,8 @@ def sweep_dense(P, reps, rows):
     reps = max(2, reps // 3)
     rows.append({"layer": "dense", **{k: v for k, v in c.items()},
                  "fwd": timeit(lambda i: P.dense_cp(Xs[i % n], *F), reps),
+                 "fwd_rebuild": timeit(lambda i: P.dense_cp_rebuild(Xs[i % n], *F), reps),
+                 "fwd_matmul": timeit(lambda i, M=P.dense_cp_recompose(*F): P.dense_matmul(Xs[i % n], M), reps),
                  "bwd_data": timeit(lambda i: P.dense_cp_backward(Xs[i % n], dYs[i % n], *F, need_dw=False), reps),
                  "bwd_factors": timeit(lambda i: P.dense_cp_backward(Xs[i % n], dYs[i % n], *F, need_dx=False), reps),
                  "hbm_floor_us": 2 * X.numel() * 4 / 6.45e12 * 1e6})
