@@ -102,8 +102,9 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
                      const float* __restrict__ KW, float* __restrict__ ws) {
   constexpr int RP = 16;
   extern __shared__ __align__(1024) uint8_t sm[];
-  float* Qs = reinterpret_cast<float*>(sm + g.oQ);    // [RP][PP] halo band of Q (kind 1 only)
-  float* Ps = reinterpret_cast<float*>(sm + g.oP);    // [RP][PP] halo band of P
+  // Two plane slots.  Kind 0 keeps P in the second one (the first is ring space from the start).  Kind 1 keeps P in
+  // the first and Q in the second: P is consumed first (the Q x P correlations), so the ring's first stages load
+  // while the stencil of Q still runs.
   float* Zs = reinterpret_cast<float*>(sm + g.oZ);    // [RP][ZP] Z (kind 0) or Qt (kind 1) on the band's own pixels
   float* Ws = reinterpret_cast<float*>(sm + g.oW);    // [9][RP] stencil weights, then [3][RP] KH, [3][RP] KW
   float* red = reinterpret_cast<float*>(sm + g.oRed); // [threads][9] spatial correlations, later the warps' channel sums
@@ -111,7 +112,8 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
   uint64_t* empty = full + kMaxStages;
   uint64_t* planes_full = empty + kMaxStages;
   uint64_t* planes_free = planes_full + 1;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(planes_free + 1);
+  uint64_t* first_free = planes_free + 1;             // kind 1: the first plane slot (P) is consumed
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(first_free + 1);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gq = lane >> 2, tq = lane & 3;
@@ -120,6 +122,8 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
   const int kind = (int)blockIdx.x < g.tiles ? 1 : 0;
   const int b = (int)blockIdx.x - (1 - kind) * g.tiles;
   const int band = b % g.bands, n = b / g.bands;
+  float* Ps = reinterpret_cast<float*>(sm + (kind ? g.oQ : g.oP));   // [RP][PP] halo band of P
+  float* Qs = reinterpret_cast<float*>(sm + g.oP);                   // [RP][PP] halo band of Q (kind 1 only)
   const int h0 = band * g.TH;
   const int W = g.W, HW = g.H * g.W, PP = g.PP, ZP = g.ZP;
   const int S = g.stages;
@@ -146,6 +150,7 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
     }
     mbar_init(planes_full, 1);
     mbar_init(planes_free, kCons);
+    mbar_init(first_free, kCons);
     *abort_flag = 0;
     fence_barrier_init();
     tc::tma_prefetch_desc(kind ? &mapX : &mapU);
@@ -167,17 +172,23 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
         if (kind) bulk_load(Qs + lane * PP + ra * W, Qg + off + (size_t)lane * HW, bytes, planes_full);
       }
     }
-    // the ring: stage s at s * stage_bytes from the start of the planes' space.  Kind 0 never loads Q, so the stages
-    // inside Q's space are free from the start; the others wait until the stencil has consumed the planes.
+    // the ring: stage s at s * stage_bytes from the start of the planes' space.  The stages inside the first plane
+    // slot are free from the start for kind 0 (it has no second plane) and once the correlations have consumed P for
+    // kind 1; the others wait until the stencil has consumed the planes.
     const CUtensorMap* map = kind ? &mapX : &mapU;
-    const int free_now = kind ? 0 : (g.oP - g.oQ) / g.stage_bytes;
-    bool planes_done = false;
+    const int nfirst = (g.oP - g.oQ) / g.stage_bytes;
+    bool first_done = kind == 0, planes_done = false;
     int slot = 0;
     uint32_t par = 1;
     for (int s = 0; s < g.nchunk; ++s) {
       if (s >= S) {
         if (!wait_or_abort(&empty[slot], par, abort_flag)) break;
-      } else if (slot >= free_now && !planes_done) {
+      } else if (slot < nfirst) {
+        if (!first_done) {
+          if (!wait_or_abort(first_free, 0, abort_flag)) break;
+          first_done = true;
+        }
+      } else if (!planes_done) {
         if (!wait_or_abort(planes_free, 0, abort_flag)) break;
         planes_done = true;
       }
@@ -242,67 +253,80 @@ cp4_grad_band_kernel(const GradGeom g, const __grid_constant__ CUtensorMap mapU,
       for (int t = 0; t < 9; ++t) w[t] = Ws[t * RP + r];
       const float* src = kind ? Qs : Ps;
       constexpr int STEP = NTC / RP;
-      int oy = (tid / RP) / spr, sx = (tid / RP) % spr;
       const int dy_step = STEP / spr, dx_step = STEP % spr;
-      for (int it = tid / RP; it < nitems; it += STEP) {
-        const int x0 = sx * 8;
-        const bool hi_ok = x0 + 4 < W, lft = x0 > 0, rgt = x0 + 8 < W;
-        float z[8];
+      // pass 0 (kind 1 only): the nine Q x P correlations, after which P's slot joins the ring; pass 1: the stencil
+      for (int pass = kind ? 0 : 1; pass < 2; ++pass) {
+        int oy = (tid / RP) / spr, sx = (tid / RP) % spr;
+        for (int it = tid / RP; it < nitems; it += STEP) {
+          const int x0 = sx * 8;
+          const bool hi_ok = x0 + 4 < W, lft = x0 > 0, rgt = x0 + 8 < W;
+          if (pass) {
+            float z[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) z[j] = 0.f;
-        const float* pr = src + r * PP + oy * W + x0;
+            for (int j = 0; j < 8; ++j) z[j] = 0.f;
+            const float* pr = src + r * PP + oy * W + x0;
 #pragma unroll
-        for (int dy = 0; dy < 3; ++dy) {
-          float v[10];
-          const float4 a = *reinterpret_cast<const float4*>(pr);
-          const float4 c = hi_ok ? *reinterpret_cast<const float4*>(pr + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-          v[0] = lft ? pr[-1] : 0.f;
-          v[9] = rgt ? pr[8] : 0.f;
-          v[1] = a.x; v[2] = a.y; v[3] = a.z; v[4] = a.w;
-          v[5] = c.x; v[6] = c.y; v[7] = c.z; v[8] = c.w;
-          pr += W;
+            for (int dy = 0; dy < 3; ++dy) {
+              float v[10];
+              const float4 a = *reinterpret_cast<const float4*>(pr);
+              const float4 c = hi_ok ? *reinterpret_cast<const float4*>(pr + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+              v[0] = lft ? pr[-1] : 0.f;
+              v[9] = rgt ? pr[8] : 0.f;
+              v[1] = a.x; v[2] = a.y; v[3] = a.z; v[4] = a.w;
+              v[5] = c.x; v[6] = c.y; v[7] = c.z; v[8] = c.w;
+              pr += W;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            z[j] = fmaf(w[dy * 3 + 0], v[j], z[j]);
-            z[j] = fmaf(w[dy * 3 + 1], v[j + 1], z[j]);
-            z[j] = fmaf(w[dy * 3 + 2], v[j + 2], z[j]);
-          }
-        }
-        float* zd = Zs + r * ZP + oy * W + x0;
-        *reinterpret_cast<float4*>(zd) = make_float4(z[0], z[1], z[2], z[3]);
-        if (hi_ok) *reinterpret_cast<float4*>(zd + 4) = make_float4(z[4], z[5], z[6], z[7]);
-        if (kind) {
-          // spatial factors: the nine correlations S[dy][dx] = sum_px Q[px] P[px + (dy-1, dx-1)] of the strip; the
-          // factor gradients are their contractions with the other factor (dKH[i] = sum_j KW[j] S[i][j], dKW[j] =
-          // sum_i KH[i] S[i][j]), formed once per CTA
-          const float* qc = Qs + r * PP + (oy + 1) * W + x0;
-          const float4 qa = *reinterpret_cast<const float4*>(qc);
-          const float4 qb = hi_ok ? *reinterpret_cast<const float4*>(qc + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-          const float q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-          const float* pp = Ps + r * PP + oy * W + x0;
+              for (int j = 0; j < 8; ++j) {
+                z[j] = fmaf(w[dy * 3 + 0], v[j], z[j]);
+                z[j] = fmaf(w[dy * 3 + 1], v[j + 1], z[j]);
+                z[j] = fmaf(w[dy * 3 + 2], v[j + 2], z[j]);
+              }
+            }
+            float* zd = Zs + r * ZP + oy * W + x0;
+            *reinterpret_cast<float4*>(zd) = make_float4(z[0], z[1], z[2], z[3]);
+            if (hi_ok) *reinterpret_cast<float4*>(zd + 4) = make_float4(z[4], z[5], z[6], z[7]);
+          } else {
+            // spatial factors: the nine correlations S[dy][dx] = sum_px Q[px] P[px + (dy-1, dx-1)] of the strip; the
+            // factor gradients are their contractions with the other factor (dKH[i] = sum_j KW[j] S[i][j], dKW[j] =
+            // sum_i KH[i] S[i][j]), formed once per CTA
+            const float* qc = Qs + r * PP + (oy + 1) * W + x0;
+            const float4 qa = *reinterpret_cast<const float4*>(qc);
+            const float4 qb = hi_ok ? *reinterpret_cast<const float4*>(qc + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            const float* pp = Ps + r * PP + oy * W + x0;
 #pragma unroll
-          for (int dy = 0; dy < 3; ++dy) {
-            float v[10];
-            const float4 a = *reinterpret_cast<const float4*>(pp);
-            const float4 c = hi_ok ? *reinterpret_cast<const float4*>(pp + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            v[0] = lft ? pp[-1] : 0.f;
-            v[9] = rgt ? pp[8] : 0.f;
-            v[1] = a.x; v[2] = a.y; v[3] = a.z; v[4] = a.w;
-            v[5] = c.x; v[6] = c.y; v[7] = c.z; v[8] = c.w;
-            pp += W;
+            for (int dy = 0; dy < 3; ++dy) {
+              float v[10];
+              const float4 a = *reinterpret_cast<const float4*>(pp);
+              const float4 c = hi_ok ? *reinterpret_cast<const float4*>(pp + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+              v[0] = lft ? pp[-1] : 0.f;
+              v[9] = rgt ? pp[8] : 0.f;
+              v[1] = a.x; v[2] = a.y; v[3] = a.z; v[4] = a.w;
+              v[5] = c.x; v[6] = c.y; v[7] = c.z; v[8] = c.w;
+              pp += W;
 #pragma unroll
-            for (int dx = 0; dx < 3; ++dx) {
-              float t = 0.f;
+              for (int dx = 0; dx < 3; ++dx) {
+                float t = 0.f;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) t = fmaf(q[j], v[j + dx], t);
-              sp[dy * 3 + dx] += t;
+                for (int j = 0; j < 8; ++j) t = fmaf(q[j], v[j + dx], t);
+                sp[dy * 3 + dx] += t;
+              }
             }
           }
+          oy += dy_step;
+          sx += dx_step;
+          if (sx >= spr) { sx -= spr; ++oy; }
         }
-        oy += dy_step;
-        sx += dx_step;
-        if (sx >= spr) { sx -= spr; ++oy; }
+        if (pass == 0) {
+          tc::fence_proxy_async();   // this thread's zero fill of P's slot is ordered before the bulk copies that reuse it
+          __syncwarp();
+          if (lane == 0) mbar_arrive(first_free);
+        }
       }
+    }
+    if (kind && !ok) {   // the producer may be waiting for P's slot
+      __syncwarp();
+      if (lane == 0) mbar_arrive(first_free);
     }
     if (kind) {
 #pragma unroll
