@@ -54,6 +54,8 @@ __global__ void __launch_bounds__(256) dense_filter_split_kernel(const DenseConv
   }
 }
 
+// F3: 3 x 3 filter -- one item per channel chunk, the nine taps unrolled with constant offsets
+template <bool F3>
 __global__ void __launch_bounds__(kThreads, 2)
 conv_dense_mma_kernel(const DenseConvGeom g, const float* __restrict__ X, const float* __restrict__ Wg,
                       float* __restrict__ U) {
@@ -118,9 +120,11 @@ conv_dense_mma_kernel(const DenseConvGeom g, const float* __restrict__ X, const 
     const float* src = Wg + ((size_t)(chunk * taps + tap0) * g.TP + t0) * kCK;
     const unsigned dst = ws_s + (unsigned)((item & 1) * 2 * kWBuf) * 4u;
     for (int i = tid; i < nt * kTM * 2; i += kThreads) {
-      const int tl = i / (kTM * 2), rem = i - tl * kTM * 2, t = rem >> 1, half = (rem & 1) * 4;
-      const float* sp = src + ((size_t)tl * g.TP + t) * kCK + half;
-      const unsigned d = dst + (unsigned)((tl * kTM + t) * kWS + half) * 4u;
+      const int tl = i / (kTM * 2), rem = i - tl * kTM * 2, t = rem >> 1, half = rem & 1;
+      const float* sp = src + ((size_t)tl * g.TP + t) * kCK + half * 4;
+      // rows t and t + 4 of an ldmatrix tile would meet on the same banks: the two 16-byte pieces of a row swap places
+      // in every second group of four rows
+      const unsigned d = dst + (unsigned)((tl * kTM + t) * kWS + ((half ^ (t >> 2)) & 1) * 4) * 4u;
       mma::cp_async16_s(d, sp, 16);
       mma::cp_async16_s(d + kWBuf * 4u, sp + g.plane, 16);
     }
@@ -137,14 +141,18 @@ conv_dense_mma_kernel(const DenseConvGeom g, const float* __restrict__ X, const 
     const int chunk = item / g.groups, grp = item - chunk * g.groups;
     const float* Xc = Xs + (chunk & 1) * kCK * g.CS + tq * g.CS;
     const float* Whi = Ws + (item & 1) * 2 * kWBuf;
-    const int tap0 = grp * kTG, nt = min(kTG, taps - tap0);
-    for (int tl = 0; tl < nt; ++tl) {
-      const int tap = tap0 + tl, y = tap / g.FW, x = tap - y * g.FW;
+    const int tap0 = grp * kTG, nt = F3 ? 9 : min(kTG, taps - tap0);
+    // ldmatrix lane address: tiles (rows 0-7, k 0-3), (rows 8-15, k 0-3), (rows 0-7, k 4-7), (rows 8-15, k 4-7) = a0..a3
+    const float* wl = Whi + (wm * 32 + (lane & 7) + ((lane >> 3) & 1) * 8) * kWS + (((lane >> 4) ^ (lane >> 2)) & 1) * 4;
+#pragma unroll
+    for (int tl = 0; tl < (F3 ? 9 : kTG); ++tl) {
+      if (!F3 && tl >= nt) break;
+      int y, x;
+      if (F3) { y = tl / 3; x = tl % 3; } else { const int tap = tap0 + tl; y = tap / g.FW; x = tap - y * g.FW; }
       uint32_t ah[2][4], al[2][4];
 #pragma unroll
       for (int mi = 0; mi < 2; ++mi) {
-        // tiles of one ldmatrix: (rows 0-7, k 0-3), (rows 8-15, k 0-3), (rows 0-7, k 4-7), (rows 8-15, k 4-7) = a0..a3
-        const float* h0 = Whi + (tl * kTM + wm * 32 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kWS + (lane >> 4) * 4;
+        const float* h0 = wl + (tl * kTM + mi * 16) * kWS;
         mma::ldmatrix_x4(ah[mi], h0);
         mma::ldmatrix_x4(al[mi], h0 + kWBuf);
       }
@@ -347,9 +355,14 @@ int conv_dense_launch(const b200cp_tensor_shape& s, const float* X, const float*
     return fail(B200CP_ERR_INVALID_ARG, "dense conv2d: the workspace must be 16-byte aligned");
   dense_filter_split_kernel<<<(unsigned)std::min<size_t>((g.plane + 255) / 256, 148 * 16), 256, 0, st>>>(g, K, scratch);
   B200CP_LAUNCH_OK("dense_filter_split_kernel");
-  B200CP_CUDA_OK(cudaFuncSetAttribute(conv_dense_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(ceil_div(g.H * g.W, kTP), ceil_div(g.T, kTM), g.N);
-  conv_dense_mma_kernel<<<grid, kThreads, smem, st>>>(g, X, scratch, U);
+  if (g.FH == 3 && g.FW == 3) {
+    B200CP_CUDA_OK(cudaFuncSetAttribute(conv_dense_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    conv_dense_mma_kernel<true><<<grid, kThreads, smem, st>>>(g, X, scratch, U);
+  } else {
+    B200CP_CUDA_OK(cudaFuncSetAttribute(conv_dense_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    conv_dense_mma_kernel<false><<<grid, kThreads, smem, st>>>(g, X, scratch, U);
+  }
   B200CP_LAUNCH_OK("conv_dense_mma_kernel");
   return B200CP_OK;
 }
