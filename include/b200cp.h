@@ -224,9 +224,12 @@ int b200cp_cp4_rebuild_fwd(const b200cp_tensor_shape* s, const float* X, const f
 int b200cp_rcp_recompose(int order, const int* cdims, const int* tdims, int R, int FH, int FW, const float* const* A,
                          const float* S, float* K, void* stream);
 
-/* M[i,o] = sum_r prod_k F_k[i_k,o_k,r], i and o flattened first-mode-slowest (test/benchmark_dense_cp.py:43-44). */
+/* M[i,o] = sum_r prod_k F_k[i_k,o_k,r], i and o flattened first-mode-slowest (test/benchmark_dense_cp.py:43-44).
+ * With the workspace the two halves of the modes are multiplied out first and M is their rank-wise outer product;
+ * without one (NULL) every element is formed from all factors, which is several times slower for large M. */
+size_t b200cp_dense_recompose_workspace_bytes(int order, const int* idims, const int* odims, int R);
 int b200cp_dense_recompose(int order, const int* idims, const int* odims, int R, const float* const* F, float* M,
-                           void* stream);
+                           void* workspace, size_t workspace_bytes, void* stream);
 
 /* Y[b,o] = sum_i X[b,i] M[i,o] (test/benchmark_dense_cp.py:45-48) with fp32-grade results: tcgen05 with three tf32
  * terms where B, I, O fill its tiles, CUDA cores otherwise. */

@@ -73,7 +73,8 @@ def _load():
         "b200cp_cp4_rebuild_fwd_workspace_bytes": (sz, [sp]),
         "b200cp_cp4_rebuild_fwd": (i, [sp, fp, fp, fp, fp, fp, fp, vp, sz, vp]),
         "b200cp_rcp_recompose": (i, [i, ip, ip, i, i, i, pp, fp, fp, vp]),
-        "b200cp_dense_recompose": (i, [i, ip, ip, i, pp, fp, vp]),
+        "b200cp_dense_recompose_workspace_bytes": (sz, [i, ip, ip, i]),
+        "b200cp_dense_recompose": (i, [i, ip, ip, i, pp, fp, vp, sz, vp]),
         "b200cp_dense_matmul_workspace_bytes": (sz, [i, i, i]),
         "b200cp_dense_matmul": (i, [i, i, i, fp, fp, fp, vp, sz, vp]),
         "b200cp_dense_bwd_workspace_bytes": (sz, [i, i, ip, ip, i, i]),

@@ -864,11 +864,20 @@ int b200cp_rcp_recompose(int order, const int* cdims, const int* tdims, int R, i
   return kron_recompose_launch(order, cdims, tdims, R, A, S, FH * FW, K, static_cast<cudaStream_t>(stream));
 }
 
+size_t b200cp_dense_recompose_workspace_bytes(int order, const int* idims, const int* odims, int R) {
+  if (order < 1 || order > 4 || !idims || !odims || R < 1) return 0;
+  return dense_recompose_scratch_floats(order, idims, odims, R) * sizeof(float);
+}
+
 int b200cp_dense_recompose(int order, const int* idims, const int* odims, int R, const float* const* F, float* M,
-                           void* stream) {
+                           void* workspace, size_t workspace_bytes, void* stream) {
   if (int rc = check_modes("b200cp_dense_recompose", order, idims, odims, F)) return rc;
   if (int rc = check_ptrs("b200cp_dense_recompose", {M})) return rc;
-  return kron_recompose_launch(order, idims, odims, R, F, nullptr, 1, M, static_cast<cudaStream_t>(stream));
+  // without the workspace (or with one that is too small) the direct kernel runs: every element from all factors
+  const size_t need = b200cp_dense_recompose_workspace_bytes(order, idims, odims, R);
+  const bool two_stage = need && workspace && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 15);
+  return dense_recompose_launch(order, idims, odims, R, F, M, two_stage ? static_cast<float*>(workspace) : nullptr,
+                                static_cast<cudaStream_t>(stream));
 }
 
 size_t b200cp_dense_matmul_workspace_bytes(int B, int I, int O) {

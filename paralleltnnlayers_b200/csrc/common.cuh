@@ -237,6 +237,9 @@ int conv_dense_launch(const b200cp_tensor_shape& s, const float* X, const float*
                       cudaStream_t st);
 int kron_recompose_launch(int order, const int* a, const int* b, int R, const float* const* F, const float* S, int taps,
                           float* Wout, cudaStream_t st);
+size_t dense_recompose_scratch_floats(int order, const int* a, const int* b, int R);
+int dense_recompose_launch(int order, const int* a, const int* b, int R, const float* const* F, float* M, float* scratch,
+                           cudaStream_t st);
 size_t dense_matmul_scratch_floats(int B, int I, int O);
 int dense_matmul_launch(int B, int I, int O, const float* X, const float* M, float* Y, float* scratch, cudaStream_t st);
 // G[e] = sum over splits of P[split][e], in split order

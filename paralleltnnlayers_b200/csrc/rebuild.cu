@@ -272,6 +272,80 @@ __global__ void __launch_bounds__(256) kron_recompose_kernel(const ModeArgs m, c
   }
 }
 
+// ---- dense layer, two or more modes: M = sum_r GA_r (x) GB_r with GA = the product of the first half of the modes,
+// GB = the second half.  The half products are small ([IA][OA][R] and [IB][OB][R]); the outer product then costs one
+// multiply-add per rank and element of M instead of one per rank, mode and element.
+__global__ void __launch_bounds__(256) kron_half_kernel(const ModeArgs m, int k0, int k1, float* __restrict__ G, int IH,
+                                                        int OH) {
+  const size_t total = (size_t)IH * OH * m.R;
+  for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(e % m.R);
+    size_t q = e / m.R;
+    int o = (int)(q % OH), i = (int)(q / OH);
+    float v = 1.f;
+    for (int k = k1 - 1; k >= k0; --k) {
+      const int ik = i % m.a[k], ok = o % m.b[k];
+      i /= m.a[k];
+      o /= m.b[k];
+      v *= __ldg(m.F[k] + (size_t)(ik * m.b[k] + ok) * m.R + r);
+    }
+    G[e] = v;
+  }
+}
+
+constexpr int kOutIB = 4, kOutOA = 8, kOutOB = 64, kOutR = 32;
+// M[(iA * IB + iB)][(oA * OB + oB)] = sum_r GA[iA][oA][r] GB[iB][oB][r], ranks added in order.
+// grid = (oA blocks * iB blocks, IA); 256 threads: thread = (oB within 64, oA pair); 2 oA x 4 iB outputs per thread.
+__global__ void __launch_bounds__(256) kron_outer_kernel(const float* __restrict__ GA, const float* __restrict__ GB,
+                                                         float* __restrict__ M, int IA, int OA, int IB, int OB, int R) {
+  __shared__ float sa[kOutOA][kOutR];
+  __shared__ float sb[kOutIB][kOutOB][kOutR + 1];
+  const int nib = (IB + kOutIB - 1) / kOutIB;
+  const int iA = blockIdx.y, ib0 = ((int)blockIdx.x % nib) * kOutIB, oa0 = ((int)blockIdx.x / nib) * kOutOA;
+  const int tid = threadIdx.x, obl = tid % kOutOB, oq = tid / kOutOB;
+  for (int ob0 = 0; ob0 < OB; ob0 += kOutOB) {
+    float acc[2][kOutIB];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int v = 0; v < kOutIB; ++v) acc[u][v] = 0.f;
+    for (int r0 = 0; r0 < R; r0 += kOutR) {
+      __syncthreads();
+      for (int i = tid; i < kOutOA * kOutR; i += 256) {
+        const int oa = i / kOutR, r = i % kOutR;
+        sa[oa][r] = (oa0 + oa < OA && r0 + r < R) ? __ldg(GA + ((size_t)iA * OA + oa0 + oa) * R + r0 + r) : 0.f;
+      }
+      for (int i = tid; i < kOutIB * kOutOB * kOutR; i += 256) {
+        const int r = i % kOutR, ob = (i / kOutR) % kOutOB, ib = i / (kOutR * kOutOB);
+        sb[ib][ob][r] = (ib0 + ib < IB && ob0 + ob < OB && r0 + r < R)
+                            ? __ldg(GB + ((size_t)(ib0 + ib) * OB + ob0 + ob) * R + r0 + r) : 0.f;
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int r = 0; r < kOutR; ++r) {
+        const float a0 = sa[oq][r], a1 = sa[oq + 4][r];
+#pragma unroll
+        for (int v = 0; v < kOutIB; ++v) {
+          const float b = sb[v][obl][r];
+          acc[0][v] = fmaf(a0, b, acc[0][v]);
+          acc[1][v] = fmaf(a1, b, acc[1][v]);
+        }
+      }
+    }
+    const int ob = ob0 + obl;
+    if (ob < OB) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int oa = oa0 + oq + 4 * u;
+        if (oa >= OA) continue;
+#pragma unroll
+        for (int v = 0; v < kOutIB; ++v)
+          if (ib0 + v < IB) M[((size_t)iA * IB + ib0 + v) * ((size_t)OA * OB) + (size_t)oa * OB + ob] = acc[u][v];
+      }
+    }
+  }
+}
+
 // dst [cols][rows] = src [rows][cols]^T, 32 x 32 tiles through shared memory; grid = (col tiles, row tiles), block (32, 8)
 __global__ void __launch_bounds__(256) transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows,
                                                         int cols) {
@@ -325,6 +399,45 @@ int kron_recompose_launch(int order, const int* a, const int* b, int R, const fl
   const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, 148 * 64);
   kron_recompose_kernel<<<blocks, 256, 0, st>>>(m, S, Wout, (int)I, (int)O);
   B200CP_LAUNCH_OK("kron_recompose_kernel");
+  return B200CP_OK;
+}
+
+// floats of scratch for the two half products of dense_recompose_launch (0: the direct kernel is used)
+size_t dense_recompose_scratch_floats(int order, const int* a, const int* b, int R) {
+  if (order < 2) return 0;
+  const int h = (order + 1) / 2;
+  size_t A = 1, B = 1;
+  for (int k = 0; k < order; ++k) (k < h ? A : B) *= (size_t)a[k] * b[k];
+  return align_up(A * R, 64) + align_up(B * R, 64);
+}
+
+// M [I][O] of the dense layer; with a scratch of dense_recompose_scratch_floats() floats the two-stage form runs
+int dense_recompose_launch(int order, const int* a, const int* b, int R, const float* const* F, float* M, float* scratch,
+                           cudaStream_t st) {
+  if (order < 2 || scratch == nullptr) return kron_recompose_launch(order, a, b, R, F, nullptr, 1, M, st);
+  ModeArgs m{};
+  const int h = (order + 1) / 2;
+  size_t IA = 1, OA = 1, IB = 1, OB = 1;
+  for (int k = 0; k < order; ++k) {
+    m.F[k] = F[k]; m.a[k] = a[k]; m.b[k] = b[k];
+    if (a[k] < 1 || b[k] < 1) return fail(B200CP_ERR_INVALID_ARG, "recompose: mode %d has size %d x %d", k, a[k], b[k]);
+    (k < h ? IA : IB) *= (size_t)a[k];
+    (k < h ? OA : OB) *= (size_t)b[k];
+  }
+  if (R < 1) return fail(B200CP_ERR_INVALID_ARG, "recompose: rank %d", R);
+  if (IA * IB > 0x7fffffff || OA * OB > 0x7fffffff || IA > 65535)
+    return fail(B200CP_ERR_UNSUPPORTED, "recompose: more than 2^31 rows or columns");
+  m.order = order; m.R = R; m.taps = 1;
+  float* GA = scratch;
+  float* GB = scratch + align_up(IA * OA * R, 64);
+  const size_t na = IA * OA * R, nb = IB * OB * R;
+  kron_half_kernel<<<(unsigned)std::min<size_t>((na + 255) / 256, 148 * 16), 256, 0, st>>>(m, 0, h, GA, (int)IA, (int)OA);
+  B200CP_LAUNCH_OK("kron_half_kernel");
+  kron_half_kernel<<<(unsigned)std::min<size_t>((nb + 255) / 256, 148 * 16), 256, 0, st>>>(m, h, order, GB, (int)IB, (int)OB);
+  B200CP_LAUNCH_OK("kron_half_kernel");
+  dim3 grid((unsigned)(ceil_div((int)OA, kOutOA) * ceil_div((int)IB, kOutIB)), (unsigned)IA);
+  kron_outer_kernel<<<grid, 256, 0, st>>>(GA, GB, M, (int)IA, (int)OA, (int)IB, (int)OB, R);
+  B200CP_LAUNCH_OK("kron_outer_kernel");
   return B200CP_OK;
 }
 

@@ -526,8 +526,11 @@ def dense_cp_recompose(*kernels):
         O *= b
     M = torch.empty((I, O), device=Fk[0].device, dtype=torch.float32)
     with torch.cuda.device(M.device):
+        wsb = lib.b200cp_dense_recompose_workspace_bytes(len(Fk), int_array(idims), int_array(odims), R)
+        ws = torch.empty(max(wsb, 4) // 4, device=M.device, dtype=torch.float32)
         check(lib.b200cp_dense_recompose(len(Fk), int_array(idims), int_array(odims), R,
-                                         ptr_array([f.data_ptr() for f in Fk]), _p(M), _stream()))
+                                         ptr_array([f.data_ptr() for f in Fk]), _p(M), _p(ws), ws.numel() * 4,
+                                         _stream()))
     return M
 
 
