@@ -371,6 +371,7 @@ int b200cp_allclose_count(const float* A, const float* B, size_t n, float tolera
 // the factor gradients are computed from those, without contracting the channels a second time.
 // (the two switches are read once, when the library is loaded)
 static const bool g_step_no_share = getenv("B200CP_STEP_NO_SHARE") != nullptr;
+static const bool g_step_no_slices = getenv("B200CP_STEP_NO_SLICES") != nullptr;   // ranks > 16: the tile gradient kernels
 static const bool g_step_no_fork = getenv("B200CP_STEP_NO_FORK") != nullptr;
 static bool step_shares_planes(const b200cp_tensor_shape* s, int flags) {
   const int path = path_of(flags);
@@ -497,6 +498,31 @@ static int cp4_step_impl(const b200cp_tensor_shape* s, const float* X, const flo
       return B200CP_OK;
     }
   }
+  if (s->Rank > 16 && exchange == nullptr && !g_step_no_slices) {
+    // larger ranks: the gradient band kernel once per slice of 16 ranks (each slice streams X and dU again, which
+    // still beats the tile kernels that contract the planes' ranks in one pass)
+    Cp4BwdFilterArgs b = a;
+    b.r0 = 0;
+    b.R = 16;
+    if (cp4_grad_band_supported(b) && a.ws_bytes >= cp4_grad_band_workspace(*s)) {
+      rejoin.join();   // both rank planes are complete before the first slice
+      bool taken = true;
+      for (unsigned r0 = 0; r0 < s->Rank && taken; r0 += 16) {
+        b.r0 = (int)r0;
+        b.R = (int)std::min(16u, s->Rank - r0);
+        bool done = false;
+        if (int rc = cp4_grad_band_launch(b, P, Q, st, &done, /*after_own_kernel=*/r0 > 0, nullptr)) return rc;
+        if (!done && r0 > 0) return fail(B200CP_ERR_UNSUPPORTED, "cp4 step: the gradient kernel took rank slice 0 but not %u", r0);
+        taken = done;
+      }
+      if (taken) return B200CP_OK;
+      if (fork) {   // not a shape for the band kernel after all: fork again for the two-branch path below
+        B200CP_CUDA_OK(cudaEventRecord(fk->fork, st));
+        B200CP_CUDA_OK(cudaStreamWaitEvent(fk->side, fk->fork, 0));
+        rejoin.joined = false;
+      }
+    }
+  }
   if (fork && s->Rank <= 64) {
     // the gradient kernel in two halves, also side by side: the dK0 half follows the forward on the caller's
     // stream, the dK1 / spatial half follows backward-data on the side stream once the forward's plane is there
@@ -606,12 +632,19 @@ int b200cp_cp4_bwd_filter_saved(const b200cp_tensor_shape* s, const float* X, co
   a.Rs = s->Rank;
   a.X = X; a.dU = dU; a.KH = KH; a.KW = KW; a.dK = dK_packed;
   a.ws = workspace; a.ws_bytes = workspace_bytes;
-  if (s->Rank <= 16) {
-    a.r0 = 0;
-    a.R = (int)s->Rank;
-    bool done = false;
-    if (int rc = cp4_grad_band_launch(a, P, Q, static_cast<cudaStream_t>(stream), &done)) return rc;
-    if (done) return B200CP_OK;
+  if (s->Rank <= 16 || !g_step_no_slices) {
+    // the gradient band kernel, in slices of 16 ranks where there are more
+    bool taken = true;
+    for (unsigned r0 = 0; r0 < s->Rank && taken; r0 += 16) {
+      a.r0 = (int)r0;
+      a.R = (int)std::min(16u, s->Rank - r0);
+      bool done = false;
+      if (int rc = cp4_grad_band_launch(a, P, Q, static_cast<cudaStream_t>(stream), &done, /*after_own_kernel=*/r0 > 0)) return rc;
+      if (!done && r0 > 0)
+        return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp4_bwd_filter_saved: the gradient kernel took rank slice 0 but not %u", r0);
+      taken = done;
+    }
+    if (taken) return B200CP_OK;
   }
   for (unsigned r0 = 0; r0 < s->Rank; r0 += 64) {
     a.r0 = r0;

@@ -593,17 +593,18 @@ bool cp4_grad_band_supported(const Cp4BwdFilterArgs& a) {
 }
 
 size_t cp4_grad_band_workspace(const b200cp_tensor_shape& s) {
-  if (s.Y != 3 || s.X != 3 || s.pad != 1 || s.Rank > 16) return 0;
+  if (s.Y != 3 || s.X != 3 || s.pad != 1) return 0;
+  const int R = (int)std::min(s.Rank, 16u);   // larger ranks go through the kernel in slices of 16
   DeviceInfo di;
   int dev_count = 0;
   if (cudaGetDeviceCount(&dev_count) != cudaSuccess || dev_count <= 0 || device_info(&di) != B200CP_OK) return 0;
   Cp4BwdFilterArgs a{};
-  a.N = s.N; a.C = s.C; a.T = s.T; a.H = s.H; a.W = s.W; a.F = 3; a.pad = 1; a.R = s.Rank;
+  a.N = s.N; a.C = s.C; a.T = s.T; a.H = s.H; a.W = s.W; a.F = 3; a.pad = 1; a.R = R;
   GradGeom g;
   size_t smem;
   int nmb;
   if (!plan_grad(a, di, &g, &smem, &nmb)) return 0;
-  return (size_t)g.tiles * ((size_t)s.T + s.C + 6) * s.Rank * sizeof(float);
+  return (size_t)g.tiles * ((size_t)s.T + s.C + 6) * R * sizeof(float);
 }
 
 // Factor gradients from the saved rank planes; *done = false: not a shape this kernel takes.
