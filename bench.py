@@ -342,6 +342,11 @@ def main():
         x, du, u, dx = sets[i % NSETS]
         P._lib.check(lib.b200cp_cp4_bwd_data_save(C.byref(s), ptr(du), *fp, ptr(dx), ptr(Qp), st, flags))
 
+    def k_convs_save(i, st):
+        # the first launch of the timed step: forward and backward-data in one launch, both rank planes saved
+        x, du, u, dx = sets[i % NSETS]
+        P._lib.check(lib.b200cp_cp4_fwd_bwd_data(C.byref(s), ptr(x), ptr(du), *fp, ptr(u), ptr(dx), ptr(Pp), ptr(Qp), st, flags))
+
     def k_bwdf_saved(i, st):
         x, du, u, dx = sets[i % NSETS]
         P._lib.check(lib.b200cp_cp4_bwd_filter_saved(C.byref(s), ptr(x), ptr(du), ptr(Pp), ptr(Qp), fp[2], fp[3], ptr(dK),
@@ -501,7 +506,8 @@ def main():
     kernels = [("cp4_fwd", k_fwd, 0), ("cp4_bwd_data", k_bwdd, 0), ("cp4_bwd_filter", k_bwdf, 0)]
     if shared:   # the kernels of the step; third entry: bytes of rank planes they move on top of the algorithmic bytes
         kernels += [("cp4_fwd_save", k_fwd_save, 4 * plane_floats), ("cp4_bwd_data_save", k_bwdd_save, 4 * plane_floats),
-                    ("cp4_bwd_filter_saved", k_bwdf_saved, 8 * plane_floats)]
+                    ("cp4_bwd_filter_saved", k_bwdf_saved, 8 * plane_floats),
+                    ("cp4_fwd_bwd_data_save", k_convs_save, 8 * plane_floats)]
         k_fwd_save(0, cur_stream())      # the planes the saved-plane kernel reads
         k_bwdd_save(0, cur_stream())
     for _, fn, _ in kernels:
@@ -633,7 +639,11 @@ def main():
     # of the step writes or reads on top of that are traffic, not algorithmic bytes
     base_bytes = 4 * n * HW * (c["C"] + c["T"]) + 4 * c["R"] * (c["T"] + c["C"] + 2 * c["F"])
     kbytes = [base_bytes for k in kernels]
-    in_step = range(3, 6) if shared else range(0, 3)      # the kernels the timed step launches
+    if shared:
+        kbytes[6] = 2 * base_bytes                         # one launch that is two of the path's kernels
+    # The launches of the timed step: with shared planes forward and backward-data are one launch (entry 6) followed
+    # by the gradient kernels (entry 5); entries 3 and 4 are that launch's two halves run on their own.
+    in_step = (6, 5) if shared else range(0, 3)
     dom = max(in_step, key=lambda i: mean_ms[i])
     alg_bytes = kbytes[dom]
     peak, peak_kind = hbm_peak()
@@ -651,7 +661,9 @@ def main():
                 "step": {"bytes": 3 * base_bytes, "us": step_us, "frac": 3 * base_bytes / (step_us * 1e-6) / 1e9 / peak},
                 "per_kernel_us": {nm: float(v * 1e3) for nm, v in zip(names, mean_ms)},
                 "per_kernel_frac": {nm: float(b / (v * 1e-3) / 1e9 / peak) for nm, v, b in zip(names, mean_ms, kbytes)},
-                "kernels_in_step": [names[i] for i in in_step]}
+                "kernels_in_step": [names[i] for i in in_step],
+                "launches_in_step": [{"kernel": names[i], "us": float(mean_ms[i] * 1e3), "algorithmic_bytes": kbytes[i],
+                                      "frac": float(kbytes[i] / (mean_ms[i] * 1e-3) / 1e9 / peak)} for i in in_step]}
 
     cpu = None
     if not args.no_cpu_baseline:

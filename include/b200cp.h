@@ -130,6 +130,14 @@ int b200cp_cp4_step(const b200cp_tensor_shape* s, const float* X, const float* d
                     const float* KH, const float* KW, float* U, float* dX, float* dK_packed, void* workspace,
                     size_t workspace_bytes, void* stream, int flags);
 
+/* Forward of X and backward-data of dU in one call: the convolutions of a training step of a layer whose factors are
+ * frozen (cp4_conv2d_forward_gpu + cp4_conv2d_backward_data_gpu of the reference, one after the other), and the first
+ * launch of b200cp_cp4_step.  Where the shape allows it one launch carries both.  P and Q (both or neither, [N,R,H,W]
+ * each; 3x3 / pad 1 / AUTO or MMA only) receive the rank planes for b200cp_cp4_bwd_filter_saved. */
+int b200cp_cp4_fwd_bwd_data(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                            const float* K1, const float* KH, const float* KW, float* U, float* dX, float* P, float* Q,
+                            void* stream, int flags);
+
 /* The pieces of b200cp_cp4_step for callers that run the forward and the backward pass at different times
  * (an autograd function): the two convolutions that also write their rank plane (P = K1^T X from the forward,
  * Q = K0^T dU from backward-data; [N,R,H,W] fp32 each, caller-owned), and the factor gradients from the two

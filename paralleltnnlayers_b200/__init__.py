@@ -17,7 +17,8 @@ _OPS_NAMES = ("allclose", "CP3Conv2dFunction", "conv2d_cp_fused_nchw", "cp3_conv
               "cp4_conv2d_forward", "cp4_conv2d_nchw", "cp4_conv2d_step", "cp4_conv2d_step_host", "cp4_conv2d_step_host_submit",
               "cp4_conv2d_step_host_wait", "cp4recom", "dense_cp",
               "dense_cp_backward", "debug_cp4_tc", "device_status", "set_band_rows", "set_band_tcgen05", "set_stream", "set_band_tensor_loads", "rcp_conv2d_backward", "tensor_shape",
-              "conv2d_dense_forward", "cp4_conv2d_rebuild_forward", "rcp_recompose", "conv2d_rcp_rebuild_nchw",
+              "conv2d_dense_forward", "cp4_conv2d_forward_backward_data", "cp4_conv2d_backward_filter_saved",
+              "cp4_conv2d_forward_save", "cp4_conv2d_backward_data_save", "cp4_conv2d_rebuild_forward", "rcp_recompose", "conv2d_rcp_rebuild_nchw",
               "dense_cp_recompose", "dense_matmul", "dense_cp_rebuild")
 __all__ = list(_LIB_NAMES + _OPS_NAMES)
 

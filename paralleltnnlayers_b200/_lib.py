@@ -52,6 +52,7 @@ def _load():
         "b200cp_cp4_step_allreduce": (i, [vp, sp, fp, fp, fp, fp, fp, fp, fp, fp, fp, vp, sz, vp, i]),
         "b200cp_cp4_step_allreduce_pipelined": (i, [vp, sp, fp, fp, fp, fp, fp, fp, fp, fp, fp, fp, vp, sz, vp, i]),
         "b200cp_p2p_flush": (i, [vp, fp, vp]),
+        "b200cp_cp4_fwd_bwd_data": (i, [sp, fp, fp, fp, fp, fp, fp, fp, fp, fp, fp, vp, i]),
         "b200cp_cp4_fwd_save": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp, i]),
         "b200cp_cp4_bwd_data_save": (i, [sp, fp, fp, fp, fp, fp, fp, fp, vp, i]),
         "b200cp_cp4_bwd_filter_saved_workspace_bytes": (sz, [sp, i]),

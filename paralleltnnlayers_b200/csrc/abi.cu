@@ -613,6 +613,37 @@ int b200cp_cp4_bwd_data_save(const b200cp_tensor_shape* s, const float* dU, cons
   return run_conv(s, dU, K0, K1, KH, KW, dX, static_cast<cudaStream_t>(stream), flags, true, nullptr, Q);
 }
 
+// Forward of X and backward-data of dU in one call -- the two convolutions of a training step of a layer whose
+// factors are frozen, and the first launch of b200cp_cp4_step: where the row stream or the row bands take the shape,
+// one launch carries both (its CTAs share the factor planes and no SM idles between the two).  P / Q (both or
+// neither) receive the rank planes.
+int b200cp_cp4_fwd_bwd_data(const b200cp_tensor_shape* s, const float* X, const float* dU, const float* K0,
+                            const float* K1, const float* KH, const float* KW, float* U, float* dX, float* P, float* Q,
+                            void* stream, int flags) {
+  if (int rc = check_shape(s, "b200cp_cp4_fwd_bwd_data")) return rc;
+  if (int rc = check_ptrs("b200cp_cp4_fwd_bwd_data", {X, dU, K0, K1, KH, KW, U, dX})) return rc;
+  if ((P == nullptr) != (Q == nullptr))
+    return fail(B200CP_ERR_INVALID_ARG, "b200cp_cp4_fwd_bwd_data: P and Q go together");
+  if (P != nullptr) {
+    if (int rc = check_ptrs("b200cp_cp4_fwd_bwd_data", {P, Q})) return rc;
+    if (!step_shares_planes(s, flags))
+      return fail(B200CP_ERR_UNSUPPORTED, "b200cp_cp4_fwd_bwd_data: rank planes for 3x3 filters with pad 1 on the default (mma) path only");
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int path = path_of(flags);
+  if (s->Y == 3 && s->X == 3 && s->pad == 1 && s->Rank <= 32 &&
+      (path == B200CP_PATH_MMA || (path == B200CP_PATH_AUTO && g_auto_mma))) {
+    Cp4Args cv[2] = {conv_args(s, X, K0, K1, KH, KW, U, false, nullptr, P), conv_args(s, dU, K0, K1, KH, KW, dX, true, nullptr, Q)};
+    bool both = false;
+    if (int rc = cp4_stream_launch(cv, 2, st, &both)) return rc;
+    if (!both)
+      if (int rc = cp4_band_launch(cv, 2, st, &both)) return rc;
+    if (both) return B200CP_OK;
+  }
+  if (int rc = run_conv(s, X, K0, K1, KH, KW, U, st, flags, false, nullptr, P)) return rc;
+  return run_conv(s, dU, K0, K1, KH, KW, dX, st, flags, true, nullptr, Q);
+}
+
 size_t b200cp_cp4_bwd_filter_saved_workspace_bytes(const b200cp_tensor_shape* s, int flags) {
   (void)flags;
   if (check_shape(s, "b200cp_cp4_bwd_filter_saved_workspace_bytes")) return 0;

@@ -72,6 +72,25 @@ def cp4_conv2d_backward_data(Upstream, FT, FC, FY, FX, pad=1, flags=0):
     return out
 
 
+def cp4_conv2d_forward_backward_data(Input, Upstream, FT, FC, FY, FX, pad=1, flags=0, save=False):
+    """Forward of ``Input`` and backward-data of ``Upstream`` in one call (one launch where the shape allows it): the
+    two convolutions of a training step with frozen factors.  Returns ``(Out, dInput)``, with ``save`` also the rank
+    planes ``(P, Q)`` for ``cp4_conv2d_backward_filter_saved``."""
+    Input, Upstream = _dev(Input, "Input"), _dev(Upstream, "Upstream")
+    FT, FC, FY, FX = (_dev(t, n) for t, n in ((FT, "FT"), (FC, "FC"), (FY, "FY"), (FX, "FX")))
+    s = _shape_from(Input, FT, FC, FY, FX, pad)
+    if tuple(Upstream.shape) != (s.N, s.T, s.H, s.W):
+        raise ValueError("Upstream must be [N, T, H, W]")
+    U = torch.empty((s.N, s.T, s.H, s.W), device=Input.device, dtype=torch.float32)
+    dX = torch.empty_like(Input)
+    Pl = torch.empty((s.N, s.Rank, s.H, s.W), device=Input.device, dtype=torch.float32) if save else None
+    Ql = torch.empty_like(Pl) if save else None
+    with torch.cuda.device(Input.device):
+        check(lib.b200cp_cp4_fwd_bwd_data(C.byref(s), _p(Input), _p(Upstream), _p(FT), _p(FC), _p(FY), _p(FX), _p(U),
+                                          _p(dX), _p(Pl) if save else None, _p(Ql) if save else None, _stream(), flags))
+    return (U, dX, Pl, Ql) if save else (U, dX)
+
+
 def cp4_conv2d_backward_filter(dLdO, In, FT, FC, FY, FX, pad=1, flags=0, packed=False):
     """The four factor gradients of ``CP::Conv2dBackwardFilter``
     (Cuda_kernels/cp4Conv2d.cu:83-153): returns (dFT, dFC, dFY, dFX), or the

@@ -106,3 +106,39 @@ def test_stream_random_shapes_against_the_exact_kernels():
             scale = float(b.abs().max()) + 1e-30
             assert float((a - b).abs().max()) <= 2e-5 * scale, f"{what}: {nm}"
     P.device_status()
+
+
+def test_forward_and_backward_data_in_one_call():
+    """``b200cp_cp4_fwd_bwd_data``: one row-stream launch for both convolutions (with and without the rank planes),
+    two launches of other kernels where the stream does not take the shape; results as the separate calls give."""
+    import paralleltnnlayers_b200 as P
+    lib = P._lib.lib
+    for k, (N, C, T, H, W, R, one) in enumerate([(3, 64, 64, 20, 56, 16, True), (2, 24, 40, 9, 24, 5, True),
+                                                 (2, 16, 16, 12, 12, 6, False), (1, 128, 128, 28, 28, 32, False)]):
+        g = torch.Generator(device="cuda").manual_seed(77 + k)
+        X = torch.rand(N, C, H, W, device="cuda", generator=g) * 2 - 1
+        dU = torch.randn(N, T, H, W, device="cuda", generator=g)
+        K0 = torch.randn(T, R, device="cuda", generator=g) * 0.2
+        K1 = torch.randn(C, R, device="cuda", generator=g) * 0.2
+        KH = torch.randn(3, R, device="cuda", generator=g) * 0.5
+        KW = torch.randn(3, R, device="cuda", generator=g) * 0.5
+        Ue = P.cp4_conv2d_forward(X, K0, K1, KH, KW, 1)
+        dXe = P.cp4_conv2d_backward_data(dU, K0, K1, KH, KW, 1)
+        before = lib.b200cp_test_stream_launches()
+        U, dX = P.cp4_conv2d_forward_backward_data(X, dU, K0, K1, KH, KW, 1)
+        assert lib.b200cp_test_stream_launches() - before == (1 if one else 0)
+        U2, dX2, Pl, Ql = P.cp4_conv2d_forward_backward_data(X, dU, K0, K1, KH, KW, 1, save=True)
+        for a, b, nm in ((U, Ue, "forward"), (dX, dXe, "backward-data"), (U2, Ue, "forward + plane"), (dX2, dXe, "backward-data + plane")):
+            assert float((a - b).abs().max()) <= 2e-5 * (float(b.abs().max()) + 1e-30), f"case {k}: {nm}"
+        dK = P.cp4_conv2d_backward_filter_saved(dU, X, Pl, Ql, K0, K1, KH, KW, 1)
+        dKe = P.cp4_conv2d_backward_filter(dU, X, K0, K1, KH, KW, 1, flags=P.PATH_SIMT)
+        for i, (a, b) in enumerate(zip(dK, dKe)):
+            assert float((a - b).abs().max()) <= 3e-5 * (float(b.abs().max()) + 1e-30), f"case {k}: dK{i} from the planes"
+    # one plane without the other is an argument error, reported as a status
+    import ctypes
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    sh = P.tensor_shape(N, C, H, W, T, 3, 3, R, 1)
+    rc = lib.b200cp_cp4_fwd_bwd_data(ctypes.byref(sh), vp(X), vp(dU), vp(K0), vp(K1), vp(KH), vp(KW), vp(U), vp(dX), vp(Pl),
+                                     None, None, 0)
+    assert rc == -1
+    P.device_status()
